@@ -1,0 +1,7 @@
+from .manager import (CacheError, CacheGroupSpec, CacheManager, OutOfPages, OutOfStateSlots, PagePool, RequestCache,
+                      SlotPool)
+
+from .storage import CacheStorage, LayerCache
+
+__all__ = ["CacheStorage", "LayerCache", "CacheError", "CacheGroupSpec", "CacheManager", "OutOfPages", "OutOfStateSlots", "PagePool",
+           "RequestCache", "SlotPool"]

@@ -1,0 +1,75 @@
+// Shared helpers of the sm_100a kernels: element types, error reporting, reductions.
+//
+// Every launcher is `extern "C" int hb_*(..., cudaStream_t)`: 0 on success, a negative code
+// with a message in hb_last_error() otherwise (the reference prints and exits on a CUDA
+// error, src/hip_compat.h:95-97, and returns -1 on bad arguments, src/api.cu:1827-1839).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#define HB_EXPORT extern "C" __attribute__((visibility("default")))
+
+enum { HB_F32 = 0, HB_BF16 = 1 };
+
+void hb_set_error(const char* fmt, ...);
+
+#define HB_FAIL(...)            \
+  do {                          \
+    hb_set_error(__VA_ARGS__);  \
+    return -1;                  \
+  } while (0)
+
+#define HB_CHECK_LAUNCH(name)                                               \
+  do {                                                                      \
+    cudaError_t e_ = cudaGetLastError();                                    \
+    if (e_ != cudaSuccess) HB_FAIL("%s: %s", name, cudaGetErrorString(e_)); \
+  } while (0)
+
+__device__ __forceinline__ float hb_to_float(float v) { return v; }
+__device__ __forceinline__ float hb_to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T hb_from_float(float v);
+template <> __device__ __forceinline__ float hb_from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 hb_from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float hb_warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float hb_warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over the block in a fixed order (lane tree, then warps 0..n-1 in sequence); every thread
+// gets the result. `sh` holds at least 32 floats.
+__device__ __forceinline__ float hb_block_sum(float v, float* sh) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = hb_warp_sum(v);
+  __syncthreads();
+  if (lane == 0) sh[w] = v;
+  __syncthreads();
+  float t = 0.f;
+  for (int i = 0; i < nw; i++) t += sh[i];
+  return t;
+}
+
+// Calls f.template operator()<TA, TB>() for the element types named by two dtype codes.
+#define HB_DISPATCH_2(da, db, NAME, ...)                                                     \
+  do {                                                                                       \
+    if ((da) == HB_F32 && (db) == HB_F32) { using TA = float; using TB = float; __VA_ARGS__; }                      \
+    else if ((da) == HB_F32 && (db) == HB_BF16) { using TA = float; using TB = __nv_bfloat16; __VA_ARGS__; }        \
+    else if ((da) == HB_BF16 && (db) == HB_F32) { using TA = __nv_bfloat16; using TB = float; __VA_ARGS__; }        \
+    else if ((da) == HB_BF16 && (db) == HB_BF16) { using TA = __nv_bfloat16; using TB = __nv_bfloat16; __VA_ARGS__; } \
+    else HB_FAIL("%s: unknown dtype code %d/%d", NAME, (int)(da), (int)(db));                \
+  } while (0)
+
+#define HB_DISPATCH_1(da, NAME, ...)                                        \
+  do {                                                                      \
+    if ((da) == HB_F32) { using TA = float; __VA_ARGS__; }                  \
+    else if ((da) == HB_BF16) { using TA = __nv_bfloat16; __VA_ARGS__; }    \
+    else HB_FAIL("%s: unknown dtype code %d", NAME, (int)(da));             \
+  } while (0)

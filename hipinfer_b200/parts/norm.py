@@ -1,0 +1,38 @@
+"""RMSNorm: y = w * (x / sqrt(mean(x^2) + eps)), plain weight (not 1 + w), computed in
+32-bit from the 32-bit residual stream and rounded once (src/kernels.cuh:108-125 rounds x*r
+to fp16 before the product with w, to match a half-precision framework)."""
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+from ..weights import ParamSpec
+from .registry import Part, register_part, to_compute
+
+
+class RMSNorm(Part):
+    """params: name (tensor name relative to the prefix), size, eps."""
+
+    def __init__(self, params, ctx, prefix=""):
+        super().__init__(params, ctx, prefix)
+        self.size, self.eps = int(params["size"]), float(params["eps"])
+        self.name = prefix + params["name"]
+        self.weight = None
+
+    def param_specs(self):
+        return [ParamSpec(self.name, (self.size,), init="ones")]
+
+    def load(self, tensors):
+        self.weight = to_compute(tensors[self.name], self.ctx)
+
+    def weight_bytes(self):
+        return self.weight.numel() * self.weight.element_size()
+
+    def forward(self, x, rows=None, out=None):
+        M = x.shape[0] if rows is None else rows.numel()
+        if out is None:
+            out = torch.empty(M, self.size, dtype=self.ctx.dtype, device=x.device)
+        return ops.rmsnorm(x, self.weight, self.eps, out, rows)
+
+
+register_part("norm", "rmsnorm", RMSNorm)
