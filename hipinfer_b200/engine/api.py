@@ -1,0 +1,200 @@
+"""The Python entry point, in the manner of the reference's binding (scripts/hipinfer.py:334-516):
+
+    eng = Engine(path, max_batch=8, max_seq=2048, max_prefill=1024)
+    tokens = eng.generate(prompt_ids, n_new)            # greedy; n_new tokens, the first from the prompt
+    eng.close()
+
+with the same attribute names (`vocab, hidden, inter, layers, heads, kv_heads, head_dim,
+max_pos, tied, weight_bytes, kv_bytes_per_token`), the slot calls `prefill(slot, tokens, p0)`,
+`prefill_logits`, `decode(B, steps)`, `history(slot, start, n)`, `logits(B)`, and `ValueError`
+for bad arguments (scripts/hipinfer.py:386-390). What is new beside them: `dtype`
+("bfloat16" or "float32"), temperature sampling, requests through the scheduler
+(`add_request`, `step`, `run`), random weights, and `runner` for the step function itself.
+
+`max_batch` is the most requests live at a time, `max_seq` the longest sequence, `max_prefill`
+the token budget of a step (the reference's prefill chunk, src/api.cu:1788).
+"""
+from __future__ import annotations
+
+import itertools
+from typing import Dict, List, Optional, Sequence, Union
+
+import torch
+
+from ..cache import OutOfPages
+from ..config import ModelConfig, config_from_dict, load_config
+from ..sampling import Sampler, SamplingParams
+from .batch import StepEntry
+from .runner import ModelRunner, StepError
+from .scheduler import AdmissionError, Request, Scheduler
+
+
+class Engine:
+    def __init__(self, path: Optional[str] = None, max_batch: int = 8, max_seq: int = 2048, max_prefill: int = 1024,
+                 dtype: str = "bfloat16", device: str = "cuda:0", config: Union[ModelConfig, dict, None] = None,
+                 random_weights: Optional[int] = None, std: float = 0.02, page_size: int = 16,
+                 num_pages: Optional[int] = None):
+        kw = dict(dtype=dtype, device=device, page_size=page_size, num_pages=num_pages, max_model_len=max_seq,
+                  max_num_seqs=max_batch)
+        if path is not None:
+            self.runner = ModelRunner.from_folder(path, **kw)
+        elif config is not None and random_weights is not None:
+            cfg = config_from_dict(config) if isinstance(config, dict) else config
+            self.runner = ModelRunner.from_random(cfg, seed=random_weights, std=std, **kw)
+        else:
+            raise ValueError("Engine needs a model folder, or config= and random_weights=seed")
+        r = self.runner
+        self.max_batch, self.max_seq, self.max_prefill = max_batch, r.max_model_len, max_prefill
+        self.device, self.dtype = r.device, dtype
+        self.scheduler = Scheduler(r.cache, max_batch, max_prefill, r.max_model_len, r.spec.eos_token_ids)
+        self.sampler = Sampler(r.device)
+        c = r.config
+        self.vocab = r.spec.vocab_size
+        self.hidden = r.spec.hidden_size
+        self.max_pos = r.spec.max_position
+        for ours, theirs in (("inter", "intermediate_size"), ("layers", "num_hidden_layers"),
+                             ("heads", "num_attention_heads"), ("kv_heads", "num_key_value_heads"),
+                             ("head_dim", "head_dim"), ("tied", "tie_word_embeddings")):
+            setattr(self, ours, getattr(c, theirs, None))
+        self.weight_bytes = r.model.step_weight_bytes()
+        self.kv_bytes_per_token = r.storage.bytes_per_token()
+        self._ids = itertools.count()
+        self._slots: Dict[int, dict] = {}
+        self._last_logits: Dict[int, torch.Tensor] = {}
+
+    # ---------------------------------------------------------------- requests through the scheduler
+    def add_request(self, prompt: Sequence[int], n_new: int, temperature: float = 0.0, seed: int = 0,
+                    stop_token_ids: Sequence[int] = (), ignore_eos: bool = True, request_id=None):
+        for t in prompt:
+            if not (0 <= int(t) < self.vocab):
+                raise ValueError(f"token {t} is outside the vocabulary of {self.vocab}")
+        rid = next(self._ids) if request_id is None else request_id
+        params = SamplingParams(temperature, seed, n_new, tuple(stop_token_ids), ignore_eos)
+        try:
+            self.scheduler.add(Request(rid, [int(t) for t in prompt], params))
+        except AdmissionError as e:
+            raise ValueError(str(e)) from None
+        return rid
+
+    def step(self) -> List[Request]:
+        """One scheduler step: schedule, run the batch, sample, record. Returns requests finished in it."""
+        sched = self.scheduler.schedule()
+        if not sched:
+            if self.scheduler.has_work():
+                raise RuntimeError("the scheduler has work but could schedule nothing")
+            return []
+        entries = [StepEntry(s.request.request_id, s.request.tokens[s.start:s.start + s.n], [s.n - 1] if s.samples else [])
+                   for s in sched]
+        logits = self.runner.step(entries)
+        samplers = [s for s in sched if s.samples]
+        toks = self.sampler.sample(logits, [s.request.params for s in samplers],
+                                   [s.start + s.n for s in samplers])
+        return self.scheduler.update(sched, toks)
+
+    def run(self) -> Dict[object, List[int]]:
+        """Step until every added request has finished; {request id: produced tokens}."""
+        out = {}
+        while self.scheduler.has_work():
+            for req in self.step():
+                out[req.request_id] = list(req.output)
+        return out
+
+    def generate(self, prompt, n_new: int, graph: bool = True, temperature: float = 0.0, seed: int = 0):
+        """n_new tokens after `prompt` (the first comes from the prompt's last position).
+        A list of prompts gives a list of results; they run as one batch."""
+        many = bool(prompt) and isinstance(prompt[0], (list, tuple))
+        prompts = list(prompt) if many else [prompt]
+        ids = [self.add_request(p, n_new, temperature, seed) for p in prompts]
+        res = self.run()
+        outs = [res[i] for i in ids]
+        return outs if many else outs[0]
+
+    # ---------------------------------------------------------------- the reference's slot calls
+    def _slot_ok(self, slot):
+        if not (0 <= slot < self.max_batch):
+            raise ValueError(f"slot {slot} is outside [0, {self.max_batch})")
+
+    def _run_tokens(self, slot: int, tokens: Sequence[int], p0: int, all_logits: bool):
+        self._slot_ok(slot)
+        rid = ("slot", slot)
+        st = self._slots.get(slot)
+        if p0 == 0 and st is not None:
+            self.runner.end(rid)
+            st = None
+        if st is None:
+            st = self._slots[slot] = dict(tokens=[])
+        if p0 != len(st["tokens"]):
+            raise ValueError(f"slot {slot} holds {len(st['tokens'])} tokens; cannot continue at p0={p0}")
+        tokens = [int(t) for t in tokens]
+        if not tokens:
+            raise ValueError("prefill needs at least one token")
+        rows = []
+        try:
+            for t0 in range(0, len(tokens), self.max_prefill):
+                part = tokens[t0:t0 + self.max_prefill]
+                last = t0 + len(part) == len(tokens)
+                want = list(range(len(part))) if all_logits else ([len(part) - 1] if last else [])
+                lg = self.runner.step([StepEntry(rid, part, want)])
+                if lg.shape[0]:
+                    rows.append(lg)
+        except (StepError, OutOfPages) as e:
+            raise ValueError(str(e)) from None
+        st["tokens"].extend(tokens)
+        logits = torch.cat(rows) if len(rows) > 1 else rows[0]
+        self._last_logits[slot] = logits[-1]
+        return logits
+
+    def prefill(self, slot: int, tokens: Sequence[int], p0: int = 0) -> int:
+        """Run `tokens` at positions p0.. of `slot`; returns the first new token (greedy) and
+        keeps it as the slot's next input (src/api.cu:1771-1822)."""
+        logits = self._run_tokens(slot, tokens, p0, False)
+        tok = self.sampler.sample(logits[-1:], [SamplingParams()], [0])[0]
+        self._slots[slot]["next"] = tok
+        return tok
+
+    def prefill_logits(self, slot: int, tokens: Sequence[int], p0: int = 0) -> torch.Tensor:
+        """Prefill and return the float32 logits of every position, [T, vocab] on the GPU."""
+        return self._run_tokens(slot, tokens, p0, True)
+
+    def decode(self, B: int, steps: int, graph: bool = True) -> float:
+        """`steps` greedy tokens for slots [0, B), each from its own position; returns GPU milliseconds."""
+        if not (1 <= B <= self.max_batch) or any(s not in self._slots or "next" not in self._slots[s] for s in range(B)):
+            raise ValueError(f"decode needs slots [0, {B}) prefilled")
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        try:
+            for _ in range(steps):
+                entries = [StepEntry(("slot", s), [self._slots[s]["next"]], [0]) for s in range(B)]
+                logits = self.runner.step(entries)
+                toks = self.sampler.sample(logits, [SamplingParams()] * B, [0] * B)
+                for s in range(B):
+                    self._slots[s]["tokens"].append(self._slots[s]["next"])
+                    self._slots[s]["next"] = toks[s]
+                    self._last_logits[s] = logits[s]
+        except (StepError, OutOfPages) as e:
+            raise ValueError(str(e)) from None
+        stop.record()
+        stop.synchronize()
+        return start.elapsed_time(stop)
+
+    def history(self, slot: int, start: int, n: int) -> List[int]:
+        """Tokens of `slot` at positions [start, start + n): the prompt, then what was generated."""
+        self._slot_ok(slot)
+        st = self._slots.get(slot)
+        seq = (st["tokens"] + [st["next"]]) if st and "next" in st else (st["tokens"] if st else [])
+        if start < 0 or n < 0 or start + n > len(seq):
+            raise ValueError(f"slot {slot} holds positions [0, {len(seq)}); asked for [{start}, {start + n})")
+        return seq[start:start + n]
+
+    def logits(self, B: int) -> torch.Tensor:
+        """The last logits of slots [0, B), float32 [B, vocab] on the GPU."""
+        if any(s not in self._last_logits for s in range(B)):
+            raise ValueError(f"logits needs slots [0, {B}) run")
+        return torch.stack([self._last_logits[s] for s in range(B)])
+
+    def close(self):
+        self.runner = None
+        self.scheduler = None
+        self._slots.clear()
+        self._last_logits.clear()
+        torch.cuda.empty_cache()

@@ -17,6 +17,7 @@ import os
 import struct
 from typing import Dict, Iterable, List, Tuple
 
+import numpy as np
 import torch
 
 _DTYPES = {
@@ -76,8 +77,8 @@ class SafetensorsFile:
         dt, shape, b, e = self._entries[name]
         if e == b:
             return torch.empty(shape, dtype=dt)
-        raw = torch.frombuffer(self._map, dtype=torch.uint8, count=e - b, offset=self._base + b)
-        return raw.clone().view(dt).reshape(shape)
+        raw = np.frombuffer(self._map, dtype=np.uint8, count=e - b, offset=self._base + b).copy()
+        return torch.from_numpy(raw).view(dt).reshape(shape)
 
     def close(self):
         if self._map is not None:
