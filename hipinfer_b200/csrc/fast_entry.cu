@@ -1,0 +1,14 @@
+// Error reporting of the `fast` library (the tensor-core and small-batch bf16 kernels).
+#include "common.cuh"
+
+#include <stdarg.h>
+
+static thread_local char g_err[512];
+void hb_set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof g_err, fmt, ap);
+  va_end(ap);
+}
+HB_EXPORT const char* hb_last_error() { return g_err; }
+HB_EXPORT int hb_fast_abi_version() { return 1; }

@@ -1,0 +1,283 @@
+// C[M,N] = A[M,K] W[N,K]^T on the 5th-generation tensor cores: bf16 operands brought into
+// shared memory by TMA (128-byte swizzle, K-major, no multicast), tcgen05.mma issued by one
+// thread, fp32 accumulators in tensor memory, read back with tcgen05.ld for the epilogue.
+//
+// One persistent CTA per SM walks tiles of 128 x BN; six warps: 0-3 epilogue (each owns the
+// 32 TMEM lanes it may touch), 4 the TMA producer, 5 the MMA issuer and TMEM owner. The
+// accumulator is double-buffered in TMEM, so the epilogue of one tile overlaps the main loop
+// of the next. K runs in blocks of 64 in ascending order for every tile: an output's value does
+// not depend on M or on which tile it lies in.
+//
+// Epilogues: store fp32 / store bf16 / add into the fp32 residual stream (the reference's
+// epilogue 1, src/kernels.cuh:881-889) / SwiGLU over gate and up columns interleaved in groups
+// of 16 (its epilogue 2, src/kernels.cuh:850-863). Replaces gemm_mma_kernel (src/kernels.cuh:585).
+// Every mbarrier wait is bounded; a wait that runs out raises the status word and the kernel
+// drains and returns.
+#include "tc_common.cuh"
+
+enum { EPI_F32 = 0, EPI_BF16 = 1, EPI_ADD_F32 = 2, EPI_SWIGLU_BF16 = 3 };
+
+constexpr int BM = 128, BK = 64;
+
+template <int BN, int STAGES>
+struct GemmSmem {
+  static constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;  // barriers + slack to align the base to 1024
+};
+
+template <int EPI>
+__device__ __forceinline__ void epilogue_store(const float* v, void* C, long ldc, int row, int col0, int M, int N) {
+  // v: 32 consecutive columns col0.. of `row`
+  if (row >= M) return;
+  if (EPI == EPI_SWIGLU_BF16) {
+    // columns [0,16) gate, [16,32) up of outputs (col0/2) .. +15
+    __nv_bfloat16* out = (__nv_bfloat16*)C + (size_t)row * ldc + (col0 >> 1);
+    const int n_out = N >> 1, o0 = col0 >> 1;
+    __align__(16) __nv_bfloat16 r[16];
+#pragma unroll
+    for (int j = 0; j < 16; j++) {
+      const float g = v[j], u = v[16 + j];
+      r[j] = __float2bfloat16_rn(g / (1.f + __expf(-g)) * u);
+    }
+    if (o0 + 16 <= n_out && ((ldc & 7) == 0)) {
+      *(uint4*)(out) = *(const uint4*)(r);
+      *(uint4*)(out + 8) = *(const uint4*)(r + 8);
+    } else {
+      for (int j = 0; j < 16 && o0 + j < n_out; j++) out[j] = r[j];
+    }
+  } else if (EPI == EPI_BF16) {
+    __nv_bfloat16* out = (__nv_bfloat16*)C + (size_t)row * ldc + col0;
+    if (col0 + 32 <= N && ((ldc & 7) == 0)) {
+      __align__(16) __nv_bfloat16 r[32];
+#pragma unroll
+      for (int j = 0; j < 32; j++) r[j] = __float2bfloat16_rn(v[j]);
+#pragma unroll
+      for (int j = 0; j < 4; j++) *(uint4*)(out + 8 * j) = *(const uint4*)(r + 8 * j);
+    } else {
+      for (int j = 0; j < 32 && col0 + j < N; j++) out[j] = __float2bfloat16_rn(v[j]);
+    }
+  } else {
+    float* out = (float*)C + (size_t)row * ldc + col0;
+    if (col0 + 32 <= N && ((ldc & 3) == 0)) {
+#pragma unroll
+      for (int j = 0; j < 8; j++) {
+        float4 o = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        if (EPI == EPI_ADD_F32) {
+          const float4 c = *(const float4*)(out + 4 * j);
+          o.x += c.x; o.y += c.y; o.z += c.z; o.w += c.w;
+        }
+        *(float4*)(out + 4 * j) = o;
+      }
+    } else {
+      for (int j = 0; j < 32 && col0 + j < N; j++) out[j] = EPI == EPI_ADD_F32 ? out[j] + v[j] : v[j];
+    }
+  }
+}
+
+template <int BN, int STAGES, int EPI>
+__global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                         const __grid_constant__ CUtensorMap map_w, void* C, long ldc,
+                                                         int M, int N, int K, int* status) {
+  using S = GemmSmem<BN, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* full = (uint64_t*)(smem + S::BAR_OFFSET);
+  uint64_t* empty = full + STAGES;
+  uint64_t* tmem_full = empty + STAGES;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_slot = (uint32_t*)(tmem_empty + 2);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN, num_tiles = m_tiles * n_tiles;
+  const int num_kb = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; s++) { hb_mbar_init(&full[s], 1); hb_mbar_init(&empty[s], 1); }
+    for (int b = 0; b < 2; b++) { hb_mbar_init(&tmem_full[b], 1); hb_mbar_init(&tmem_empty[b], 4); }
+    *abort_flag = 0;
+    hb_fence_barrier_init();
+  }
+  if (warp == 5) {
+    hb_tmem_alloc(tmem_slot, 2 * BN);
+    hb_tmem_relinquish();
+  }
+  if (warp == 4 && lane == 0) { hb_tma_prefetch_desc(&map_a); hb_tma_prefetch_desc(&map_w); }
+  hb_tc_fence_before();
+  __syncthreads();
+  hb_tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 4) {
+    if (lane == 0) {  // ---------------- TMA producer
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
+        for (int kb = 0; kb < num_kb; kb++, it++) {
+          const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+          if (!hb_mbar_wait(&empty[s], ph ^ 1, abort_flag)) { ok = false; break; }
+          hb_mbar_expect_tx(&full[s], S::STAGE_BYTES);
+          hb_tma_load_2d(smem + s * S::STAGE_BYTES, &map_a, &full[s], kb * BK, m0);
+          hb_tma_load_2d(smem + s * S::STAGE_BYTES + S::A_BYTES, &map_w, &full[s], kb * BK, n0);
+        }
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {  // ---------------- MMA issuer
+      constexpr uint32_t idesc = hb_umma_idesc_bf16(BM, BN);
+      uint32_t it = 0, tile_i = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, tile_i++) {
+        const uint32_t buf = tile_i & 1, aph = (tile_i >> 1) & 1;
+        if (!hb_mbar_wait(&tmem_empty[buf], aph ^ 1, abort_flag)) break;
+        hb_tc_fence_after();
+        const uint32_t d = tmem_base + buf * BN;
+        for (int kb = 0; kb < num_kb; kb++, it++) {
+          const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+          if (!hb_mbar_wait(&full[s], ph, abort_flag)) { ok = false; break; }
+          hb_tc_fence_after();
+          const uint64_t da = hb_umma_desc_k128(hb_smem_u32(smem + s * S::STAGE_BYTES));
+          const uint64_t db = hb_umma_desc_k128(hb_smem_u32(smem + s * S::STAGE_BYTES + S::A_BYTES));
+#pragma unroll
+          for (int k = 0; k < BK / 16; k++) hb_umma_bf16(d, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+          hb_umma_commit(&empty[s]);
+        }
+        if (ok) hb_umma_commit(&tmem_full[buf]);
+      }
+    }
+  } else {  // ---------------- epilogue warps 0..3
+    uint32_t tile_i = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, tile_i++) {
+      const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
+      const uint32_t buf = tile_i & 1, aph = (tile_i >> 1) & 1;
+      if (!hb_mbar_wait(&tmem_full[buf], aph, abort_flag)) break;
+      hb_tc_fence_after();
+      const int row = m0 + warp * 32 + lane;
+      const uint32_t t0 = tmem_base + ((uint32_t)(warp * 32) << 16) + buf * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; c++) {
+        float v[32];
+        hb_tmem_ld32(t0 + c * 32, v);
+        if (n0 + c * 32 < N) epilogue_store<EPI>(v, C, ldc, row, n0 + c * 32, M, N);
+      }
+      hb_tc_fence_before();
+      __syncwarp();
+      if (lane == 0) hb_mbar_arrive(&tmem_empty[buf]);
+    }
+  }
+
+  hb_tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    if (threadIdx.x == 0) atomicExch(status, 1);
+    __nanosleep(100000);  // let copies that may still be in flight land before the shared memory is given up
+  }
+  if (warp == 5) {
+    __syncwarp();
+    hb_tmem_dealloc(tmem_base, 2 * BN);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+int hb_make_tensor_map_bf16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t row_stride_elems,
+                            uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) HB_FAIL("cuTensorMapEncodeTiled is not available from this driver");
+  if (((uintptr_t)base & 15) || (row_stride_elems * 2) % 16)
+    HB_FAIL("tensor map: base %p and row stride %llu elements must be 16-byte aligned", base,
+            (unsigned long long)row_stride_elems);
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {row_stride_elems * 2};
+  const cuuint32_t box[2] = {64, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) HB_FAIL("cuTensorMapEncodeTiled failed with code %d (rows %llu, cols %llu)", (int)r,
+                                 (unsigned long long)rows, (unsigned long long)cols);
+  return 0;
+}
+
+static int sm_count() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return n;
+}
+
+template <int BN, int STAGES, int EPI>
+static int launch_gemm_tc(const CUtensorMap& ma, const CUtensorMap& mw, void* C, long ldc, int M, int N, int K,
+                          int* status, cudaStream_t s) {
+  using S = GemmSmem<BN, STAGES>;
+  auto kern = gemm_tc_kernel<BN, STAGES, EPI>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+    if (e != cudaSuccess) HB_FAIL("hb_gemm_tc: %s", cudaGetErrorString(e));
+    configured = true;
+  }
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  kern<<<grid, 192, S::TOTAL, s>>>(ma, mw, C, ldc, M, N, K, status);
+  return 0;
+}
+
+template <int BN, int STAGES>
+static int dispatch_epi(int epi, const CUtensorMap& ma, const CUtensorMap& mw, void* C, long ldc, int M, int N, int K,
+                        int* status, cudaStream_t s) {
+  switch (epi) {
+    case EPI_F32: return launch_gemm_tc<BN, STAGES, EPI_F32>(ma, mw, C, ldc, M, N, K, status, s);
+    case EPI_BF16: return launch_gemm_tc<BN, STAGES, EPI_BF16>(ma, mw, C, ldc, M, N, K, status, s);
+    case EPI_ADD_F32: return launch_gemm_tc<BN, STAGES, EPI_ADD_F32>(ma, mw, C, ldc, M, N, K, status, s);
+    case EPI_SWIGLU_BF16: return launch_gemm_tc<BN, STAGES, EPI_SWIGLU_BF16>(ma, mw, C, ldc, M, N, K, status, s);
+  }
+  HB_FAIL("hb_gemm_tc: unknown epilogue %d", epi);
+}
+
+// C (+)= A W^T. A [M, K] bf16 (row stride lda), W [N, K] bf16 (row stride ldw); C per `epi`:
+// 0 fp32 [M, N], 1 bf16 [M, N], 2 fp32 += , 3 bf16 [M, N/2] = SwiGLU over 16-interleaved gate/up
+// columns. `status` is a device-visible word that is set to 1 if a wait ran out.
+// tile_n: 128 or 256 (0: chosen from M, N alone).
+HB_EXPORT int hb_gemm_tc(const void* A, long lda, const void* W, long ldw, void* C, long ldc, int M, int N, int K,
+                         int epi, int tile_n, int* status, cudaStream_t s) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || (K & 7)) HB_FAIL("hb_gemm_tc: K = %d must be a positive multiple of 8 (16-byte rows for TMA)", K);
+  if (epi == EPI_SWIGLU_BF16 && (N & 31)) HB_FAIL("hb_gemm_tc: SwiGLU needs N = %d to be a multiple of 32", N);
+  if (!status) HB_FAIL("hb_gemm_tc: no status word");
+  if (tile_n == 0) {
+    const long tiles256 = (long)((M + BM - 1) / BM) * ((N + 255) / 256);
+    tile_n = (N >= 256 && tiles256 >= 2L * sm_count()) ? 256 : 128;
+  }
+  if (tile_n != 128 && tile_n != 256) HB_FAIL("hb_gemm_tc: tile_n must be 128 or 256");
+  CUtensorMap ma, mw;
+  if (hb_make_tensor_map_bf16(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM)) return -1;
+  if (hb_make_tensor_map_bf16(&mw, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, (uint32_t)tile_n)) return -1;
+  int r = tile_n == 256 ? dispatch_epi<256, 4>(epi, ma, mw, C, ldc, M, N, K, status, s)
+                        : dispatch_epi<128, 6>(epi, ma, mw, C, ldc, M, N, K, status, s);
+  if (r) return r;
+  HB_CHECK_LAUNCH("hb_gemm_tc");
+  return 0;
+}

@@ -1,2 +1,146 @@
-// placeholder until the tensor-core kernels arrive
+// Blackwell (sm_100a) building blocks in inline PTX: mbarriers with BOUNDED waits, TMA tile
+// loads (never multicast), tensor memory allocation, tcgen05.mma with shared-memory operand
+// descriptors, tcgen05.ld for the epilogue, and the legacy mma.sync used by the small-batch
+// kernels. A wait that runs out sets an error word and lets the kernel return; nothing traps.
 #pragma once
+#include "common.cuh"
+
+#include <cuda.h>
+
+#define HB_WAIT_LIMIT (1u << 20)  // try_wait polls before a wait gives up (each poll may itself suspend briefly)
+
+__device__ __forceinline__ uint32_t hb_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+// ---------------------------------------------------------------- mbarrier
+__device__ __forceinline__ void hb_mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(hb_smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void hb_fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void hb_fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void hb_mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(hb_smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void hb_mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(hb_smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool hb_mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(hb_smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Waits for the phase of `parity` to complete. Gives up after HB_WAIT_LIMIT polls or as soon as
+// another role raised *abort (shared memory); then it raises *abort itself and returns false.
+__device__ __forceinline__ bool hb_mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort) {
+  for (uint32_t i = 0; i < HB_WAIT_LIMIT; i++) {
+    if (hb_mbar_try_wait(bar, parity)) return true;
+    if ((i & 63u) == 63u && *abort) return false;
+  }
+  *abort = 1;
+  return false;
+}
+
+// ---------------------------------------------------------------- TMA (tile mode, no multicast)
+__device__ __forceinline__ void hb_tma_prefetch_desc(const CUtensorMap* m) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)m) : "memory");
+}
+// The innermost coordinate c0 times the element size must be a multiple of 16 bytes.
+__device__ __forceinline__ void hb_tma_load_2d(void* dst, const CUtensorMap* m, uint64_t* bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(hb_smem_u32(dst)), "l"((uint64_t)m), "r"(hb_smem_u32(bar)), "r"(c0), "r"(c1)
+      : "memory");
+}
+
+// ---------------------------------------------------------------- tensor memory
+__device__ __forceinline__ void hb_tmem_alloc(uint32_t* dst_smem, uint32_t ncols) {  // one whole warp
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(hb_smem_u32(dst_smem)), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void hb_tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void hb_tmem_dealloc(uint32_t taddr, uint32_t ncols) {  // the warp that allocated
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void hb_tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void hb_tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// ---------------------------------------------------------------- tcgen05.mma
+// Shared-memory operand descriptor for a K-major tile whose rows are 64 bf16 = 128 bytes,
+// written by TMA with the 128-byte swizzle: 8-row groups are 1024 bytes apart (SBO), the
+// leading offset is unused for this layout, version 1, layout type 2 (SWIZZLE_128B). The tile
+// base must be 1024-byte aligned; a step of 16 elements along K adds 32 bytes to the address.
+__device__ __forceinline__ uint64_t hb_umma_desc_k128(uint32_t smem_addr) {
+  return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+         ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// Instruction descriptor, kind::f16: D fp32, A and B bf16, both K-major, dense, M x N.
+__host__ __device__ constexpr uint32_t hb_umma_idesc_bf16(int M, int N) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+__device__ __forceinline__ void hb_umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                             uint32_t accumulate) {  // one thread
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives on `bar` once every tcgen05.mma issued so far by this thread has completed.
+__device__ __forceinline__ void hb_umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(hb_smem_u32(bar))
+               : "memory");
+}
+
+// ---------------------------------------------------------------- tcgen05.ld
+// 32 lanes x 32 consecutive columns of fp32: thread i of the warp gets lane (base lane + i),
+// v[j] = column (base column + j). A warp may only touch lanes 32 * (warp % 4) .. + 31.
+__device__ __forceinline__ void hb_tmem_ld32(uint32_t taddr, float* v) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
+}
+
+// ---------------------------------------------------------------- legacy warp MMA (small batches)
+// D[16x8] += A[16x16] * B[16x8], bf16 in, fp32 accumulate.
+__device__ __forceinline__ void hb_mma_16816(float* d, const uint32_t* a, const uint32_t* b) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+// 16-byte global load that does not pollute L1 (weights are read once per step).
+__device__ __forceinline__ uint4 hb_ldg_stream(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+// Host side: a 2-D bf16 tensor map [rows, cols] (cols contiguous) with a box of box_rows x 64
+// columns and the 128-byte swizzle. Returns 0 or -1 (message in hb_last_error).
+int hb_make_tensor_map_bf16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t row_stride_elems,
+                            uint32_t box_rows);
