@@ -1,0 +1,296 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of hipinfer_b200 at Llama-3.2-1B shape with random weights.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L] [--impl ours|reference]
+
+One JSON line on stdout. `value` is decoded tokens a second at the given batch: K decode steps
+(forward from the paged cache + on-device sampling, the sampled tokens feeding the next step on
+the device) timed with CUDA events after W warm-up steps; the requests hold 2,048-token random
+prompts, so the steps run at contexts 2,048 + W .. 2,048 + W + K. `e2e` is the same through
+`Engine.step()` (scheduler, host tokens in and out). `prefill` is one 2,048-token prompt in one
+step. `roofline` divides the bytes a decode step has to read (every weight it uses once, and the
+cache of the live requests) by its time. Peaks come from MEASURED_PEAKS.json beside this file,
+else from the fallback figures. The reference measures the same quantities in
+scripts/bench.py:384-449 (decode over many replayed steps, floor = weight + cache bytes / peak).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# BASELINE configs[2]: Llama-3.2-1B shape
+MODEL = dict(architectures=["LlamaForCausalLM"], vocab_size=128256, hidden_size=2048, intermediate_size=8192,
+             num_hidden_layers=16, num_attention_heads=32, num_key_value_heads=8, head_dim=64,
+             max_position_embeddings=131072, rms_norm_eps=1e-5, rope_theta=500000.0,
+             rope_scaling=dict(rope_type="llama3", factor=32.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                               original_max_position_embeddings=8192),
+             tie_word_embeddings=True, hidden_act="silu")
+CONTEXT_LEN, PROMPT_LEN, PREFILL_TOKENS, PAGE = 4096, 2048, 2048, 16
+FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0)
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(p):
+        with open(p) as f:
+            d = json.load(f)
+        return dict(hbm_gbs=float(d["hbm_gbs"]), bf16_tflops=float(d["bf16_tflops"]),
+                    bf16_tflops_sustained=float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), source="measured")
+    return dict(FALLBACK_PEAKS, source="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons while the timed region runs (reading only)."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows, self.proc = [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm = [int(r[0]) for r in self.rows if len(r) >= 6 and r[0].isdigit()]
+        mx = [int(r[1]) for r in self.rows if len(r) >= 6 and r[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) >= 6 and r[2 + i].lower().startswith("active") for r in self.rows)]
+        return dict(sm_mhz=int(statistics.median(sm)) if sm else None, sm_max_mhz=max(mx) if mx else None,
+                    reasons=reasons, samples=len(sm))
+
+
+def build_engine(layers: int, max_batch: int, total_steps: int):
+    import torch  # noqa: F401
+    from hipinfer_b200 import Engine
+
+    cfg = dict(MODEL, num_hidden_layers=layers)
+    pages_per_seq = -(-(PROMPT_LEN + total_steps + 2 * PAGE) // PAGE)
+    return Engine(config=cfg, random_weights=0, std=0.02, dtype="bfloat16", max_batch=max_batch, max_seq=CONTEXT_LEN,
+                  max_prefill=PREFILL_TOKENS, page_size=PAGE, num_pages=max_batch * pages_per_seq + 8)
+
+
+def prompts(n, seed):
+    import torch
+
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, MODEL["vocab_size"], (n, PROMPT_LEN), generator=g).tolist()
+
+
+def decode_device(eng, batch: int, steps: int, warmup: int, sampler=None):
+    """K decode steps timed on the device; the sampled tokens stay on the device. Returns
+    (ms per step, mean context of the timed steps, launches per step)."""
+    import torch
+
+    from hipinfer_b200.engine import StepEntry
+    from hipinfer_b200.kernels import library, ops
+
+    runner = eng.runner
+    ids = [("bench", batch, i) for i in range(batch)]
+    first = []
+    for rid, p in zip(ids, prompts(batch, 1)):
+        logits = runner.step([StepEntry(rid, p, [PROMPT_LEN - 1])])
+        first.append(ops.sample(logits, None, None, None))
+    tokens = torch.cat(first).contiguous()
+    entries = [StepEntry(rid, [0], [0]) for rid in ids]
+
+    def one():
+        logits = runner.step(entries, device_tokens=tokens)
+        ops.sample(logits, None, None, None, out=tokens)
+
+    for _ in range(warmup):
+        one()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    l0 = library.launches[0]
+    with (sampler or _Null()):
+        start.record()
+        for _ in range(steps):
+            one()
+        stop.record()
+        stop.synchronize()
+    ms = start.elapsed_time(stop) / steps
+    launches = (library.launches[0] - l0) / steps
+    from hipinfer_b200.kernels import fast
+    fast.check_status()
+    for rid in ids:
+        runner.end(rid)
+    return ms, PROMPT_LEN + warmup + (steps - 1) / 2.0 + 1, launches
+
+
+class _Null:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        pass
+
+
+def decode_e2e(eng, batch: int, steps: int, warmup: int):
+    """The same through Engine.step(): scheduler, batch built on the host and copied from pinned
+    memory every step, sampled tokens read back every step. Wall clock around synchronised ends."""
+    import torch
+
+    for p in prompts(batch, 2):
+        eng.add_request(p, warmup + steps + 1)
+    while any(not r.decoding for r in eng.scheduler.running) or eng.scheduler.waiting:
+        eng.step()
+    for _ in range(warmup):
+        eng.step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(steps - 1):
+        eng.step()
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    eng.run()
+    groups = len(eng.runner.cache.groups)
+    width = -(-CONTEXT_LEN // PAGE)
+    n_int = 3 * batch + 4 * batch + batch + groups * batch * width + groups * batch
+    return dt / (steps - 1) * 1e3, n_int * 4, batch * 4
+
+
+def prefill_device(eng, warmup: int, reps: int):
+    import torch
+
+    from hipinfer_b200.engine import StepEntry
+    from hipinfer_b200.kernels import fast
+
+    runner = eng.runner
+    toks = prompts(1, 3)[0][:PREFILL_TOKENS]
+    times = []
+    for i in range(warmup + reps):
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        runner.step([StepEntry(("prefill", i), toks, [PREFILL_TOKENS - 1])])
+        stop.record()
+        stop.synchronize()
+        runner.end(("prefill", i))
+        if i >= warmup:
+            times.append(start.elapsed_time(stop))
+    fast.check_status()
+    return statistics.median(times)
+
+
+def prefill_flops(layers: int) -> float:
+    m, T = MODEL, PREFILL_TOKENS
+    H, I, D, Hq, Hkv, V = (m["hidden_size"], m["intermediate_size"], m["head_dim"], m["num_attention_heads"],
+                           m["num_key_value_heads"], m["vocab_size"])
+    per_layer = (Hq + 2 * Hkv) * D * H + H * Hq * D + 3 * I * H
+    linear = 2.0 * T * per_layer * layers
+    attention = 4.0 * Hq * D * (T * (T + 1) / 2) * layers   # causal: q k^T and p v over the visible keys
+    return linear + attention + 2.0 * V * H
+
+
+def reference_arm(a) -> int:
+    """The unmodified reference through its own API. It is installed offline into baseline/_ref by
+    the one pip command the contract names; where that cannot be done this arm says so."""
+    why = reference_unavailable()
+    print(json.dumps({"impl": "reference", "unavailable": why}))
+    return 0
+
+
+def reference_unavailable() -> str:
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(ref) or not os.listdir(ref):
+        return ("Sky1219/hipinfer has no setup.py/pyproject.toml: it is a Makefile project (one nvcc line building "
+                "libhipinfer.so) and cannot be pip-installed offline into baseline/_ref")
+    return "baseline/_ref holds no importable hipinfer package"
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=MODEL["num_hidden_layers"],
+                    help="fewer layers than the configuration has (both numbers are reported)")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 decode points")
+    a = ap.parse_args()
+    if a.impl == "reference":
+        return reference_arm(a)
+    if a.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {a.gpus} is not supported")
+        return 2
+    if a.warmup < 3:
+        a.warmup = 3
+    import torch
+
+    pk = peaks()
+    point_batches = [] if a.no_points else [b for b in (1, 64) if b != a.batch]
+    max_batch = max([a.batch] + point_batches)
+    eng = build_engine(a.layers, max_batch, a.steps + a.warmup + 8)
+    clocks = ClockSampler()
+    ms, mean_ctx, launches = decode_device(eng, a.batch, a.steps, a.warmup, clocks)
+    value = a.batch / ms * 1e3
+    step_bytes = eng.weight_bytes + a.batch * mean_ctx * eng.kv_bytes_per_token
+    achieved = step_bytes / ms / 1e6
+    points = {f"decode_b{a.batch}": round(value, 1)}
+    for b in point_batches:
+        pms, _, _ = decode_device(eng, b, min(a.steps, 64), a.warmup)
+        points[f"decode_b{b}"] = round(b / pms * 1e3, 1)
+    pre_ms = prefill_device(eng, 3, 5)
+    pre_frac = prefill_flops(a.layers) / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12)
+    e2e_ms, h2d, d2h = decode_e2e(eng, a.batch, min(a.steps, 64), a.warmup)
+    out = {
+        "metric": "decode tok/s at batch 8 (Llama-3.2-1B shape, 2,048-token prompts)" if a.batch == 8 else
+                  f"decode tok/s at batch {a.batch} (Llama-3.2-1B shape, 2,048-token prompts)",
+        "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": a.steps, "warmup": a.warmup,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: uniform-random token ids, random N(0, 0.02) bf16 weights",
+        "impl": "ours",
+        "config": {"model": "Llama-3.2-1B shape", "layers": a.layers, "layers_full": MODEL["num_hidden_layers"],
+                   "hidden": MODEL["hidden_size"], "heads": MODEL["num_attention_heads"],
+                   "kv_heads": MODEL["num_key_value_heads"], "head_dim": MODEL["head_dim"],
+                   "intermediate": MODEL["intermediate_size"], "vocab": MODEL["vocab_size"], "global_batch": a.batch,
+                   "seq_len": CONTEXT_LEN, "prompt_len": PROMPT_LEN, "page_size": PAGE, "kv_dtype": "bf16",
+                   "parallelism": "single GPU",
+                   "l2": f"inputs larger than L2: {eng.weight_bytes / 1e9:.2f} GB of weights read per step"},
+        "clocks": clocks.summary(),
+        "e2e": {"value": round(a.batch / e2e_ms * 1e3, 1), "unit": "tok/s", "ms_per_step": round(e2e_ms, 4),
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": int(round(launches * a.steps)),
+        "prefill": {"value": round(PREFILL_TOKENS / pre_ms * 1e3, 1), "tokens": PREFILL_TOKENS, "ms": round(pre_ms, 4),
+                    "frac": round(pre_frac, 4), "peak_tflops": pk["bf16_tflops"], "peaks": pk["source"]},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4), "peaks": pk["source"],
+                     "bytes_per_step": int(step_bytes), "mean_context": mean_ctx},
+        "points": points,
+    }
+    eng.close()
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -382,6 +382,22 @@ HB_EXPORT int hb_attn_rows(const void* q, int q_dt, const void* kc, const void* 
   return 0;
 }
 
+// Finishes rows that span several key chunks from partials laid out as hb_attn_rows leaves them
+// (for attention kernels of other libraries that write the same partials).
+HB_EXPORT int hb_attn_merge(float* workspace, const int* pos, void* out, int out_dt, int T, int Hq, int D, int window,
+                            int chunk, int max_pos, cudaStream_t s) {
+  const int S = max_pos / chunk + 1;
+  if (T <= 0 || S <= 1) return 0;
+  if (!workspace) HB_FAIL("hb_attn_merge: no workspace");
+  float* part_acc = workspace;
+  float* part_ml = workspace + (size_t)T * Hq * S * D;
+  dim3 mg(Hq, T);
+  HB_DISPATCH_1(out_dt, "hb_attn_merge",
+                (attn_merge_kernel<TA><<<mg, 64, 0, s>>>(part_acc, part_ml, pos, (TA*)out, Hq, D, window, chunk, S)));
+  HB_CHECK_LAUNCH("hb_attn_merge");
+  return 0;
+}
+
 // ---------------------------------------------------------------------------------------
 // Sampling from 32-bit logits, one block per row. temperature 0: the largest value, the
 // lowest index on ties, NaN above every number, index 0 when all are -inf

@@ -1,0 +1,249 @@
+// The decode-step matrix product on the 5th-generation tensor cores, operands swapped:
+// C^T[N, M] = W[N,K] A[M,K]^T. The 128 weight rows of a CTA are the M side of tcgen05.mma, the
+// few token rows (padded to NT = 16, 32 or 64) its N side, so no tensor-core work is wasted on
+// padding and every weight byte is read from HBM once, by TMA, through a four-deep pipeline;
+// several CTAs share an SM, which keeps close to 200 KB of loads in flight per SM. The
+// accumulator (128 lanes x NT columns of tensor memory) comes back with tcgen05.ld: lane = output
+// column n, so a warp's stores for one token are 128 contiguous bytes.
+//
+// A CTA owns 128 output columns and one slice of K; the number of slices depends on (N, K)
+// only, never on M, so a token's result does not depend on what else is in the batch. Slices
+// leave fp32 partials [slice][token][column]; the CTA that finishes a column block last adds
+// them in slice order and applies the epilogue (store fp32 / store bf16 / add into the fp32
+// residual / SwiGLU over gate and up columns interleaved by 16), then zeroes the counter.
+// It replaces gemv_kernel and gemm_skinny_kernel of the reference (src/kernels.cuh:164, 911).
+// All waits are bounded.
+#include "tc_common.cuh"
+
+enum { ST_F32 = 0, ST_BF16 = 1, ST_ADD_F32 = 2, ST_SWIGLU_BF16 = 3 };
+constexpr int ST_ROWS = 128, ST_BK = 64, ST_W_BYTES = ST_ROWS * ST_BK * 2;
+
+template <int NT> struct StreamCfg {
+  static constexpr int STAGE = ST_W_BYTES + NT * ST_BK * 2;
+  static constexpr int STAGES = NT <= 32 ? 4 : 3;
+  static constexpr int BAR = STAGES * STAGE;
+  static constexpr int TOTAL = BAR + 256 + 1024;
+  static constexpr int TMEM_COLS = NT < 32 ? 32 : NT;
+};
+
+__device__ __forceinline__ void stream_store(int epi, void* C, long ldc, int m, int n, int N, float v, float v_up, bool lower_half) {
+  // lower_half: this column is a gate column (n % 32 < 16); v_up is the matching up column's value
+  if (epi == ST_SWIGLU_BF16) {
+    if (lower_half && n < N) ((__nv_bfloat16*)C)[(size_t)m * ldc + (n >> 5) * 16 + (n & 15)] =
+        __float2bfloat16_rn(v / (1.f + __expf(-v)) * v_up);
+  } else if (n < N) {
+    if (epi == ST_BF16) ((__nv_bfloat16*)C)[(size_t)m * ldc + n] = __float2bfloat16_rn(v);
+    else if (epi == ST_ADD_F32) ((float*)C)[(size_t)m * ldc + n] += v;
+    else ((float*)C)[(size_t)m * ldc + n] = v;
+  }
+}
+
+template <int NT>
+__global__ void __launch_bounds__(192) gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w,
+                                                          const __grid_constant__ CUtensorMap map_x, void* C, long ldc,
+                                                          int M, int N, int K, int kslice, float* ws, int* counters,
+                                                          int epi, int* status) {
+  using S = StreamCfg<NT>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* full = (uint64_t*)(smem + S::BAR);
+  uint64_t* empty = full + S::STAGES;
+  uint64_t* done = empty + S::STAGES;
+  uint32_t* tmem_slot = (uint32_t*)(done + 1);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+  int* is_last = (int*)(tmem_slot + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nb = blockIdx.x, sp = blockIdx.y, ksplit = gridDim.y, NP = gridDim.x * ST_ROWS;
+  const int n0 = nb * ST_ROWS, k_begin = sp * kslice, k_end = min(K, k_begin + kslice);
+  const int num_kb = (k_end - k_begin + ST_BK - 1) / ST_BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S::STAGES; s++) { hb_mbar_init(&full[s], 1); hb_mbar_init(&empty[s], 1); }
+    hb_mbar_init(done, 1);
+    *abort_flag = 0;
+    hb_fence_barrier_init();
+  }
+  if (warp == 5) {
+    hb_tmem_alloc(tmem_slot, S::TMEM_COLS);
+    hb_tmem_relinquish();
+  }
+  if (warp == 4 && lane == 0) { hb_tma_prefetch_desc(&map_w); hb_tma_prefetch_desc(&map_x); }
+  hb_tc_fence_before();
+  __syncthreads();
+  hb_tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      for (int kb = 0; kb < num_kb; kb++) {
+        const uint32_t s = kb % S::STAGES, ph = (kb / S::STAGES) & 1;
+        if (!hb_mbar_wait(&empty[s], ph ^ 1, abort_flag)) break;
+        hb_mbar_expect_tx(&full[s], S::STAGE);
+        hb_tma_load_2d(smem + s * S::STAGE, &map_w, &full[s], k_begin + kb * ST_BK, n0);
+        hb_tma_load_2d(smem + s * S::STAGE + ST_W_BYTES, &map_x, &full[s], k_begin + kb * ST_BK, 0);
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = hb_umma_idesc_bf16(ST_ROWS, NT);
+      bool ok = true;
+      for (int kb = 0; kb < num_kb; kb++) {
+        const uint32_t s = kb % S::STAGES, ph = (kb / S::STAGES) & 1;
+        if (!hb_mbar_wait(&full[s], ph, abort_flag)) { ok = false; break; }
+        hb_tc_fence_after();
+        const uint64_t dw = hb_umma_desc_k128(hb_smem_u32(smem + s * S::STAGE));
+        const uint64_t dx = hb_umma_desc_k128(hb_smem_u32(smem + s * S::STAGE + ST_W_BYTES));
+#pragma unroll
+        for (int k = 0; k < ST_BK / 16; k++) hb_umma_bf16(tmem_base, dw + 2 * k, dx + 2 * k, idesc, (kb | k) != 0);
+        hb_umma_commit(&empty[s]);
+      }
+      if (ok) hb_umma_commit(done);
+    }
+  } else {
+    // epilogue warps: lane = output column n0 + 32 * warp + lane, v[m] = token m
+    const bool ok = hb_mbar_wait(done, 0, abort_flag);
+    hb_tc_fence_after();
+    float v[NT];
+#pragma unroll
+    for (int c = 0; c < NT / 16; c++) hb_tmem_ld16(tmem_base + ((uint32_t)(warp * 32) << 16) + c * 16, v + 16 * c);
+    const int n = n0 + warp * 32 + lane;
+    if (ksplit == 1) {
+#pragma unroll
+      for (int m = 0; m < NT; m++) {
+        if (m < M) {
+          const float up = __shfl_down_sync(0xffffffffu, v[m], 16);
+          if (ok) stream_store(epi, C, ldc, m, n, N, v[m], up, (lane & 16) == 0);
+        }
+      }
+    } else if (ok) {
+#pragma unroll
+      for (int m = 0; m < NT; m++)
+        if (m < M) ws[((size_t)sp * NT + m) * NP + n] = v[m];
+    }
+    hb_tc_fence_before();
+  }
+
+  __threadfence();
+  __syncthreads();
+  if (warp == 5) {
+    __syncwarp();
+    hb_tmem_dealloc(tmem_base, S::TMEM_COLS);
+  }
+  if (*abort_flag) {
+    if (threadIdx.x == 0) atomicExch(status, 1);
+    __nanosleep(100000);
+  }
+  if (ksplit == 1) return;
+
+  if (threadIdx.x == 0) *is_last = atomicAdd(&counters[nb], 1) == ksplit - 1;
+  __syncthreads();
+  if (!*is_last) return;
+  __threadfence();
+  // four consecutive columns per thread, the slices' loads issued four at a time, added in slice order
+  const size_t slice_stride = (size_t)NT * NP;
+  for (int i = threadIdx.x; i < (ST_ROWS / 4) * M; i += 192) {
+    const int m = i / (ST_ROWS / 4), nl = (i - m * (ST_ROWS / 4)) * 4, n = n0 + nl;
+    const bool gate = (nl & 16) == 0, swiglu = epi == ST_SWIGLU_BF16;
+    if (n >= N || (swiglu && !gate)) continue;
+    const float* p = ws + (size_t)m * NP + n;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f), up = acc;
+    int sl = 0;
+    for (; sl + 4 <= ksplit; sl += 4) {
+      float4 a[4], u[4];
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        a[j] = __ldcg((const float4*)(p + (sl + j) * slice_stride));
+        if (swiglu) u[j] = __ldcg((const float4*)(p + (sl + j) * slice_stride + 16));
+      }
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        acc.x += a[j].x; acc.y += a[j].y; acc.z += a[j].z; acc.w += a[j].w;
+        if (swiglu) { up.x += u[j].x; up.y += u[j].y; up.z += u[j].z; up.w += u[j].w; }
+      }
+    }
+    for (; sl < ksplit; sl++) {
+      const float4 a = __ldcg((const float4*)(p + sl * slice_stride));
+      acc.x += a.x; acc.y += a.y; acc.z += a.z; acc.w += a.w;
+      if (swiglu) {
+        const float4 u = __ldcg((const float4*)(p + sl * slice_stride + 16));
+        up.x += u.x; up.y += u.y; up.z += u.z; up.w += u.w;
+      }
+    }
+    stream_store(epi, C, ldc, m, n, N, acc.x, up.x, gate);
+    stream_store(epi, C, ldc, m, n + 1, N, acc.y, up.y, gate);
+    stream_store(epi, C, ldc, m, n + 2, N, acc.z, up.z, gate);
+    stream_store(epi, C, ldc, m, n + 3, N, acc.w, up.w, gate);
+  }
+  if (threadIdx.x == 0) counters[nb] = 0;
+}
+
+// The split of K for an [N, K] weight: a function of the weight's shape alone.
+static void stream_plan(int N, int K, int sms, int* kslice, int* ksplit) {
+  const int n_blocks = (N + ST_ROWS - 1) / ST_ROWS;
+  int want = (3 * sms) / n_blocks;
+  int max_split = K / 256;               // a slice is at least 256 deep, and there are at most 16
+  if (max_split > 16) max_split = 16;
+  if (want > max_split) want = max_split;
+  if (want < 1) want = 1;
+  int ks = (K + want - 1) / want;
+  ks = (ks + ST_BK - 1) / ST_BK * ST_BK;
+  *kslice = ks;
+  *ksplit = (K + ks - 1) / ks;
+}
+
+HB_EXPORT int hb_gemm_stream_plan(int N, int K, int* kslice, int* ksplit, long* ws_floats_per_token, int* n_blocks) {
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  stream_plan(N, K, sms, kslice, ksplit);
+  *n_blocks = (N + ST_ROWS - 1) / ST_ROWS;
+  *ws_floats_per_token = *ksplit > 1 ? (long)(*ksplit) * (*n_blocks) * ST_ROWS : 0;
+  return 0;
+}
+
+template <int NT>
+static int launch_stream(const CUtensorMap& mw, const CUtensorMap& mx, void* C, long ldc, int M, int N, int K, int kslice,
+                         int ksplit, int n_blocks, float* ws, int* counters, int epi, int* status, cudaStream_t s) {
+  using S = StreamCfg<NT>;
+  auto kern = gemm_stream_kernel<NT>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+    if (e != cudaSuccess) HB_FAIL("hb_gemm_stream: %s", cudaGetErrorString(e));
+    configured = true;
+  }
+  kern<<<dim3(n_blocks, ksplit), 192, S::TOTAL, s>>>(mw, mx, C, ldc, M, N, K, kslice, ws, counters, epi, status);
+  return 0;
+}
+
+// C per `epi` (0 fp32, 1 bf16, 2 fp32 +=, 3 bf16 SwiGLU [M, N/2]) for M <= 64. ws: at least
+// ksplit * n_blocks * 128 * NT floats when ksplit > 1 (NT = M rounded up to 16, 32 or 64);
+// counters: n_blocks ints, all zero (left zero). Calls sharing ws/counters must not overlap.
+HB_EXPORT int hb_gemm_stream(const void* A, long lda, const void* W, long ldw, void* C, long ldc, int M, int N, int K,
+                             int epi, float* ws, long ws_floats, int* counters, int n_counters, int* status,
+                             cudaStream_t s) {
+  if (M <= 0 || N <= 0) return 0;
+  if (M > 64) HB_FAIL("hb_gemm_stream: M = %d is beyond 64 rows", M);
+  if (K <= 0 || (K & 7)) HB_FAIL("hb_gemm_stream: K = %d must be a positive multiple of 8 (16-byte rows for TMA)", K);
+  if (epi < 0 || epi > 3) HB_FAIL("hb_gemm_stream: unknown epilogue %d", epi);
+  if (epi == ST_SWIGLU_BF16 && (N & 31)) HB_FAIL("hb_gemm_stream: SwiGLU needs N = %d to be a multiple of 32", N);
+  if (!status) HB_FAIL("hb_gemm_stream: no status word");
+  int kslice, ksplit, n_blocks;
+  long per_token;
+  hb_gemm_stream_plan(N, K, &kslice, &ksplit, &per_token, &n_blocks);
+  const int NT = M <= 16 ? 16 : M <= 32 ? 32 : 64;
+  if (ksplit > 1 && (!ws || ws_floats < per_token * NT))
+    HB_FAIL("hb_gemm_stream: workspace of %ld floats, %ld needed", ws_floats, per_token * NT);
+  if (ksplit > 1 && (!counters || n_counters < n_blocks)) HB_FAIL("hb_gemm_stream: %d counters, %d needed", n_counters, n_blocks);
+  CUtensorMap mw, mx;
+  if (hb_make_tensor_map_bf16(&mw, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, ST_ROWS)) return -1;
+  if (hb_make_tensor_map_bf16(&mx, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, (uint32_t)NT)) return -1;
+  int r;
+  if (NT == 16) r = launch_stream<16>(mw, mx, C, ldc, M, N, K, kslice, ksplit, n_blocks, ws, counters, epi, status, s);
+  else if (NT == 32) r = launch_stream<32>(mw, mx, C, ldc, M, N, K, kslice, ksplit, n_blocks, ws, counters, epi, status, s);
+  else r = launch_stream<64>(mw, mx, C, ldc, M, N, K, kslice, ksplit, n_blocks, ws, counters, epi, status, s);
+  if (r) return r;
+  HB_CHECK_LAUNCH("hb_gemm_stream");
+  return 0;
+}

@@ -51,9 +51,13 @@ class StepBatch:
 
 def build_step_batch(entries: Sequence[StepEntry], ctx_lens: Sequence[int], state_slots: Sequence[int],
                      tables: Sequence[Sequence[Sequence[int]]], slot_maps: Sequence[Sequence[Sequence[int]]],
-                     n_groups: int, device) -> StepBatch:
+                     n_groups: int, device, table_widths: Optional[Sequence[int]] = None,
+                     static: Optional[torch.Tensor] = None, max_pos: Optional[int] = None) -> StepBatch:
     """entries[r] runs at positions ctx_lens[r].. ; tables[r][g] is the request's block table of
-    group g AFTER room was made for this step; slot_maps[r][g][i] the cache slot of its i-th token."""
+    group g AFTER room was made for this step; slot_maps[r][g][i] the cache slot of its i-th token.
+    `table_widths` fixes the block tables' widths and `static` is a device buffer to fill instead
+    of a fresh one (both for steps replayed from a CUDA graph, whose addresses and launch
+    geometry must not change); `max_pos` then states the bound the geometry was made for."""
     R = len(entries)
     q_len = [len(e.tokens) for e in entries]
     T = sum(q_len)
@@ -63,6 +67,9 @@ def build_step_batch(entries: Sequence[StepEntry], ctx_lens: Sequence[int], stat
     want_rows = [q_start[r] + int(w) for r, e in enumerate(entries) for w in e.want]
     W = len(want_rows)
     widths = [max(1, max((len(tables[r][g]) for r in range(R)), default=1)) for g in range(n_groups)]
+    if table_widths is not None:
+        assert all(w <= tw for w, tw in zip(widths, table_widths)), "a block table is wider than the graph was made for"
+        widths = list(table_widths)
     n_int = 3 * T + 4 * R + W + sum(R * w for w in widths) + n_groups * T
     host = torch.empty(max(n_int, 1), dtype=torch.int32, pin_memory=torch.device(device).type == "cuda")
     buf = host.numpy()
@@ -83,13 +90,20 @@ def build_step_batch(entries: Sequence[StepEntry], ctx_lens: Sequence[int], stat
     o_w = put(want_rows, W)
     o_bt = []
     for g in range(n_groups):
-        flat = []
+        o, w = off, widths[g]
+        buf[o:o + R * w] = -1
         for r in range(R):
-            row = list(tables[r][g])
-            flat.extend(row + [-1] * (widths[g] - len(row)))
-        o_bt.append(put(flat, R * widths[g]))
+            row = tables[r][g]
+            buf[o + r * w:o + r * w + len(row)] = row
+        off += R * w
+        o_bt.append(o)
     o_sm = [put([s for r in range(R) for s in slot_maps[r][g]], T) for g in range(n_groups)]
-    dev = host.to(device, non_blocking=True)
+    if static is not None:
+        assert static.numel() >= n_int
+        static[:n_int].copy_(host[:n_int], non_blocking=True)
+        dev = static
+    else:
+        dev = host.to(device, non_blocking=True)
 
     def view(o, n):
         return dev[o:o + n]
@@ -101,4 +115,4 @@ def build_step_batch(entries: Sequence[StepEntry], ctx_lens: Sequence[int], stat
         block_tables=[view(o_bt[g], R * widths[g]).view(R, widths[g]) for g in range(n_groups)],
         slot_maps=[view(o_sm[g], T) for g in range(n_groups)],
         h_q_start=q_start, h_q_len=q_len, h_ctx_len=list(ctx_lens), h_state_slot=list(state_slots),
-        max_pos=max(pos) if pos else 0, max_q_len=max(q_len) if q_len else 0)
+        max_pos=(max(pos) if pos else 0) if max_pos is None else max_pos, max_q_len=max(q_len) if q_len else 0)

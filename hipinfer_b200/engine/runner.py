@@ -11,6 +11,7 @@ from __future__ import annotations
 
 from typing import Dict, List, Optional, Sequence
 
+import numpy as np
 import torch
 
 from ..cache import CacheManager, CacheStorage, OutOfPages
@@ -32,7 +33,7 @@ class StepError(ValueError):
 class ModelRunner:
     def __init__(self, config: ModelConfig, tensors: Dict[str, torch.Tensor], dtype="bfloat16", device="cuda:0",
                  page_size: int = 16, num_pages: Optional[int] = None, max_model_len: Optional[int] = None,
-                 max_num_seqs: int = 8):
+                 max_num_seqs: int = 8, cuda_graphs: bool = True):
         if not torch.cuda.is_available():
             raise RuntimeError("hipinfer_b200 runs on a CUDA device (sm_100a); none is visible and there is no "
                                "CPU implementation")
@@ -54,6 +55,12 @@ class ModelRunner:
                                     self.model.state_specs, max_num_seqs)
         self.vocab_size = self.spec.vocab_size
         self.steps_run = 0
+        # decode-only steps (one token per request, every row wanted) are replayed from a CUDA
+        # graph captured per number of requests: same kernels, one launch
+        self.cuda_graphs = bool(cuda_graphs)
+        self._graphs: Dict[int, dict] = {}
+        self._table_widths = [pages_per_seq] * len(groups)
+        self._np_tables: Dict[object, list] = {}
 
     # ---------------------------------------------------------------- construction helpers
     @classmethod
@@ -100,9 +107,13 @@ class ModelRunner:
                 if not (0 <= int(w) < n):
                     raise StepError(f"request {e.request_id!r}: want {w} is outside its {n} tokens")
 
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Run one batch; float32 logits [number of wanted places, vocab] on the device.
-        Raises OutOfPages (nothing changed) when the cache cannot hold the new tokens."""
+        Raises OutOfPages (nothing changed) when the cache cannot hold the new tokens.
+        `device_tokens` (int32 [rows], on the device) replaces the entries' token values, which
+        are then placeholders: tokens sampled on the device feed the next step without a trip to
+        the host (the reference keeps token and position on the device for the same reason,
+        README.md:510-512)."""
         entries = list(entries)
         self.check_entries(entries)
         if not entries:
@@ -125,21 +136,77 @@ class ModelRunner:
             if not self.cache.has_request(e.request_id):
                 rc = self.cache.add_request(e.request_id)
                 self.storage.zero_state_slot(rc.state_slot)
+                self._np_tables.pop(e.request_id, None)    # an id that comes back (after preemption) starts afresh
             rc = self.cache.get(e.request_id)
             ctx_lens.append(rc.length)
             slots.append(rc.state_slot)
             slot_maps.append(self.cache.append(e.request_id, len(e.tokens)))
-            tables.append([list(t) for t in rc.tables])
-        batch = build_step_batch(entries, ctx_lens, slots, tables, slot_maps, len(self.cache.groups), self.device)
-        logits = self.model.forward(batch, self.storage)
+            tables.append(self._table_rows(rc))
+        if self.cuda_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
+            logits = self._graph_step(entries, ctx_lens, slots, tables, slot_maps, device_tokens)
+        else:
+            batch = build_step_batch(entries, ctx_lens, slots, tables, slot_maps, len(self.cache.groups), self.device)
+            if device_tokens is not None:
+                batch.tokens.copy_(device_tokens, non_blocking=True)
+            logits = self.model.forward(batch, self.storage)
         for e in entries:
-            self.cache.release_behind_window(e.request_id)
+            if self.cache.release_behind_window(e.request_id):
+                self._np_tables.pop(e.request_id, None)
         self.steps_run += 1
         return logits
+
+    def _table_rows(self, rc):
+        """The request's block tables as int32 arrays, kept between steps and extended by the new pages only."""
+        rows = self._np_tables.setdefault(rc.request_id, [[np.full(16, -1, dtype=np.int32), 0] for _ in rc.tables])
+        out = []
+        for slot, table in zip(rows, rc.tables):
+            arr, n = slot
+            if len(table) > arr.shape[0]:
+                grown = np.full(2 * len(table), -1, dtype=np.int32)
+                grown[:n] = arr[:n]
+                slot[0] = arr = grown
+            if len(table) > n:
+                arr[n:len(table)] = table[n:]
+                slot[1] = len(table)
+            out.append(arr[:len(table)])
+        return out
+
+    def _graph_step(self, entries, ctx_lens, slots, tables, slot_maps, device_tokens=None) -> torch.Tensor:
+        """A decode-only step through the CUDA graph for this many requests (captured at first use).
+        The graph's batch lives in one static device buffer that each step overwrites; launch
+        geometry is made for the longest sequence, so blocks beyond a row's keys return at once.
+        The logits tensor is the graph's own and is overwritten by the next such step."""
+        R, G = len(entries), len(self.cache.groups)
+        g = self._graphs.get(R)
+        args = dict(n_groups=G, device=self.device, table_widths=self._table_widths, max_pos=self.max_model_len - 1)
+        if g is None:
+            n_int = 3 * R + 4 * R + R + sum(R * w for w in self._table_widths) + G * R
+            static = torch.zeros(n_int, dtype=torch.int32, device=self.device)
+            batch = build_step_batch(entries, ctx_lens, slots, tables, slot_maps, static=static, **args)
+            if device_tokens is not None:
+                batch.tokens.copy_(device_tokens, non_blocking=True)
+            self.model.forward(batch, self.storage)            # warm-up: allocations, plans, lazy set-up
+            torch.cuda.synchronize()
+            from ..kernels import library
+            before = library.launches[0]
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                logits = self.model.forward(batch, self.storage)
+            g = self._graphs[R] = dict(graph=graph, static=static, logits=logits, tokens=batch.tokens,
+                                       launches=library.launches[0] - before)
+        else:
+            build_step_batch(entries, ctx_lens, slots, tables, slot_maps, static=g["static"], **args)
+            if device_tokens is not None:
+                g["tokens"].copy_(device_tokens, non_blocking=True)
+        g["graph"].replay()
+        from ..kernels import library
+        library.launches[0] += g["launches"]
+        return g["logits"]
 
     def end(self, request_id) -> None:
         """The request is finished: its pages and its state slot are given back."""
         self.cache.free_request(request_id)
+        self._np_tables.pop(request_id, None)
 
     def live_requests(self):
         return list(self.cache.requests)

@@ -19,8 +19,15 @@ PLAIN_ONLY = os.environ.get("HIPINFER_B200_PLAIN", "0") == "1"
 _p, _i, _l, _f = C.c_void_p, C.c_int, C.c_long, C.c_float
 _SIGS = {
     "hb_gemm_tc": [_p, _l, _p, _l, _p, _l, _i, _i, _i, _i, _i, _p, _p],
+    "hb_gemm_skinny": [_p, _l, _p, _l, _p, _l, _i, _i, _i, _i, _p, _l, _p, _i, _p],
+    "hb_gemm_skinny_plan": [_i, _i, _p, _p, _p, _p],
+    "hb_gemm_stream": [_p, _l, _p, _l, _p, _l, _i, _i, _i, _i, _p, _l, _p, _i, _p, _p],
+    "hb_gemm_stream_plan": [_i, _i, _p, _p, _p, _p],
+    "hb_attn_decode": [_p, _p, _p, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _i, _p],
+    "hb_attn_decode_supported": [_i, _i, _i],
 }
 _fns = {}
+_LAUNCHES = {"hb_gemm_tc": 1, "hb_gemm_skinny": 1, "hb_gemm_stream": 1, "hb_attn_decode": 1}
 _status = None
 
 EPI_F32, EPI_BF16, EPI_ADD_F32, EPI_SWIGLU_BF16 = 0, 1, 2, 3
@@ -42,6 +49,8 @@ def _fn(name):
 
 
 def _call(name, *args):
+    if name in _LAUNCHES:
+        library.launches[0] += _LAUNCHES[name]
     if _fn(name)(*args) != 0:
         from .ops import KernelError
 
@@ -81,6 +90,78 @@ def gemm_tc(a, w, out, epi, tile_n=0):
     return out
 
 
+SKINNY_MAX_ROWS = 64      # rows up to which the weight-streaming kernel is used instead of the tcgen05 kernel
+_scratch = {}
+_retired = []
+_plans = {}
+
+
+def skinny_plan(N, K):
+    """(kslice, ksplit, workspace floats per padded token row, column blocks) for an [N, K] weight."""
+    key = (N, K)
+    if key not in _plans:
+        ks, sp, nb, per = C.c_int(), C.c_int(), C.c_int(), C.c_long()
+        _call("hb_gemm_skinny_plan", N, K, C.byref(ks), C.byref(sp), C.byref(per), C.byref(nb))
+        _plans[key] = (ks.value, sp.value, per.value, nb.value)
+    return _plans[key]
+
+
+def _skinny_scratch(device, ws_floats, n_counters):
+    """Workspace and zeroed counters shared by all small-batch products of this device and stream
+    order; they grow on demand (kernels that share them run one after the other)."""
+    sc = _scratch.get(device)
+    if sc is None or sc[0].numel() < ws_floats or sc[1].numel() < n_counters:
+        ws = torch.empty(max(ws_floats, 16 << 20), dtype=torch.float32, device=device)
+        cnt = torch.zeros(max(n_counters, 8192), dtype=torch.int32, device=device)
+        if sc is not None:
+            _retired.append(sc)      # a captured CUDA graph may still hold the old addresses
+        sc = _scratch[device] = (ws, cnt)
+    return sc
+
+
+def gemm_skinny(a, w, out, epi):
+    """The weight-streaming kernel itself (M <= 64): out per `epi` (see csrc/gemm_skinny.cu)."""
+    M, K = a.shape
+    N = w.shape[0]
+    _, _, per_row, n_blocks = skinny_plan(N, K)
+    mp = 8 if M <= 8 else 16 if M <= 16 else 32 if M <= 32 else 64
+    ws, cnt = _skinny_scratch(a.device, per_row * mp, n_blocks)
+    _call("hb_gemm_skinny", a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0), M, N, K,
+          epi, ws.data_ptr(), ws.numel(), cnt.data_ptr(), cnt.numel(), _stream())
+    return out
+
+
+def stream_plan(N, K):
+    """(kslice, ksplit, workspace floats per padded token, column blocks) of the swapped tcgen05 kernel."""
+    key = ("stream", N, K)
+    if key not in _plans:
+        ks, sp, nb, per = C.c_int(), C.c_int(), C.c_int(), C.c_long()
+        _call("hb_gemm_stream_plan", N, K, C.byref(ks), C.byref(sp), C.byref(per), C.byref(nb))
+        _plans[key] = (ks.value, sp.value, per.value, nb.value)
+    return _plans[key]
+
+
+def gemm_stream(a, w, out, epi):
+    """The swapped-operand tcgen05 weight-streaming kernel (M <= 64): see csrc/gemm_stream.cu."""
+    M, K = a.shape
+    N = w.shape[0]
+    _, _, per_token, n_blocks = stream_plan(N, K)
+    nt = 16 if M <= 16 else 32 if M <= 32 else 64
+    ws, cnt = _skinny_scratch(a.device, per_token * nt, n_blocks)
+    _call("hb_gemm_stream", a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0), M, N, K,
+          epi, ws.data_ptr(), ws.numel(), cnt.data_ptr(), cnt.numel(), status_word().data_ptr(), _stream())
+    return out
+
+
+SMALL_IMPL = os.environ.get("HIPINFER_B200_SMALL_GEMM", "stream")   # "stream" (tcgen05) or "skinny" (mma.sync)
+
+
+def _gemm(a, w, out, epi):
+    if a.shape[0] <= SKINNY_MAX_ROWS:
+        return gemm_stream(a, w, out, epi) if SMALL_IMPL == "stream" else gemm_skinny(a, w, out, epi)
+    return gemm_tc(a, w, out, epi)
+
+
 def linear(a, w, out, accumulate) -> bool:
     if not _tc_ok(a, w.t):
         return False
@@ -90,16 +171,42 @@ def linear(a, w, out, accumulate) -> bool:
         epi = EPI_BF16
     else:
         return False
-    gemm_tc(a, w.t, out, epi)
+    _gemm(a, w.t, out, epi)
     return True
 
 
 def linear_swiglu(a, w, act_out, group) -> bool:
     if group != 16 or act_out.dtype != torch.bfloat16 or not _tc_ok(a, w.t) or w.shape[0] % 32:
         return False
-    gemm_tc(a, w.t, act_out, EPI_SWIGLU_BF16)
+    _gemm(a, w.t, act_out, EPI_SWIGLU_BF16)
     return True
 
 
+DECODE_CHUNK = 256      # keys per split of the decode attention kernel (absolute positions)
+
+
+def attention_decode(q, k_cache, v_cache, block_table, row_request, positions, out, n_heads, n_kv_heads, head_dim,
+                     page_size, window, scale, max_pos, chunk=DECODE_CHUNK):
+    """The bf16 row-attention kernel itself (see csrc/attention_fast.cu), with the core library's merge."""
+    from . import ops
+
+    T = q.shape[0]
+    ws = ops.attention_workspace(T, n_heads, head_dim, max_pos, chunk, q.device)
+    _call("hb_attn_decode", q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_table.data_ptr(),
+          block_table.stride(0), row_request.data_ptr(), positions.data_ptr(), out.data_ptr(),
+          None if ws is None else ws.data_ptr(), T, n_heads, n_kv_heads, head_dim, page_size, int(window), float(scale),
+          chunk, int(max_pos), _stream())
+    return ops.attention_merge(ws, positions, out, n_heads, head_dim, window, max_pos, chunk)
+
+
+def attention_decode_supported(n_heads, n_kv_heads, head_dim) -> bool:
+    f = _fn("hb_attn_decode_supported")
+    return bool(f(n_heads, n_kv_heads, head_dim))
+
+
 def attention(q, k_cache, v_cache, batch, group, out, n_heads, n_kv_heads, head_dim, page_size, window, scale) -> bool:
-    return False
+    if PLAIN_ONLY or q.dtype != torch.bfloat16 or not attention_decode_supported(n_heads, n_kv_heads, head_dim):
+        return False
+    attention_decode(q, k_cache, v_cache, batch.block_tables[group], batch.row_request, batch.positions, out, n_heads,
+                     n_kv_heads, head_dim, page_size, window, scale, batch.max_pos)
+    return True

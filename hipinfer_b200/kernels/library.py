@@ -25,12 +25,12 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(os.path.dirname(_HERE), "csrc")
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-              "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "-shared"]
+              "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "-shared", "--threads", "4"]
 
 # library name -> sources (relative to csrc/); headers every library depends on
 LIBRARIES: Dict[str, List[str]] = {
     "core": ["core.cu"],
-    "fast": ["fast_entry.cu", "gemm_tc.cu"],
+    "fast": ["fast_entry.cu", "gemm_tc.cu", "gemm_skinny.cu", "gemm_stream.cu", "attention_fast.cu"],
 }
 HEADERS = ["common.cuh", "tc_common.cuh"]
 
@@ -40,6 +40,7 @@ class KernelLibraryError(RuntimeError):
 
 
 _loaded: Dict[str, ctypes.CDLL] = {}
+launches = [0]   # kernels launched through this package's libraries since import (a graph replay adds its own count)
 _lock = threading.Lock()
 
 

@@ -28,6 +28,7 @@ _SIGS = {
         "hb_rope_table": [_p, _p, _i, _i, _p],
         "hb_rope_kv": [_p, _i, _l, _p, _p, _p, _p, _i, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p],
         "hb_attn_rows": [_p, _i, _p, _p, _i, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _i, _p],
+        "hb_attn_merge": [_p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p],
         "hb_sample": [_p, _l, _i, _i, _p, _p, _p, _p, _p],
         "hb_convert": [_p, _i, _p, _i, _l, _p],
     },
@@ -51,7 +52,11 @@ def _fn(lib_name: str, name: str):
     return f
 
 
+_NO_LAUNCH = {"hb_attn_rows_workspace"}
+
+
 def _call(lib_name: str, name: str, *args):
+    library.launches[0] += 1
     r = _fn(lib_name, name)(*args)
     if r != 0:
         raise KernelError(library.load(lib_name).hb_last_error().decode())
@@ -190,6 +195,23 @@ def attention_rows(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor
           block_table.data_ptr(), block_table.stride(0), row_request.data_ptr(), positions.data_ptr(),
           out.data_ptr(), _ptr(ws), T, n_heads, n_kv_heads, head_dim, page_size, int(window), float(scale), chunk,
           int(max_pos), _stream())
+    return out
+
+
+def attention_workspace(T: int, n_heads: int, head_dim: int, max_pos: int, chunk: int, device):
+    """The partials buffer for rows whose keys span several chunks (None when none does)."""
+    lib = library.load("core")
+    lib.hb_attn_rows_workspace.restype = C.c_long
+    lib.hb_attn_rows_workspace.argtypes = [_i, _i, _i, _i, _i]
+    n_ws = lib.hb_attn_rows_workspace(T, n_heads, head_dim, int(max_pos), chunk)
+    return torch.empty(n_ws, dtype=torch.float32, device=device) if n_ws else None
+
+
+def attention_merge(ws, positions, out, n_heads, head_dim, window, max_pos, chunk):
+    if ws is None:
+        return out
+    _call("core", "hb_attn_merge", ws.data_ptr(), positions.data_ptr(), out.data_ptr(), _dt(out), out.shape[0], n_heads,
+          head_dim, int(window), chunk, int(max_pos), _stream())
     return out
 
 

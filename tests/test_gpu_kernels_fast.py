@@ -87,3 +87,117 @@ def test_gemm_tc_strided_views():
     ref = a.float() @ w.float().T
     assert float((out - ref).abs().max()) < 1e-3
     assert bool((out_big[:, :32] == 0).all()) and bool((out_big[:, 128:] == 0).all())
+
+
+# ------------------------------------------------------------------------------------------
+# the weight-streaming kernel for small batches
+# ------------------------------------------------------------------------------------------
+IMPLS = ["skinny", "stream"]
+
+
+def small(impl):
+    return getattr(fast(), "gemm_" + impl)
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16, 31, 64])
+@pytest.mark.parametrize("N,K", [(128, 128), (96, 72), (300, 200), (1000, 320), (704, 2048), (256, 4104)])
+def test_gemm_small(M, N, K, impl):
+    a, w = rnd(M, K, seed=11), rnd(N, K, seed=12, scale=0.1)
+    ref = a.float().double() @ w.float().double().T
+    tol = 2e-5 * max(1.0, float(ref.abs().max())) * (K ** 0.5)
+    for _ in range(2):                    # twice: the counters must have been left at zero
+        out = torch.full((M + 1, N), 7.0, dtype=torch.float32, device=DEV)
+        small(impl)(a, w, out[:M], fast().EPI_F32)
+        sync_check()
+        assert float((out[:M].double() - ref).abs().max()) < tol
+        assert bool((out[M] == 7.0).all()), "wrote past the last row"
+    acc = rnd(M, N, seed=13, dtype=torch.float32)
+    want = acc.double() + ref
+    small(impl)(a, w, acc, fast().EPI_ADD_F32)
+    assert float((acc.double() - want).abs().max()) < tol
+    ob = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    small(impl)(a, w, ob, fast().EPI_BF16)
+    assert float((ob.double() - ref).abs().max()) < 1e-2 * max(1.0, float(ref.abs().max()))
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+@pytest.mark.parametrize("M,I,K", [(1, 16, 64), (5, 176, 96), (17, 320, 136), (64, 1024, 2048)])
+def test_gemm_small_swiglu(M, I, K, impl):
+    a = rnd(M, K, seed=14)
+    g, u = rnd(I, K, seed=15, scale=0.2), rnd(I, K, seed=16, scale=0.2)
+    gu = torch.stack([g.reshape(I // 16, 16, K), u.reshape(I // 16, 16, K)], 1).reshape(2 * I, K).contiguous()
+    gg, uu = a.float() @ g.float().T, a.float() @ u.float().T
+    ref = gg / (1 + torch.exp(-gg)) * uu
+    out = torch.full((M + 1, I), 7.0, dtype=torch.bfloat16, device=DEV)
+    small(impl)(a, gu, out[:M], fast().EPI_SWIGLU_BF16)
+    assert float((out[:M].float() - ref).abs().max()) < 1e-2 * max(1.0, float(ref.abs().max()))
+    assert bool((out[M] == 7.0).all())
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+def test_gemm_small_row_does_not_depend_on_batch(impl):
+    """A token's result is bit-identical alone, among 8 and among 64 (the K split depends on the weight only)."""
+    a, w = rnd(64, 2048, seed=17), rnd(384, 2048, seed=18, scale=0.1)
+    full = torch.empty(64, 384, dtype=torch.float32, device=DEV)
+    small(impl)(a, w, full, fast().EPI_F32)
+    for rows in ([0], [5, 63], list(range(3, 12)), list(range(20, 50))):
+        sub = torch.empty(len(rows), 384, dtype=torch.float32, device=DEV)
+        small(impl)(a[rows].contiguous(), w, sub, fast().EPI_F32)
+        assert torch.equal(sub, full[rows])
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+def test_small_and_tile_kernels_agree_to_rounding(impl):
+    a, w = rnd(64, 1024, seed=19), rnd(512, 1024, seed=20, scale=0.1)
+    x, y = torch.empty(64, 512, device=DEV), torch.empty(64, 512, device=DEV)
+    small(impl)(a, w, x, fast().EPI_F32)
+    fast().gemm_tc(a, w, y, fast().EPI_F32)
+    sync_check()
+    assert float((x - y).abs().max()) < 1e-4 * float(y.abs().max())
+
+
+# ------------------------------------------------------------------------------------------
+# attention over the paged bf16 cache
+# ------------------------------------------------------------------------------------------
+import math
+
+import plain_llama as plain
+from test_gpu_kernels_plain import _paged_setup
+
+
+@pytest.mark.parametrize("Hq,Hkv,D,ps,window", [(8, 2, 64, 16, 0), (3, 1, 32, 8, 0), (10, 2, 128, 16, 0), (8, 8, 64, 32, 0),
+                                                (8, 1, 64, 16, 0), (6, 2, 32, 16, 40), (4, 2, 64, 16, 300)])
+def test_attention_decode(Hq, Hkv, D, ps, window):
+    lens = [700, 37, 1, 300]
+    kc, vc, bt, ks, vs = _paged_setup(lens, Hkv, D, ps, torch.bfloat16, 21)
+    rows = [(0, 699), (1, 30), (1, 31), (1, 36), (2, 0), (3, 255), (3, 256), (3, 299), (0, 511), (0, 512)]
+    T = len(rows)
+    q = rnd(T, Hq * D, seed=22)
+    qf = q.float().cpu().reshape(T, Hq, D)
+    out = torch.empty(T, Hq * D, dtype=torch.bfloat16, device=DEV)
+    rr = torch.tensor([r for r, _ in rows], dtype=torch.int32, device=DEV)
+    pos = torch.tensor([p for _, p in rows], dtype=torch.int32, device=DEV)
+    fast().attention_decode(q, kc, vc, bt, rr, pos, out, Hq, Hkv, D, ps, window, 1.0 / math.sqrt(D), max(p for _, p in rows))
+    got = out.float().cpu().reshape(T, Hq, D)
+    for t, (r, p) in enumerate(rows):
+        ref = plain.attention_scores_softmax_values(qf[t:t + 1], ks[r][:p + 1], vs[r][:p + 1], [p], list(range(p + 1)),
+                                                    window or None)
+        torch.testing.assert_close(got[t:t + 1], ref, rtol=1e-2, atol=1e-2, msg=lambda m: f"row {t} {rows[t]}: {m}")
+
+
+def test_attention_decode_far_key_stands_out():
+    Hq, Hkv, D, ps = 4, 1, 64, 16
+    kc, vc, bt, ks, vs = _paged_setup([900], Hkv, D, ps, torch.bfloat16, 23)
+    q = rnd(1, Hq * D, seed=24)
+    qf = q.float().cpu().reshape(1, Hq, D)
+    far = 5
+    page, off = int(bt[0, far // ps]), far % ps
+    kc[page, 0, off] = (qf[0, 0] * 4.0).to(torch.bfloat16).to(DEV)
+    ks[0][far, 0] = kc[page, 0, off].float().cpu()
+    out = torch.empty(1, Hq * D, dtype=torch.bfloat16, device=DEV)
+    fast().attention_decode(q, kc, vc, bt, torch.zeros(1, dtype=torch.int32, device=DEV),
+                            torch.tensor([899], dtype=torch.int32, device=DEV), out, Hq, Hkv, D, ps, 0, 1 / math.sqrt(D), 899)
+    ref = plain.attention_scores_softmax_values(qf, ks[0], vs[0], [899], list(range(900)))
+    torch.testing.assert_close(out.float().cpu().reshape(1, Hq, D), ref, rtol=1e-2, atol=1e-2)
+    assert float((out.float().cpu().reshape(Hq, D)[0] - vs[0][far, 0]).abs().max()) < 0.05
