@@ -16,7 +16,7 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc,
     const int* __restrict__ bt, int bt_stride, const int* __restrict__ row_req, const int* __restrict__ pos,
     __nv_bfloat16* __restrict__ out, float* __restrict__ part_acc, float* __restrict__ part_ml, int Hq, int Hkv,
-    int page_size, int window, float scale, int chunk, int S) {
+    int page_size, int window, float scale, int chunk, int S, const int* __restrict__ q_len, int row_limit) {
   constexpr int EPL = D / 32;  // value elements per lane
   extern __shared__ float smem[];
   float* qs = smem;                 // [G][D], scaled
@@ -24,6 +24,7 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
   float* ml = sc + G * chunk;       // [G][2]
   float* red = ml + 2 * G;          // [4 warps][G][D]
   const int t = blockIdx.z, h = blockIdx.y, s = blockIdx.x;
+  if (q_len && q_len[row_req[t]] >= row_limit) return;  // a long portion: the flash kernel's
   const int p = pos[t];
   const int lo = window > 0 ? max(0, p - window + 1) : 0;
   const int s_lo = lo / chunk, s_hi = p / chunk;
@@ -134,11 +135,11 @@ template <int D>
 static int launch_decode(int G, dim3 grid, size_t smem, cudaStream_t st, const __nv_bfloat16* q, const __nv_bfloat16* kc,
                          const __nv_bfloat16* vc, const int* bt, int bt_stride, const int* row_req, const int* pos,
                          __nv_bfloat16* out, float* pa, float* pm, int Hq, int Hkv, int page_size, int window, float scale,
-                         int chunk, int S) {
+                         int chunk, int S, const int* q_len, int row_limit) {
 #define HB_AD_CASE(GG)                                                                                              \
   case GG:                                                                                                          \
     attn_decode_kernel<D, GG><<<grid, AD_THREADS, smem, st>>>(q, kc, vc, bt, bt_stride, row_req, pos, out, pa, pm, Hq, \
-                                                              Hkv, page_size, window, scale, chunk, S);             \
+                                                              Hkv, page_size, window, scale, chunk, S, q_len, row_limit); \
     return 0;
   switch (G) {
     HB_AD_CASE(1) HB_AD_CASE(2) HB_AD_CASE(3) HB_AD_CASE(4) HB_AD_CASE(5) HB_AD_CASE(6) HB_AD_CASE(7) HB_AD_CASE(8)
@@ -154,10 +155,12 @@ HB_EXPORT int hb_attn_decode_supported(int Hq, int Hkv, int D) {
 
 // Partials layout as hb_attn_rows of the core library: workspace = part_acc [T, Hq, S, D] then
 // part_ml [T, Hq, S, 2], S = max_pos / chunk + 1; rows spanning several chunks are finished by
-// hb_attn_merge (core library) with the same chunk.
+// hb_attn_merge (core library) with the same chunk. With q_len given, rows of requests whose
+// portion has row_limit rows or more are skipped (the flash kernel computes those).
 HB_EXPORT int hb_attn_decode(const void* q, const void* kc, const void* vc, const int* bt, int bt_stride,
                              const int* row_req, const int* pos, void* out, float* workspace, int T, int Hq, int Hkv,
-                             int D, int page_size, int window, float scale, int chunk, int max_pos, cudaStream_t st) {
+                             int D, int page_size, int window, float scale, int chunk, int max_pos, const int* q_len,
+                             int row_limit, cudaStream_t st) {
   if (T <= 0) return 0;
   if (!hb_attn_decode_supported(Hq, Hkv, D)) HB_FAIL("hb_attn_decode: %d/%d heads of %d are not supported", Hq, Hkv, D);
   if (chunk <= 0 || chunk % 32) HB_FAIL("hb_attn_decode: chunk %d must be a positive multiple of 32", chunk);
@@ -171,9 +174,9 @@ HB_EXPORT int hb_attn_decode(const void* q, const void* kc, const void* vc, cons
   dim3 grid(S, Hkv, T);
   const __nv_bfloat16 *qq = (const __nv_bfloat16*)q, *kk = (const __nv_bfloat16*)kc, *vv = (const __nv_bfloat16*)vc;
   int r = 1;
-  if (D == 32) r = launch_decode<32>(G, grid, smem, st, qq, kk, vv, bt, bt_stride, row_req, pos, (__nv_bfloat16*)out, pa, pm, Hq, Hkv, page_size, window, scale, chunk, S);
-  else if (D == 64) r = launch_decode<64>(G, grid, smem, st, qq, kk, vv, bt, bt_stride, row_req, pos, (__nv_bfloat16*)out, pa, pm, Hq, Hkv, page_size, window, scale, chunk, S);
-  else if (D == 128) r = launch_decode<128>(G, grid, smem, st, qq, kk, vv, bt, bt_stride, row_req, pos, (__nv_bfloat16*)out, pa, pm, Hq, Hkv, page_size, window, scale, chunk, S);
+  if (D == 32) r = launch_decode<32>(G, grid, smem, st, qq, kk, vv, bt, bt_stride, row_req, pos, (__nv_bfloat16*)out, pa, pm, Hq, Hkv, page_size, window, scale, chunk, S, q_len, row_limit);
+  else if (D == 64) r = launch_decode<64>(G, grid, smem, st, qq, kk, vv, bt, bt_stride, row_req, pos, (__nv_bfloat16*)out, pa, pm, Hq, Hkv, page_size, window, scale, chunk, S, q_len, row_limit);
+  else if (D == 128) r = launch_decode<128>(G, grid, smem, st, qq, kk, vv, bt, bt_stride, row_req, pos, (__nv_bfloat16*)out, pa, pm, Hq, Hkv, page_size, window, scale, chunk, S, q_len, row_limit);
   if (r) HB_FAIL("hb_attn_decode: no kernel for group %d", G);
   HB_CHECK_LAUNCH("hb_attn_decode");
   return 0;

@@ -325,8 +325,9 @@ __global__ void __launch_bounds__(128) attn_rows_kernel(
 template <typename TQ>
 __global__ void attn_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                   const int* __restrict__ pos, TQ* __restrict__ out, int Hq, int D, int window, int chunk,
-                                  int S) {
+                                  int S, const int* __restrict__ row_req, const int* __restrict__ q_len, int row_limit) {
   const int t = blockIdx.y, hq = blockIdx.x;
+  if (q_len && q_len[row_req[t]] >= row_limit) return;
   const int p = pos[t];
   const int lo = window > 0 ? max(0, p - window + 1) : 0;
   const int s_lo = lo / chunk, s_hi = p / chunk;
@@ -375,7 +376,7 @@ HB_EXPORT int hb_attn_rows(const void* q, int q_dt, const void* kc, const void* 
                                  part_acc, part_ml, Hq, Hkv, D, page_size, window, scale, chunk, S);
     if (S > 1) {
       dim3 mg(Hq, T);
-      attn_merge_kernel<TA><<<mg, 64, 0, s>>>(part_acc, part_ml, pos, (TA*)out, Hq, D, window, chunk, S);
+      attn_merge_kernel<TA><<<mg, 64, 0, s>>>(part_acc, part_ml, pos, (TA*)out, Hq, D, window, chunk, S, nullptr, nullptr, 0);
     }
   });
   HB_CHECK_LAUNCH("hb_attn_rows");
@@ -385,7 +386,7 @@ HB_EXPORT int hb_attn_rows(const void* q, int q_dt, const void* kc, const void* 
 // Finishes rows that span several key chunks from partials laid out as hb_attn_rows leaves them
 // (for attention kernels of other libraries that write the same partials).
 HB_EXPORT int hb_attn_merge(float* workspace, const int* pos, void* out, int out_dt, int T, int Hq, int D, int window,
-                            int chunk, int max_pos, cudaStream_t s) {
+                            int chunk, int max_pos, const int* row_req, const int* q_len, int row_limit, cudaStream_t s) {
   const int S = max_pos / chunk + 1;
   if (T <= 0 || S <= 1) return 0;
   if (!workspace) HB_FAIL("hb_attn_merge: no workspace");
@@ -393,7 +394,8 @@ HB_EXPORT int hb_attn_merge(float* workspace, const int* pos, void* out, int out
   float* part_ml = workspace + (size_t)T * Hq * S * D;
   dim3 mg(Hq, T);
   HB_DISPATCH_1(out_dt, "hb_attn_merge",
-                (attn_merge_kernel<TA><<<mg, 64, 0, s>>>(part_acc, part_ml, pos, (TA*)out, Hq, D, window, chunk, S)));
+                (attn_merge_kernel<TA><<<mg, 64, 0, s>>>(part_acc, part_ml, pos, (TA*)out, Hq, D, window, chunk, S, row_req,
+                                                         q_len, row_limit)));
   HB_CHECK_LAUNCH("hb_attn_merge");
   return 0;
 }

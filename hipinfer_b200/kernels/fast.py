@@ -23,11 +23,13 @@ _SIGS = {
     "hb_gemm_skinny_plan": [_i, _i, _p, _p, _p, _p],
     "hb_gemm_stream": [_p, _l, _p, _l, _p, _l, _i, _i, _i, _i, _p, _l, _p, _i, _p, _p],
     "hb_gemm_stream_plan": [_i, _i, _p, _p, _p, _p],
-    "hb_attn_decode": [_p, _p, _p, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _i, _p],
+    "hb_attn_decode": [_p, _p, _p, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _i, _p, _i, _p],
+    "hb_flash_prefill": [_p, _p, _p, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p],
+    "hb_flash_prefill_supported": [_i, _i, _i],
     "hb_attn_decode_supported": [_i, _i, _i],
 }
 _fns = {}
-_LAUNCHES = {"hb_gemm_tc": 1, "hb_gemm_skinny": 1, "hb_gemm_stream": 1, "hb_attn_decode": 1}
+_LAUNCHES = {"hb_gemm_tc": 1, "hb_gemm_skinny": 1, "hb_gemm_stream": 1, "hb_attn_decode": 1, "hb_flash_prefill": 1}
 _status = None
 
 EPI_F32, EPI_BF16, EPI_ADD_F32, EPI_SWIGLU_BF16 = 0, 1, 2, 3
@@ -186,8 +188,9 @@ DECODE_CHUNK = 256      # keys per split of the decode attention kernel (absolut
 
 
 def attention_decode(q, k_cache, v_cache, block_table, row_request, positions, out, n_heads, n_kv_heads, head_dim,
-                     page_size, window, scale, max_pos, chunk=DECODE_CHUNK):
-    """The bf16 row-attention kernel itself (see csrc/attention_fast.cu), with the core library's merge."""
+                     page_size, window, scale, max_pos, chunk=DECODE_CHUNK, q_len=None, row_limit=0):
+    """The bf16 row-attention kernel itself (see csrc/attention_fast.cu), with the core library's merge.
+    With q_len (int32 per request) rows of requests with row_limit rows or more are skipped."""
     from . import ops
 
     T = q.shape[0]
@@ -195,18 +198,43 @@ def attention_decode(q, k_cache, v_cache, block_table, row_request, positions, o
     _call("hb_attn_decode", q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_table.data_ptr(),
           block_table.stride(0), row_request.data_ptr(), positions.data_ptr(), out.data_ptr(),
           None if ws is None else ws.data_ptr(), T, n_heads, n_kv_heads, head_dim, page_size, int(window), float(scale),
-          chunk, int(max_pos), _stream())
-    return ops.attention_merge(ws, positions, out, n_heads, head_dim, window, max_pos, chunk)
+          chunk, int(max_pos), None if q_len is None else q_len.data_ptr(), int(row_limit), _stream())
+    return ops.attention_merge(ws, positions, out, n_heads, head_dim, window, max_pos, chunk, row_request, q_len, row_limit)
 
 
 def attention_decode_supported(n_heads, n_kv_heads, head_dim) -> bool:
-    f = _fn("hb_attn_decode_supported")
-    return bool(f(n_heads, n_kv_heads, head_dim))
+    return bool(_fn("hb_attn_decode_supported")(n_heads, n_kv_heads, head_dim))
+
+
+def flash_prefill_supported(n_heads, n_kv_heads, head_dim) -> bool:
+    return bool(_fn("hb_flash_prefill_supported")(n_heads, n_kv_heads, head_dim))
+
+
+def flash_prefill(q, k_cache, v_cache, block_table, q_start, q_len, ctx_len, out, max_q_len, n_heads, n_kv_heads,
+                  head_dim, page_size, window, scale, min_rows=1):
+    """The flash kernel for prompt portions itself (see csrc/attention_prefill.cu): per request
+    q_start, q_len, ctx_len (int32 on the device); requests with fewer than min_rows rows are skipped."""
+    _call("hb_flash_prefill", q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_table.data_ptr(),
+          block_table.stride(0), q_start.data_ptr(), q_len.data_ptr(), ctx_len.data_ptr(), out.data_ptr(),
+          q_len.numel(), int(max_q_len), n_heads, n_kv_heads, head_dim, page_size, int(window), float(scale),
+          int(min_rows), _stream())
+    return out
+
+
+FLASH_MIN_ROWS = 16     # portions of at least this many rows go to the flash kernel, shorter ones to the row kernel
 
 
 def attention(q, k_cache, v_cache, batch, group, out, n_heads, n_kv_heads, head_dim, page_size, window, scale) -> bool:
     if PLAIN_ONLY or q.dtype != torch.bfloat16 or not attention_decode_supported(n_heads, n_kv_heads, head_dim):
         return False
-    attention_decode(q, k_cache, v_cache, batch.block_tables[group], batch.row_request, batch.positions, out, n_heads,
-                     n_kv_heads, head_dim, page_size, window, scale, batch.max_pos)
+    use_flash = flash_prefill_supported(n_heads, n_kv_heads, head_dim) and batch.max_q_len >= FLASH_MIN_ROWS
+    need_rows = not use_flash or min(batch.h_q_len) < FLASH_MIN_ROWS
+    bt = batch.block_tables[group]
+    if use_flash:
+        flash_prefill(q, k_cache, v_cache, bt, batch.req_q_start, batch.req_q_len, batch.req_ctx_len, out,
+                      batch.max_q_len, n_heads, n_kv_heads, head_dim, page_size, window, scale, FLASH_MIN_ROWS)
+    if need_rows:
+        attention_decode(q, k_cache, v_cache, bt, batch.row_request, batch.positions, out, n_heads, n_kv_heads,
+                         head_dim, page_size, window, scale, batch.max_pos,
+                         q_len=batch.req_q_len if use_flash else None, row_limit=FLASH_MIN_ROWS)
     return True

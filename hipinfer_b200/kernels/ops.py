@@ -28,7 +28,7 @@ _SIGS = {
         "hb_rope_table": [_p, _p, _i, _i, _p],
         "hb_rope_kv": [_p, _i, _l, _p, _p, _p, _p, _i, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p],
         "hb_attn_rows": [_p, _i, _p, _p, _i, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _i, _p],
-        "hb_attn_merge": [_p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p],
+        "hb_attn_merge": [_p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p, _p, _i, _p],
         "hb_sample": [_p, _l, _i, _i, _p, _p, _p, _p, _p],
         "hb_convert": [_p, _i, _p, _i, _l, _p],
     },
@@ -207,11 +207,13 @@ def attention_workspace(T: int, n_heads: int, head_dim: int, max_pos: int, chunk
     return torch.empty(n_ws, dtype=torch.float32, device=device) if n_ws else None
 
 
-def attention_merge(ws, positions, out, n_heads, head_dim, window, max_pos, chunk):
+def attention_merge(ws, positions, out, n_heads, head_dim, window, max_pos, chunk, row_request=None, q_len=None,
+                    row_limit=0):
+    """Finish rows whose keys span several chunks; rows of requests with row_limit rows or more are left alone."""
     if ws is None:
         return out
     _call("core", "hb_attn_merge", ws.data_ptr(), positions.data_ptr(), out.data_ptr(), _dt(out), out.shape[0], n_heads,
-          head_dim, int(window), chunk, int(max_pos), _stream())
+          head_dim, int(window), chunk, int(max_pos), _ptr(row_request), _ptr(q_len), int(row_limit), _stream())
     return out
 
 

@@ -201,3 +201,55 @@ def test_attention_decode_far_key_stands_out():
     ref = plain.attention_scores_softmax_values(qf, ks[0], vs[0], [899], list(range(900)))
     torch.testing.assert_close(out.float().cpu().reshape(1, Hq, D), ref, rtol=1e-2, atol=1e-2)
     assert float((out.float().cpu().reshape(Hq, D)[0] - vs[0][far, 0]).abs().max()) < 0.05
+
+
+@pytest.mark.parametrize("Hq,Hkv,D,ps,window", [(8, 2, 64, 16, 0), (3, 1, 128, 16, 0), (4, 4, 64, 8, 0), (6, 2, 64, 16, 100),
+                                                (2, 1, 128, 32, 0)])
+def test_flash_prefill(Hq, Hkv, D, ps, window):
+    """Portions of several requests in one launch: a whole prompt from position 0 with a ragged
+    last tile, a portion in the middle of a sequence that starts inside a page and inside a key
+    tile, a long portion behind a long context, and a short portion that must be left alone."""
+    ctx = [0, 83, 400, 50]
+    qn = [150, 77, 130, 5]
+    lens = [c + n for c, n in zip(ctx, qn)]
+    kc, vc, bt, ks, vs = _paged_setup(lens, Hkv, D, ps, torch.bfloat16, 31)
+    T = sum(qn)
+    q = rnd(T, Hq * D, seed=32)
+    qf = q.float().cpu().reshape(T, Hq, D)
+    out = torch.full((T, Hq * D), 7.0, dtype=torch.bfloat16, device=DEV)
+    starts = [sum(qn[:i]) for i in range(4)]
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    fast().flash_prefill(q, kc, vc, bt, i32(starts), i32(qn), i32(ctx), out, max(qn), Hq, Hkv, D, ps, window,
+                         1.0 / math.sqrt(D), min_rows=16)
+    got = out.float().cpu().reshape(T, Hq, D)
+    for r in range(3):
+        pos = list(range(ctx[r], ctx[r] + qn[r]))
+        ref = plain.attention_scores_softmax_values(qf[starts[r]:starts[r] + qn[r]], ks[r], vs[r], pos, list(range(lens[r])),
+                                                    window or None)
+        torch.testing.assert_close(got[starts[r]:starts[r] + qn[r]], ref, rtol=2e-2, atol=2e-2,
+                                   msg=lambda m: f"request {r}: {m}")
+    assert bool((got[starts[3]:] == 7.0).all()), "the short portion was touched"
+
+
+def test_flash_prefill_far_key_and_cutting():
+    """A far key made to stand out comes through; the same rows cut into two portions give the same bits."""
+    Hq, Hkv, D, ps = 4, 2, 64, 16
+    n = 600
+    kc, vc, bt, ks, vs = _paged_setup([n], Hkv, D, ps, torch.bfloat16, 33)
+    q = rnd(n, Hq * D, seed=34)
+    qf = q.float().cpu().reshape(n, Hq, D)
+    far, row = 7, 555
+    page, off = int(bt[0, far // ps]), far % ps
+    kc[page, 0, off] = (qf[row, 0] * 4.0).to(torch.bfloat16).to(DEV)
+    ks[0][far, 0] = kc[page, 0, off].float().cpu()
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    whole = torch.empty(n, Hq * D, dtype=torch.bfloat16, device=DEV)
+    fast().flash_prefill(q, kc, vc, bt, i32([0]), i32([n]), i32([0]), whole, n, Hq, Hkv, D, ps, 0, 1 / math.sqrt(D))
+    ref = plain.attention_scores_softmax_values(qf, ks[0], vs[0], list(range(n)), list(range(n)))
+    torch.testing.assert_close(whole.float().cpu().reshape(n, Hq, D), ref, rtol=2e-2, atol=2e-2)
+    assert float((whole.float().cpu().reshape(n, Hq, D)[row, 0] - vs[0][far, 0]).abs().max()) < 0.05
+    cut = 333
+    tail = torch.empty(n - cut, Hq * D, dtype=torch.bfloat16, device=DEV)
+    fast().flash_prefill(q[cut:].contiguous(), kc, vc, bt, i32([0]), i32([n - cut]), i32([cut]), tail, n - cut, Hq, Hkv, D,
+                         ps, 0, 1 / math.sqrt(D))
+    assert torch.equal(tail, whole[cut:])

@@ -10,10 +10,12 @@ import tiny
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"a": [5, 11, 17, 64, 100, 128, 33, 90], "b": [1, 7, 33, 64, 200, 256, 150, 81]}
+LENGTHS = {"a": [5, 11, 17, 64, 100, 128, 33, 90], "b": [1, 7, 33, 64, 200, 256, 150, 81],
+           "c": [700, 130, 64, 257, 400, 16, 33, 90]}
 
 
-@pytest.fixture(scope="module", params=[("a", "float32"), ("b", "float32"), ("a", "bfloat16"), ("b", "bfloat16")],
+@pytest.fixture(scope="module", params=[("a", "float32"), ("b", "float32"), ("c", "float32"), ("a", "bfloat16"), ("b", "bfloat16"),
+                                        ("c", "bfloat16")],
                 ids=lambda p: f"{p[0]}-{p[1]}")
 def setup(request, tmp_path_factory):
     which, dtype = request.param
