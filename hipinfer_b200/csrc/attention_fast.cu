@@ -17,12 +17,13 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
     const int* __restrict__ bt, int bt_stride, const int* __restrict__ row_req, const int* __restrict__ pos,
     __nv_bfloat16* __restrict__ out, float* __restrict__ part_acc, float* __restrict__ part_ml, int Hq, int Hkv,
     int page_size, int window, float scale, int chunk, int S, const int* __restrict__ q_len, int row_limit) {
-  constexpr int EPL = D / 32;  // value elements per lane
   extern __shared__ float smem[];
   float* qs = smem;                 // [G][D], scaled
   float* sc = qs + G * D;           // [G][chunk]
   float* ml = sc + G * chunk;       // [G][2]
   float* red = ml + 2 * G;          // [4 warps][G][D]
+  hb_pdl_launch();
+  hb_pdl_wait();
   const int t = blockIdx.z, h = blockIdx.y, s = blockIdx.x;
   if (q_len && q_len[row_req[t]] >= row_limit) return;  // a long portion: the flash kernel's
   const int p = pos[t];
@@ -83,38 +84,44 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
   }
   __syncthreads();
 
-  // values: warp w takes keys w, w + 4, ...; a lane owns EPL consecutive dimensions for all G heads
-  float acc[G][EPL];
+  // values: D/8 lanes share a key's row with 16-byte loads, so a warp takes 32 / (D/8) keys per pass
+  // and each value is read once for all G heads; lanes, then warps, are summed in a fixed order
+  constexpr int TPK = D / 8, KPW = 32 / TPK;
+  const int kq = lane / TPK, dc = lane % TPK;
+  float acc[G][8];
 #pragma unroll
   for (int g = 0; g < G; g++)
 #pragma unroll
-    for (int e = 0; e < EPL; e++) acc[g][e] = 0.f;
-  for (int j = warp; j < nk; j += 4) {
+    for (int e = 0; e < 8; e++) acc[g][e] = 0.f;
+#pragma unroll 4
+  for (int j = warp * KPW + kq; j < nk; j += 4 * KPW) {
     const int kp = k0 + j;
     const size_t page = table[kp / page_size];
-    const __nv_bfloat16* vr = vc + ((page * Hkv + h) * page_size + kp % page_size) * D + lane * EPL;
-    float vf[EPL];
-    if (EPL == 1) {
-      vf[0] = __bfloat162float(vr[0]);
-    } else if (EPL == 2) {
-      const float2 f = __bfloat1622float2(*(const __nv_bfloat162*)vr);
-      vf[0] = f.x; vf[EPL - 1] = f.y;
-    } else {
-      const uint2 raw = *(const uint2*)vr;
-      const float2 f0 = __bfloat1622float2(*(const __nv_bfloat162*)&raw.x), f1 = __bfloat1622float2(*(const __nv_bfloat162*)&raw.y);
-      vf[0] = f0.x; vf[1 % EPL] = f0.y; vf[2 % EPL] = f1.x; vf[3 % EPL] = f1.y;
+    const uint4 raw = *(const uint4*)(vc + ((page * Hkv + h) * page_size + kp % page_size) * D + dc * 8);
+    const __nv_bfloat162* v2 = (const __nv_bfloat162*)&raw;
+    float vf[8];
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+      const float2 f = __bfloat1622float2(v2[e]);
+      vf[2 * e] = f.x;
+      vf[2 * e + 1] = f.y;
     }
 #pragma unroll
     for (int g = 0; g < G; g++) {
       const float pj = sc[g * chunk + j];
 #pragma unroll
-      for (int e = 0; e < EPL; e++) acc[g][e] = fmaf(pj, vf[e], acc[g][e]);
+      for (int e = 0; e < 8; e++) acc[g][e] = fmaf(pj, vf[e], acc[g][e]);
     }
   }
 #pragma unroll
   for (int g = 0; g < G; g++)
 #pragma unroll
-    for (int e = 0; e < EPL; e++) red[(warp * G + g) * D + lane * EPL + e] = acc[g][e];
+    for (int e = 0; e < 8; e++) {
+      float a = acc[g][e];
+#pragma unroll
+      for (int o = TPK; o < 32; o <<= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+      if (kq == 0) red[(warp * G + g) * D + dc * 8 + e] = a;
+    }
   __syncthreads();
   const bool whole = s_lo == s_hi;
   for (int i = tid; i < G * D; i += AD_THREADS) {
@@ -138,8 +145,8 @@ static int launch_decode(int G, dim3 grid, size_t smem, cudaStream_t st, const _
                          int chunk, int S, const int* q_len, int row_limit) {
 #define HB_AD_CASE(GG)                                                                                              \
   case GG:                                                                                                          \
-    attn_decode_kernel<D, GG><<<grid, AD_THREADS, smem, st>>>(q, kc, vc, bt, bt_stride, row_req, pos, out, pa, pm, Hq, \
-                                                              Hkv, page_size, window, scale, chunk, S, q_len, row_limit); \
+    hb_launch(attn_decode_kernel<D, GG>, grid, AD_THREADS, smem, st, q, kc, vc, bt, bt_stride, row_req, pos, out, pa, pm, \
+              Hq, Hkv, page_size, window, scale, chunk, S, q_len, row_limit);                                        \
     return 0;
   switch (G) {
     HB_AD_CASE(1) HB_AD_CASE(2) HB_AD_CASE(3) HB_AD_CASE(4) HB_AD_CASE(5) HB_AD_CASE(6) HB_AD_CASE(7) HB_AD_CASE(8)

@@ -73,3 +73,31 @@ __device__ __forceinline__ float hb_block_sum(float v, float* sh) {
     else if ((da) == HB_BF16) { using TA = __nv_bfloat16; __VA_ARGS__; }    \
     else HB_FAIL("%s: unknown dtype code %d", NAME, (int)(da));             \
   } while (0)
+
+// ---------------------------------------------------------------------------------------
+// Programmatic dependent launch: a kernel launched with hb_launch() may start while the kernel
+// before it in the stream is still running. It calls hb_pdl_launch() at once (so that ITS
+// successor can be staged as early) and hb_pdl_wait() before its first access to anything an
+// earlier kernel wrote or still reads; only work on constants (weights, its own shared memory,
+// barriers, tensor memory) may come before the wait. hb_pdl_wait() returns when the preceding
+// kernel has finished and its writes are visible. With g_hb_pdl == 0 launches are ordinary.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void hb_pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void hb_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+extern int g_hb_pdl;
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t hb_launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_hb_pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}

@@ -20,12 +20,16 @@ void hb_set_error(const char* fmt, ...) {
 }
 HB_EXPORT const char* hb_last_error() { return g_err; }
 HB_EXPORT int hb_core_abi_version() { return 1; }
+int g_hb_pdl = 1;
+HB_EXPORT void hb_set_pdl(int on) { g_hb_pdl = on; }
 
 // ---------------------------------------------------------------------------------------
 // Embedding: out[i, :] = table[tok[i], :] into the 32-bit residual stream.
 // ---------------------------------------------------------------------------------------
 template <typename TE>
 __global__ void embed_kernel(const TE* __restrict__ table, const int* __restrict__ tok, float* __restrict__ out, int H) {
+  hb_pdl_launch();
+  hb_pdl_wait();
   const TE* src = table + (size_t)tok[blockIdx.x] * H;
   float* dst = out + (size_t)blockIdx.x * H;
   for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = hb_to_float(src[i]);
@@ -33,7 +37,7 @@ __global__ void embed_kernel(const TE* __restrict__ table, const int* __restrict
 
 HB_EXPORT int hb_embed(const void* table, int table_dt, const int* tok, float* out, int T, int H, cudaStream_t s) {
   if (T <= 0) return 0;
-  HB_DISPATCH_1(table_dt, "hb_embed", (embed_kernel<TA><<<T, 256, 0, s>>>((const TA*)table, tok, out, H)));
+  HB_DISPATCH_1(table_dt, "hb_embed", (hb_launch(embed_kernel<TA>, T, 256, 0, s, (const TA*)table, tok, out, H)));
   HB_CHECK_LAUNCH("hb_embed");
   return 0;
 }
@@ -56,9 +60,71 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const TW* __restrict
   for (int i = threadIdx.x; i < H; i += blockDim.x) yr[i] = hb_from_float<TO>(hb_to_float(w[i]) * (xr[i] * inv));
 }
 
+__device__ __forceinline__ float4 hb_load4(const float* p) { return *(const float4*)p; }
+__device__ __forceinline__ float4 hb_load4(const __nv_bfloat16* p) {
+  const uint2 r = *(const uint2*)p;
+  const float2 a = __bfloat1622float2(*(const __nv_bfloat162*)&r.x), b = __bfloat1622float2(*(const __nv_bfloat162*)&r.y);
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void hb_store4(float* p, float4 v) { *(float4*)p = v; }
+__device__ __forceinline__ void hb_store4(__nv_bfloat16* p, float4 v) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  uint2 r;
+  r.x = *(uint32_t*)&a;
+  r.y = *(uint32_t*)&b;
+  *(uint2*)p = r;
+}
+
+// The same with 16-byte accesses and the row held in registers between the two passes
+// (H a multiple of 4, at most 256 * 4 * NV elements). The sum runs over the same per-thread
+// partial sums whatever M is.
+template <typename TW, typename TO, int NV>
+__global__ void __launch_bounds__(256) rmsnorm_vec_kernel(const float* __restrict__ x, const TW* __restrict__ w,
+                                                          TO* __restrict__ y, const int* __restrict__ rows, int H,
+                                                          float eps) {
+  __shared__ float sh[32];
+  hb_pdl_launch();
+  hb_pdl_wait();
+  const size_t r = rows ? (size_t)rows[blockIdx.x] : (size_t)blockIdx.x;
+  const float* xr = x + r * H;
+  const int nvec = H >> 2;
+  float4 v[NV];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; i++) {
+    const int c = threadIdx.x + i * 256;
+    v[i] = c < nvec ? hb_load4(xr + 4 * c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    ss = fmaf(v[i].x, v[i].x, ss); ss = fmaf(v[i].y, v[i].y, ss);
+    ss = fmaf(v[i].z, v[i].z, ss); ss = fmaf(v[i].w, v[i].w, ss);
+  }
+  const float inv = rsqrtf(hb_block_sum(ss, sh) / (float)H + eps);
+  TO* yr = y + (size_t)blockIdx.x * H;
+#pragma unroll
+  for (int i = 0; i < NV; i++) {
+    const int c = threadIdx.x + i * 256;
+    if (c < nvec) {
+      const float4 ww = hb_load4(w + 4 * c);
+      hb_store4(yr + 4 * c, make_float4(ww.x * (v[i].x * inv), ww.y * (v[i].y * inv), ww.z * (v[i].z * inv),
+                                        ww.w * (v[i].w * inv)));
+    }
+  }
+}
+
 HB_EXPORT int hb_rmsnorm(const float* x, const void* w, int w_dt, void* y, int y_dt, const int* rows, int M, int H,
                          float eps, cudaStream_t s) {
   if (M <= 0) return 0;
+  const bool aligned = !(((uintptr_t)x | (uintptr_t)w | (uintptr_t)y) & 15);
+  if ((H & 3) == 0 && H <= 8192 && aligned) {
+    if (H <= 2048) {
+      HB_DISPATCH_2(w_dt, y_dt, "hb_rmsnorm",
+                    (hb_launch(rmsnorm_vec_kernel<TA, TB, 2>, M, 256, 0, s, x, (const TA*)w, (TB*)y, rows, H, eps)));
+    } else {
+      HB_DISPATCH_2(w_dt, y_dt, "hb_rmsnorm",
+                    (hb_launch(rmsnorm_vec_kernel<TA, TB, 8>, M, 256, 0, s, x, (const TA*)w, (TB*)y, rows, H, eps)));
+    }
+    HB_CHECK_LAUNCH("hb_rmsnorm");
+    return 0;
+  }
   HB_DISPATCH_2(w_dt, y_dt, "hb_rmsnorm",
                 (rmsnorm_kernel<TA, TB><<<M, 256, 0, s>>>(x, (const TA*)w, (TB*)y, rows, H, eps)));
   HB_CHECK_LAUNCH("hb_rmsnorm");
@@ -232,12 +298,62 @@ __global__ void rope_kv_kernel(const TI* __restrict__ qkv, long ld, const int* _
   }
 }
 
+// The same four elements at a time (rotary over the whole head, head_dim a multiple of 8).
+template <typename TI, typename TQ, typename TC>
+__global__ void __launch_bounds__(256) rope_kv_vec_kernel(const TI* __restrict__ qkv, long ld, const int* __restrict__ pos,
+                                                          const int* __restrict__ slot_map, const float2* __restrict__ table,
+                                                          TQ* __restrict__ q_out, TC* __restrict__ kc, TC* __restrict__ vc,
+                                                          int Hq, int Hkv, int D, int page_size) {
+  hb_pdl_launch();
+  hb_pdl_wait();
+  const int t = blockIdx.x, half = D >> 1, hv = half >> 2;  // hv: groups of 4 pairs per head
+  const TI* base = qkv + (size_t)t * ld;
+  const float2* cs = table + (size_t)pos[t] * half;
+  const int slot = slot_map ? slot_map[t] : -1;
+  const size_t page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot % page_size : 0;
+  const int n_rot = (slot >= 0 ? Hq + Hkv : Hq) * hv;
+  for (int i = threadIdx.x; i < n_rot; i += blockDim.x) {
+    const int hh = i / hv, j = (i - hh * hv) * 4;
+    const float4 x1 = hb_load4(base + hh * D + j), x2 = hb_load4(base + hh * D + half + j);
+    const float4 c01 = *(const float4*)(cs + j), c23 = *(const float4*)(cs + j + 2);  // (cos, sin) pairs
+    float4 y1, y2;
+    y1.x = __fsub_rn(__fmul_rn(x1.x, c01.x), __fmul_rn(x2.x, c01.y)); y2.x = __fadd_rn(__fmul_rn(x2.x, c01.x), __fmul_rn(x1.x, c01.y));
+    y1.y = __fsub_rn(__fmul_rn(x1.y, c01.z), __fmul_rn(x2.y, c01.w)); y2.y = __fadd_rn(__fmul_rn(x2.y, c01.z), __fmul_rn(x1.y, c01.w));
+    y1.z = __fsub_rn(__fmul_rn(x1.z, c23.x), __fmul_rn(x2.z, c23.y)); y2.z = __fadd_rn(__fmul_rn(x2.z, c23.x), __fmul_rn(x1.z, c23.y));
+    y1.w = __fsub_rn(__fmul_rn(x1.w, c23.z), __fmul_rn(x2.w, c23.w)); y2.w = __fadd_rn(__fmul_rn(x2.w, c23.z), __fmul_rn(x1.w, c23.w));
+    if (hh < Hq) {
+      TQ* dst = q_out + (size_t)t * Hq * D + hh * D + j;
+      hb_store4(dst, y1);
+      hb_store4(dst + half, y2);
+    } else {
+      TC* dst = kc + ((page * Hkv + (hh - Hq)) * page_size + off) * D + j;
+      hb_store4(dst, y1);
+      hb_store4(dst + half, y2);
+    }
+  }
+  if (slot < 0) return;
+  const TI* v = base + (size_t)(Hq + Hkv) * D;
+  const int dv = D >> 2;
+  for (int i = threadIdx.x; i < Hkv * dv; i += blockDim.x) {
+    const int h = i / dv, d = (i - h * dv) * 4;
+    hb_store4(vc + ((page * Hkv + h) * page_size + off) * D + d, hb_load4(v + h * D + d));
+  }
+}
+
 HB_EXPORT int hb_rope_kv(const void* qkv, int qkv_dt, long ld, const int* pos, const int* slot_map, const void* table,
                          void* q_out, int q_dt, void* kc, void* vc, int cache_dt, int T, int Hq, int Hkv, int D, int rot,
                          int page_size, cudaStream_t s) {
   if (T <= 0) return 0;
   if (rot < 0 || rot > D || (rot & 1)) HB_FAIL("hb_rope_kv: rotary width %d must be even and at most head_dim %d", rot, D);
   if (q_dt != cache_dt) HB_FAIL("hb_rope_kv: q and the cache must have the same element type");
+  const bool aligned = !(((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)kc | (uintptr_t)vc | (uintptr_t)table) & 15);
+  if (rot == D && (D & 7) == 0 && (ld & 3) == 0 && aligned) {
+    HB_DISPATCH_2(qkv_dt, q_dt, "hb_rope_kv",
+                  (hb_launch(rope_kv_vec_kernel<TA, TB, TB>, T, 256, 0, s, (const TA*)qkv, ld, pos, slot_map,
+                             (const float2*)table, (TB*)q_out, (TB*)kc, (TB*)vc, Hq, Hkv, D, page_size)));
+    HB_CHECK_LAUNCH("hb_rope_kv");
+    return 0;
+  }
   HB_DISPATCH_2(qkv_dt, q_dt, "hb_rope_kv",
                 (rope_kv_kernel<TA, TB, TB><<<T, 256, 0, s>>>((const TA*)qkv, ld, pos, slot_map, (const float2*)table,
                                                               (TB*)q_out, (TB*)kc, (TB*)vc, Hq, Hkv, D, rot, page_size)));
@@ -326,6 +442,8 @@ template <typename TQ>
 __global__ void attn_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                   const int* __restrict__ pos, TQ* __restrict__ out, int Hq, int D, int window, int chunk,
                                   int S, const int* __restrict__ row_req, const int* __restrict__ q_len, int row_limit) {
+  hb_pdl_launch();
+  hb_pdl_wait();
   const int t = blockIdx.y, hq = blockIdx.x;
   if (q_len && q_len[row_req[t]] >= row_limit) return;
   const int p = pos[t];
@@ -376,7 +494,8 @@ HB_EXPORT int hb_attn_rows(const void* q, int q_dt, const void* kc, const void* 
                                  part_acc, part_ml, Hq, Hkv, D, page_size, window, scale, chunk, S);
     if (S > 1) {
       dim3 mg(Hq, T);
-      attn_merge_kernel<TA><<<mg, 64, 0, s>>>(part_acc, part_ml, pos, (TA*)out, Hq, D, window, chunk, S, nullptr, nullptr, 0);
+      hb_launch(attn_merge_kernel<TA>, mg, 64, 0, s, (const float*)part_acc, (const float*)part_ml, pos, (TA*)out, Hq, D, window,
+                chunk, S, (const int*)nullptr, (const int*)nullptr, 0);
     }
   });
   HB_CHECK_LAUNCH("hb_attn_rows");
@@ -394,8 +513,8 @@ HB_EXPORT int hb_attn_merge(float* workspace, const int* pos, void* out, int out
   float* part_ml = workspace + (size_t)T * Hq * S * D;
   dim3 mg(Hq, T);
   HB_DISPATCH_1(out_dt, "hb_attn_merge",
-                (attn_merge_kernel<TA><<<mg, 64, 0, s>>>(part_acc, part_ml, pos, (TA*)out, Hq, D, window, chunk, S, row_req,
-                                                         q_len, row_limit)));
+                (hb_launch(attn_merge_kernel<TA>, mg, 64, 0, s, (const float*)part_acc, (const float*)part_ml, pos, (TA*)out, Hq,
+                           D, window, chunk, S, row_req, q_len, row_limit)));
   HB_CHECK_LAUNCH("hb_attn_merge");
   return 0;
 }
@@ -429,6 +548,8 @@ __global__ void __launch_bounds__(1024) sample_kernel(const float* __restrict__ 
                                                       int* __restrict__ out) {
   __shared__ float bv[32];
   __shared__ int bi[32];
+  hb_pdl_launch();
+  hb_pdl_wait();
   const float* l = logits + (size_t)blockIdx.x * ld;
   const float temp = temperature ? temperature[blockIdx.x] : 0.f;
   const uint32_t sd = seed ? seed[blockIdx.x] : 0u, ps = position ? (uint32_t)position[blockIdx.x] : 0u;
@@ -458,7 +579,7 @@ HB_EXPORT int hb_sample(const float* logits, long ld, int rows, int V, const flo
                         const int* position, int* out, cudaStream_t s) {
   if (rows <= 0) return 0;
   if (V <= 0) HB_FAIL("hb_sample: empty vocabulary");
-  sample_kernel<<<rows, 1024, 0, s>>>(logits, ld, V, temperature, seed, position, out);
+  hb_launch(sample_kernel, rows, 1024, 0, s, logits, ld, V, temperature, seed, position, out);
   HB_CHECK_LAUNCH("hb_sample");
   return 0;
 }

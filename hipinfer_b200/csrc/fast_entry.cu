@@ -12,3 +12,5 @@ void hb_set_error(const char* fmt, ...) {
 }
 HB_EXPORT const char* hb_last_error() { return g_err; }
 HB_EXPORT int hb_fast_abi_version() { return 1; }
+int g_hb_pdl = 1;
+HB_EXPORT void hb_set_pdl(int on) { g_hb_pdl = on; }

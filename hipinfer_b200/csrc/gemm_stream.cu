@@ -53,6 +53,7 @@ __global__ void __launch_bounds__(192) gemm_stream_kernel(const __grid_constant_
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
   int* is_last = (int*)(tmem_slot + 2);
 
+  hb_pdl_launch();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nb = blockIdx.x, sp = blockIdx.y, ksplit = gridDim.y, NP = gridDim.x * ST_ROWS;
   const int n0 = nb * ST_ROWS, k_begin = sp * kslice, k_end = min(K, k_begin + kslice);
@@ -76,7 +77,17 @@ __global__ void __launch_bounds__(192) gemm_stream_kernel(const __grid_constant_
 
   if (warp == 4) {
     if (lane == 0) {
-      for (int kb = 0; kb < num_kb; kb++) {
+      // the weights do not depend on the kernel before this one: the first stages' weight tiles
+      // are requested before the wait, the activations after it
+      const int pre = num_kb < S::STAGES ? num_kb : S::STAGES;
+      for (int kb = 0; kb < pre; kb++) {
+        hb_mbar_expect_tx(&full[kb], S::STAGE);
+        hb_tma_load_2d(smem + kb * S::STAGE, &map_w, &full[kb], k_begin + kb * ST_BK, n0);
+      }
+      hb_pdl_wait();
+      for (int kb = 0; kb < pre; kb++)
+        hb_tma_load_2d(smem + kb * S::STAGE + ST_W_BYTES, &map_x, &full[kb], k_begin + kb * ST_BK, 0);
+      for (int kb = pre; kb < num_kb; kb++) {
         const uint32_t s = kb % S::STAGES, ph = (kb / S::STAGES) & 1;
         if (!hb_mbar_wait(&empty[s], ph ^ 1, abort_flag)) break;
         hb_mbar_expect_tx(&full[s], S::STAGE);
@@ -104,6 +115,7 @@ __global__ void __launch_bounds__(192) gemm_stream_kernel(const __grid_constant_
     // epilogue warps: lane = output column n0 + 32 * warp + lane, v[m] = token m
     const bool ok = hb_mbar_wait(done, 0, abort_flag);
     hb_tc_fence_after();
+    hb_pdl_wait();  // before the first access to memory that earlier kernels wrote or still read
     float v[NT];
 #pragma unroll
     for (int c = 0; c < NT / 16; c++) hb_tmem_ld16(tmem_base + ((uint32_t)(warp * 32) << 16) + c * 16, v + 16 * c);
@@ -213,7 +225,9 @@ static int launch_stream(const CUtensorMap& mw, const CUtensorMap& mx, void* C, 
     if (e != cudaSuccess) HB_FAIL("hb_gemm_stream: %s", cudaGetErrorString(e));
     configured = true;
   }
-  kern<<<dim3(n_blocks, ksplit), 192, S::TOTAL, s>>>(mw, mx, C, ldc, M, N, K, kslice, ws, counters, epi, status);
+  cudaError_t e = hb_launch(kern, dim3(n_blocks, ksplit), 192, S::TOTAL, s, mw, mx, C, ldc, M, N, K, kslice, ws, counters,
+                            epi, status);
+  if (e != cudaSuccess) HB_FAIL("hb_gemm_stream: %s", cudaGetErrorString(e));
   return 0;
 }
 

@@ -268,8 +268,10 @@ HB_EXPORT int hb_gemm_tc(const void* A, long lda, const void* W, long ldw, void*
   if (epi == EPI_SWIGLU_BF16 && (N & 31)) HB_FAIL("hb_gemm_tc: SwiGLU needs N = %d to be a multiple of 32", N);
   if (!status) HB_FAIL("hb_gemm_tc: no status word");
   if (tile_n == 0) {
+    // 128 x 256 tiles feed the tensor cores best; the narrower tile only when the wide one
+    // would leave most SMs without work
     const long tiles256 = (long)((M + BM - 1) / BM) * ((N + 255) / 256);
-    tile_n = (N >= 256 && tiles256 >= 2L * sm_count()) ? 256 : 128;
+    tile_n = (N >= 256 && 4 * tiles256 >= 3L * sm_count()) ? 256 : 128;
   }
   if (tile_n != 128 && tile_n != 256) HB_FAIL("hb_gemm_tc: tile_n must be 128 or 256");
   CUtensorMap ma, mw;

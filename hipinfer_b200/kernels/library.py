@@ -156,6 +156,8 @@ def load(name: str) -> ctypes.CDLL:
         except OSError as e:
             raise KernelLibraryError(f"cannot load {so}: {e}") from None
         lib.hb_last_error.restype = ctypes.c_char_p
+        if os.environ.get("HIPINFER_B200_PDL", "1") == "0":     # ordinary launches instead of programmatic dependent ones
+            lib.hb_set_pdl(0)
         _loaded[name] = lib
         return lib
 
