@@ -575,11 +575,84 @@ __global__ void __launch_bounds__(1024) sample_kernel(const float* __restrict__ 
   }
 }
 
+// Two stages for large vocabularies: slices of a row in parallel, then the best of the slices.
+// The comparison is a total order (value, then lower index), so the split does not change the result.
+__global__ void __launch_bounds__(256) sample_slice_kernel(const float* __restrict__ logits, long ld, int V, int slice,
+                                                           const float* __restrict__ temperature,
+                                                           const uint32_t* __restrict__ seed, const int* __restrict__ position,
+                                                           float* __restrict__ part_v, int* __restrict__ part_i) {
+  __shared__ float bv[8];
+  __shared__ int bi[8];
+  hb_pdl_launch();
+  hb_pdl_wait();
+  const int row = blockIdx.y, s = blockIdx.x;
+  const float* l = logits + (size_t)row * ld;
+  const float temp = temperature ? temperature[row] : 0.f;
+  const uint32_t sd = seed ? seed[row] : 0u, ps = position ? (uint32_t)position[row] : 0u;
+  const int i0 = s * slice, i1 = min(V, i0 + slice);
+  float best = -INFINITY;
+  int idx = i0 < V ? i0 : 0;
+  for (int i = i0 + threadIdx.x; i < i1; i += 256) {
+    float v = l[i];
+    if (temp > 0.f) v = v / temp - logf(-logf(sample_uniform(sd, ps, (uint32_t)i)));
+    if (better(v, i, best, idx)) { best = v; idx = i; }
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+    if (better(ov, oi, best, idx)) { best = ov; idx = oi; }
+  }
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  if (lane == 0) { bv[w] = best; bi[w] = idx; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int i = 1; i < 8; i++)
+      if (better(bv[i], bi[i], best, idx)) { best = bv[i]; idx = bi[i]; }
+    part_v[(size_t)row * gridDim.x + s] = best;
+    part_i[(size_t)row * gridDim.x + s] = idx;
+  }
+}
+
+__global__ void __launch_bounds__(32) sample_final_kernel(const float* __restrict__ part_v, const int* __restrict__ part_i,
+                                                          int n, int* __restrict__ out) {
+  hb_pdl_launch();
+  hb_pdl_wait();
+  const int row = blockIdx.x;
+  float best = -INFINITY;
+  int idx = 0;
+  bool have = false;
+  for (int i = threadIdx.x; i < n; i += 32) {
+    const float v = part_v[(size_t)row * n + i];
+    const int ix = part_i[(size_t)row * n + i];
+    if (!have || better(v, ix, best, idx)) { best = v; idx = ix; have = true; }
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+    const int oh = __shfl_xor_sync(0xffffffffu, (int)have, o);
+    if (oh && (!have || better(ov, oi, best, idx))) { best = ov; idx = oi; have = true; }
+  }
+  if (threadIdx.x == 0) out[row] = idx;
+}
+
+// Slices per row that hb_sample uses for a vocabulary of V (its workspace holds 2 * rows * slices 32-bit words).
+HB_EXPORT int hb_sample_slices(int V) { return V <= 4096 ? 1 : (V + 2047) / 2048 > 128 ? 128 : (V + 2047) / 2048; }
+
 HB_EXPORT int hb_sample(const float* logits, long ld, int rows, int V, const float* temperature, const uint32_t* seed,
-                        const int* position, int* out, cudaStream_t s) {
+                        const int* position, int* out, void* workspace, cudaStream_t s) {
   if (rows <= 0) return 0;
   if (V <= 0) HB_FAIL("hb_sample: empty vocabulary");
-  hb_launch(sample_kernel, rows, 1024, 0, s, logits, ld, V, temperature, seed, position, out);
+  const int n = hb_sample_slices(V);
+  if (n == 1 || !workspace) {
+    hb_launch(sample_kernel, rows, 1024, 0, s, logits, ld, V, temperature, seed, position, out);
+  } else {
+    if (rows > 65535) HB_FAIL("hb_sample: %d rows are beyond the grid limit", rows);
+    float* pv = (float*)workspace;
+    int* pi = (int*)workspace + (size_t)rows * n;
+    const int slice = (V + n - 1) / n;
+    hb_launch(sample_slice_kernel, dim3(n, rows), 256, 0, s, logits, ld, V, slice, temperature, seed, position, pv, pi);
+    hb_launch(sample_final_kernel, rows, 32, 0, s, (const float*)pv, (const int*)pi, n, out);
+  }
   HB_CHECK_LAUNCH("hb_sample");
   return 0;
 }

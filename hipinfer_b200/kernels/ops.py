@@ -29,7 +29,7 @@ _SIGS = {
         "hb_rope_kv": [_p, _i, _l, _p, _p, _p, _p, _i, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p],
         "hb_attn_rows": [_p, _i, _p, _p, _i, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _i, _p],
         "hb_attn_merge": [_p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p, _p, _i, _p],
-        "hb_sample": [_p, _l, _i, _i, _p, _p, _p, _p, _p],
+        "hb_sample": [_p, _l, _i, _i, _p, _p, _p, _p, _p, _p],
         "hb_convert": [_p, _i, _p, _i, _l, _p],
     },
 }
@@ -231,8 +231,10 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], seed: Opti
         assert temperature.dtype == torch.float32 and temperature.numel() == R
         assert seed is not None and seed.dtype in (torch.int32, torch.uint32) and seed.numel() == R
         assert position is not None and position.dtype == torch.int32 and position.numel() == R
+    n = library.load("core").hb_sample_slices(V)
+    ws = torch.empty(2 * R * n, dtype=torch.int32, device=logits.device) if n > 1 else None
     _call("core", "hb_sample", logits.data_ptr(), logits.stride(0), R, V, _ptr(temperature), _ptr(seed),
-          _ptr(position), out.data_ptr(), _stream())
+          _ptr(position), out.data_ptr(), _ptr(ws), _stream())
     return out
 
 
