@@ -261,3 +261,54 @@ HB_EXPORT int hb_gemm_stream(const void* A, long lda, const void* W, long ldw, v
   HB_CHECK_LAUNCH("hb_gemm_stream");
   return 0;
 }
+
+// ---------------------------------------------------------------------------------------
+// hb_gemm_stream_static: the same product for callers that must not allocate (declared in
+// gemm_stream_static.h). The split-K partial sums and the per-block counters live in two
+// file-scope device arrays instead of a caller-provided workspace.
+// ---------------------------------------------------------------------------------------
+#include "gemm_stream_static.h"
+
+static __device__ __align__(256) float g_static_ws[HB_STATIC_WS_FLOATS];
+static __device__ __align__(256) int g_static_counters[HB_STATIC_COUNTERS];
+
+// The arrays' device addresses, looked up once per device. In host code the names above are
+// host-side stand-ins, not device addresses, so they are never passed to a kernel directly.
+static float* g_static_ws_ptr[HB_STATIC_MAX_DEVICES];
+static int* g_static_cnt_ptr[HB_STATIC_MAX_DEVICES];
+
+HB_EXPORT int hb_gemm_stream_static(const void* A, long lda, const void* W, long ldw, void* C, long ldc, int M, int N,
+                                    int K, int epi, int* status, cudaStream_t s) {
+  if (M <= 0 || N <= 0) return 0;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) HB_FAIL("hb_gemm_stream_static: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= HB_STATIC_MAX_DEVICES) HB_FAIL("hb_gemm_stream_static: device %d is beyond %d", dev, HB_STATIC_MAX_DEVICES);
+  if (!g_static_ws_ptr[dev]) {  // first call on this device (it is the current one): not inside a stream capture
+    void *pw = nullptr, *pc = nullptr;
+    e = cudaGetSymbolAddress(&pw, g_static_ws);
+    if (e != cudaSuccess) HB_FAIL("hb_gemm_stream_static: address of the scratch array: %s", cudaGetErrorString(e));
+    e = cudaGetSymbolAddress(&pc, g_static_counters);
+    if (e != cudaSuccess) HB_FAIL("hb_gemm_stream_static: address of the counter array: %s", cudaGetErrorString(e));
+    g_static_cnt_ptr[dev] = (int*)pc;
+    g_static_ws_ptr[dev] = (float*)pw;
+  }
+  if (M > 64) HB_FAIL("hb_gemm_stream_static: M = %d is beyond 64 rows", M);
+  if (K <= 0 || (K & 7)) HB_FAIL("hb_gemm_stream_static: K = %d must be a positive multiple of 8", K);
+  int kslice, ksplit, n_blocks;
+  long per_token;
+  hb_gemm_stream_plan(N, K, &kslice, &ksplit, &per_token, &n_blocks);
+  const int NT = M <= 16 ? 16 : M <= 32 ? 32 : 64;
+  if (per_token * NT > (long)HB_STATIC_WS_FLOATS)
+    HB_FAIL("hb_gemm_stream_static: M = %d, N = %d, K = %d need %ld floats of scratch; the static array holds %ld", M, N, K,
+            per_token * NT, (long)HB_STATIC_WS_FLOATS);
+  if (n_blocks > HB_STATIC_COUNTERS)
+    HB_FAIL("hb_gemm_stream_static: N = %d needs %d block counters; the static array holds %d", N, n_blocks, HB_STATIC_COUNTERS);
+  if (ksplit > 1) {
+    // every call shares the arrays and finds what the last one left: the counters this call uses must start at zero
+    e = cudaMemsetAsync(g_static_cnt_ptr[dev], 0, sizeof(int) * n_blocks, s);
+    if (e != cudaSuccess) HB_FAIL("hb_gemm_stream_static: clearing the counters: %s", cudaGetErrorString(e));
+  }
+  return hb_gemm_stream(A, lda, W, ldw, C, ldc, M, N, K, epi, g_static_ws_ptr[dev], (long)HB_STATIC_WS_FLOATS,
+                        g_static_cnt_ptr[dev], HB_STATIC_COUNTERS, status, s);
+}

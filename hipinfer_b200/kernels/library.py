@@ -32,7 +32,7 @@ LIBRARIES: Dict[str, List[str]] = {
     "core": ["core.cu"],
     "fast": ["fast_entry.cu", "gemm_tc.cu", "gemm_skinny.cu", "gemm_stream.cu", "attention_fast.cu", "attention_prefill.cu"],
 }
-HEADERS = ["common.cuh", "tc_common.cuh"]
+HEADERS = ["common.cuh", "tc_common.cuh", "gemm_stream_static.h"]
 
 
 class KernelLibraryError(RuntimeError):
