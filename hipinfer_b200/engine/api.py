@@ -117,17 +117,21 @@ class Engine:
     def _run_tokens(self, slot: int, tokens: Sequence[int], p0: int, all_logits: bool):
         self._slot_ok(slot)
         rid = ("slot", slot)
-        st = self._slots.get(slot)
-        if p0 == 0 and st is not None:
-            self.runner.end(rid)
-            st = None
-        if st is None:
-            st = self._slots[slot] = dict(tokens=[])
-        if p0 != len(st["tokens"]):
-            raise ValueError(f"slot {slot} holds {len(st['tokens'])} tokens; cannot continue at p0={p0}")
         tokens = [int(t) for t in tokens]
         if not tokens:
             raise ValueError("prefill needs at least one token")
+        if p0 < 0 or p0 + len(tokens) > self.max_seq:
+            raise ValueError(f"positions [{p0}, {p0 + len(tokens)}) exceed the longest sequence {self.max_seq}")
+        if any(not (0 <= t < self.vocab) for t in tokens):
+            raise ValueError(f"a token is outside the vocabulary of {self.vocab}")
+        st = self._slots.get(slot)
+        held = len(st["tokens"]) if st else 0
+        if p0 != 0 and p0 != held:
+            raise ValueError(f"slot {slot} holds {held} tokens; cannot continue at p0={p0}")
+        if p0 == 0:                                   # a fresh start of the slot
+            if self.runner.cache.has_request(rid):
+                self.runner.end(rid)
+            st = self._slots[slot] = dict(tokens=[])
         rows = []
         try:
             for t0 in range(0, len(tokens), self.max_prefill):

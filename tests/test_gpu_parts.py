@@ -1,0 +1,309 @@
+"""Each part alone beside the plain implementation, and the generality of the assembly: toy
+parts and a toy architecture that are defined HERE and registered through the public
+registries, without a change to the framework's files: a mixer with state of its own, a window
+of keys, a layer that runs twice, a layer that reads another layer's cache."""
+import math
+from dataclasses import dataclass
+
+import pytest
+import torch
+
+import plain_llama as plain
+import tiny
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DT = [torch.float32, torch.bfloat16]
+
+
+def ctx_for(dtype, page_size=16, max_len=256):
+    from hipinfer_b200.parts import BuildContext
+
+    return BuildContext(dtype, torch.device(DEV), page_size, max_len)
+
+
+def rnd(*shape, seed=0, scale=1.0, dtype=torch.float32):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype)
+
+
+class FakeBatch:
+    """What a part sees of a step, for one request of n tokens starting at position ctx."""
+
+    def __init__(self, n, ctx, block_table, page_size):
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+        pos = list(range(ctx, ctx + n))
+        self.n_rows, self.n_requests, self.n_want = n, 1, 0
+        self.positions, self.row_request = i32(pos), i32([0] * n)
+        self.req_q_start, self.req_q_len, self.req_ctx_len, self.req_state_slot = i32([0]), i32([n]), i32([ctx]), i32([0])
+        self.block_tables = [i32([block_table])]
+        self.slot_maps = [i32([block_table[p // page_size] * page_size + p % page_size for p in pos])]
+        self.h_q_start, self.h_q_len, self.h_ctx_len, self.h_state_slot = [0], [n], [ctx], [0]
+        self.max_pos, self.max_q_len = ctx + n - 1, n
+
+
+@pytest.mark.parametrize("dtype", DT)
+def test_rmsnorm_part(dtype):
+    from hipinfer_b200.parts import PartSpec, build_part
+
+    part = build_part("norm", PartSpec("rmsnorm", dict(name="n.weight", size=200, eps=1e-3)), ctx_for(dtype), "p.")
+    assert [(s.name, s.shape, s.init) for s in part.param_specs()] == [("p.n.weight", (200,), "ones")]
+    w = 1 + rnd(200, seed=1) * 0.1
+    part.load({"p.n.weight": w.to(torch.bfloat16).to(DEV)})
+    x = rnd(9, 200, seed=2, scale=2.0).to(DEV)
+    ref = plain.rmsnorm(x.cpu(), w.to(torch.bfloat16).float(), 1e-3)
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    torch.testing.assert_close(part.forward(x).float().cpu(), ref, rtol=tol, atol=tol)
+
+
+@pytest.mark.parametrize("dtype", DT)
+def test_swiglu_part(dtype):
+    from hipinfer_b200.parts import PartSpec, build_part
+
+    H, I, T = 72, 176, 21
+    part = build_part("feed_forward", PartSpec("swiglu", dict(hidden_size=H, intermediate_size=I)), ctx_for(dtype), "l.")
+    assert sorted(s.name for s in part.param_specs()) == ["l.mlp.down_proj.weight", "l.mlp.gate_proj.weight", "l.mlp.up_proj.weight"]
+    wt = {n: rnd(*shape, seed=i, scale=0.1, dtype=torch.bfloat16) for i, (n, shape) in enumerate(
+        [("l.mlp.gate_proj.weight", (I, H)), ("l.mlp.up_proj.weight", (I, H)), ("l.mlp.down_proj.weight", (H, I))])}
+    part.load({k: v.to(DEV) for k, v in wt.items()})
+    xn = rnd(T, H, seed=5).to(dtype)
+    x = rnd(T, H, seed=6)
+    want = x + plain.swiglu_mlp(xn.float(), *(wt[f"l.mlp.{k}_proj.weight"].float() for k in ("gate", "up", "down")))
+    xd = x.to(DEV)
+    part.forward(xn.to(DEV), xd, None)
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    torch.testing.assert_close(xd.cpu(), want, rtol=tol, atol=tol)
+    with pytest.raises(ValueError, match="multiple of 16"):
+        build_part("feed_forward", PartSpec("swiglu", dict(hidden_size=H, intermediate_size=100)), ctx_for(dtype), "l.")
+
+
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("Hq,Hkv,D,window,scaling", [(4, 2, 16, 0, None), (6, 2, 64, 0, "llama3"), (3, 1, 32, 24, None)])
+def test_attention_mixer_alone(dtype, Hq, Hkv, D, window, scaling):
+    """The attention part on a cache it fills itself: 50 tokens whole, against 37 then 13."""
+    from hipinfer_b200.cache import CacheGroupSpec, CacheStorage
+    from hipinfer_b200.models.decoder import StepCachePlan
+    from hipinfer_b200.parts import PartSpec, build_part
+
+    H, ps, n = 80, 16, 50
+    sc = dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
+              original_max_position_embeddings=32) if scaling else None
+    pos_spec = PartSpec("rope", dict(head_dim=D, theta=10000.0, scaling=sc))
+    ctx = ctx_for(dtype, ps, 128)
+    part = build_part("mixer", PartSpec("attention", dict(hidden_size=H, n_heads=Hq, n_kv_heads=Hkv, head_dim=D,
+                                                          window=window, position=pos_spec)), ctx, "l.")
+    need = part.cache_need()
+    assert (need.kind, need.kv_heads, need.head_dim, need.window) == ("window" if window else "full", Hkv, D, window)
+    names = {k: f"l.self_attn.{k}_proj.weight" for k in "qkvo"}
+    shapes = {"q": (Hq * D, H), "k": (Hkv * D, H), "v": (Hkv * D, H), "o": (H, Hq * D)}
+    wt = {names[k]: rnd(*shapes[k], seed=i, scale=0.15, dtype=torch.bfloat16) for i, k in enumerate("qkvo")}
+    part.load({k: v.to(DEV) for k, v in wt.items()})
+    xn = rnd(n, H, seed=9).to(dtype)
+    x0 = rnd(n, H, seed=10)
+    inv = plain.rope_inv_freq(D, 10000.0, sc)
+    want = x0 + plain.attention_block(xn.float(), *(wt[names[k]].float() for k in "qkvo"), list(range(n)), Hq, Hkv, D, inv,
+                                      window or None)
+    table = [5, 2, 7, 0]                                     # pages in no particular order
+    # the error is measured against the size of what the mixer adds: 32-bit rounding, or a few roundings to
+    # 8 bits of mantissa (q, k, v, the probabilities and the attention output)
+    scale = float((want - x0).abs().max())
+    tol = (2e-5 if dtype == torch.float32 else 2e-2) * scale
+    for cuts in ([n], [37, 13]):
+        storage = CacheStorage([CacheGroupSpec("g", need.kind, 1, Hkv, D, window)], [8], ps, dtype, DEV, {}, 1)
+        cache = storage.layer_cache(StepCachePlan(0, 0, True))
+        x = x0.clone().to(DEV)
+        done = 0
+        for c in cuts:
+            part.forward(xn[done:done + c].to(DEV), x[done:done + c], FakeBatch(c, done, table, ps), cache, {})
+            done += c
+        err = float((x.cpu() - want).abs().max())
+        assert err <= tol, f"cuts {cuts}: max |diff| {err:.3e} > {tol:.3e} (scale {scale:.3e})"
+
+
+@pytest.mark.parametrize("dtype", DT)
+def test_embedding_and_head_parts(dtype):
+    from hipinfer_b200.parts import PartSpec, build_part
+
+    V, H = 301, 72
+    emb = build_part("embedding", PartSpec("token", dict(name="e.weight", vocab_size=V, hidden_size=H)), ctx_for(dtype))
+    tied = build_part("head", PartSpec("linear", dict(tied_to="e.weight", vocab_size=V, hidden_size=H)), ctx_for(dtype))
+    own = build_part("head", PartSpec("linear", dict(name="h.weight", vocab_size=V, hidden_size=H)), ctx_for(dtype))
+    assert tied.param_specs() == [] and [s.name for s in own.param_specs()] == ["h.weight"]
+    e, h = rnd(V, H, seed=1, dtype=torch.bfloat16), rnd(V, H, seed=2, dtype=torch.bfloat16)
+    tensors = {"e.weight": e.to(DEV), "h.weight": h.to(DEV)}
+    for p in (emb, tied, own):
+        p.load(tensors)
+    tok = torch.tensor([0, 300, 17], dtype=torch.int32, device=DEV)
+    assert torch.equal(emb.forward(tok).cpu(), e.float()[[0, 300, 17]])
+    xn = rnd(3, H, seed=3).to(dtype)
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    torch.testing.assert_close(tied.forward(xn.to(DEV)).cpu(), xn.float() @ e.float().T, rtol=tol, atol=tol)
+    torch.testing.assert_close(own.forward(xn.to(DEV)).cpu(), xn.float() @ h.float().T, rtol=tol, atol=tol)
+
+
+# ------------------------------------------------------------------------------------------
+# A toy architecture, defined and registered here: nothing in the framework's files knows it.
+#   layer 0: attention (all keys) + SwiGLU          layer 1: DecayMixer (state of its own) + SwiGLU
+#   layer 2: attention with a window + SwiGLU
+#   order:   0, 1, 2, 1 again (its own state), 0 again reading the cache the first step wrote
+# ------------------------------------------------------------------------------------------
+def _register_toy():
+    from hipinfer_b200.config import ModelConfig, register_architecture, take
+    from hipinfer_b200.parts import LayerSpec, Mixer, ModelSpec, PartSpec, RunStep, register_part
+    from hipinfer_b200.weights import ParamSpec
+
+    class DecayMixer(Mixer):
+        """h_t = a h_{t-1} + xn_t per request, carried from step to step in the request's state
+        slot; the mixer's output is h_t W^T. It keeps no keys or values."""
+
+        def __init__(self, params, ctx, prefix=""):
+            super().__init__(params, ctx, prefix)
+            self.hidden, self.a, self.name = params["hidden_size"], params["decay"], prefix + "decay.weight"
+
+        def param_specs(self):
+            return [ParamSpec(self.name, (self.hidden, self.hidden))]
+
+        def load(self, tensors):
+            self.w = tensors[self.name].float()
+
+        def state_need(self):
+            return {"h": ((self.hidden,), torch.float32)}
+
+        def forward(self, xn, x, batch, cache, state):
+            assert cache is None
+            for r in range(batch.n_requests):
+                s, n, slot = batch.h_q_start[r], batch.h_q_len[r], batch.h_state_slot[r]
+                h = state["h"][slot].clone()
+                for i in range(n):
+                    h = self.a * h + xn[s + i].float()
+                    x[s + i] += h @ self.w.T
+                state["h"][slot] = h
+
+    @dataclass(frozen=True)
+    class ToyConfig(ModelConfig):
+        vocab_size: int
+        hidden_size: int
+        n_heads: int
+        n_kv_heads: int
+        head_dim: int
+        intermediate_size: int
+        window: int
+        decay: float
+        eps: float
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(d["architectures"][0], *(take(d, k, int) for k in ("vocab_size", "hidden_size", "n_heads",
+                       "n_kv_heads", "head_dim", "intermediate_size", "window")), take(d, "decay", float), take(d, "eps", float))
+
+        def to_dict(self):
+            return dict(architectures=[self.architecture], **{k: getattr(self, k) for k in (
+                "vocab_size", "hidden_size", "n_heads", "n_kv_heads", "head_dim", "intermediate_size", "window", "decay", "eps")})
+
+    def toy_spec(c):
+        H = c.hidden_size
+        norm = lambda name: PartSpec("rmsnorm", dict(name=name, size=H, eps=c.eps))
+        ffn = PartSpec("swiglu", dict(hidden_size=H, intermediate_size=c.intermediate_size))
+        pos = PartSpec("rope", dict(head_dim=c.head_dim, theta=10000.0, scaling=None))
+        att = lambda window: PartSpec("attention", dict(hidden_size=H, n_heads=c.n_heads, n_kv_heads=c.n_kv_heads,
+                                                        head_dim=c.head_dim, window=window, position=pos))
+        mixers = [att(0), PartSpec("toy_decay", dict(hidden_size=H, decay=c.decay)), att(c.window)]
+        layers = tuple(LayerSpec(f"toy.layers.{i}.", "pre_norm", m, norm("input_layernorm.weight"), ffn,
+                                 norm("post_attention_layernorm.weight")) for i, m in enumerate(mixers))
+        order = (RunStep(0), RunStep(1), RunStep(2), RunStep(1), RunStep(0, reads_cache_of=0))
+        return ModelSpec(c.architecture, H, c.vocab_size, 256,
+                         PartSpec("token", dict(name="toy.embed.weight", vocab_size=c.vocab_size, hidden_size=H)), layers, order,
+                         norm("toy.norm.weight"), PartSpec("linear", dict(tied_to="toy.embed.weight", vocab_size=c.vocab_size,
+                                                                         hidden_size=H)))
+
+    register_part("mixer", "toy_decay", DecayMixer)
+    register_architecture("ToyForCausalLM", ToyConfig, toy_spec)
+
+
+TOY = dict(architectures=["ToyForCausalLM"], vocab_size=200, hidden_size=64, n_heads=4, n_kv_heads=2, head_dim=32,
+           intermediate_size=96, window=40, decay=0.5, eps=1e-5)
+
+
+def toy_plain(c, w, tokens):
+    """The toy model on a whole sequence with the plain implementation's parts."""
+    T, H, Hq, Hkv, D = len(tokens), c["hidden_size"], c["n_heads"], c["n_kv_heads"], c["head_dim"]
+    pos = list(range(T))
+    inv = plain.rope_inv_freq(D, 10000.0)
+    x = plain.embed(tokens, w["toy.embed.weight"])
+
+    def norms(i):
+        p = f"toy.layers.{i}."
+        return w[p + "input_layernorm.weight"], w[p + "post_attention_layernorm.weight"]
+
+    def mlp(i, x):
+        p = f"toy.layers.{i}.mlp."
+        return x + plain.swiglu_mlp(plain.rmsnorm(x, norms(i)[1], c["eps"]), w[p + "gate_proj.weight"], w[p + "up_proj.weight"],
+                                    w[p + "down_proj.weight"])
+
+    def qkvo(i):
+        return [w[f"toy.layers.{i}.self_attn.{k}_proj.weight"] for k in "qkvo"]
+
+    def decay(x):
+        xn, h, out = plain.rmsnorm(x, norms(1)[0], c["eps"]), torch.zeros(H), []
+        for t in range(T):
+            h = c["decay"] * h + xn[t]
+            out.append(h @ w["toy.layers.1.decay.weight"].T)
+        return mlp(1, x + torch.stack(out))
+
+    xn0 = plain.rmsnorm(x, norms(0)[0], c["eps"])
+    x = mlp(0, x + plain.attention_block(xn0, *qkvo(0), pos, Hq, Hkv, D, inv))
+    x = decay(x)
+    x = mlp(2, x + plain.attention_block(plain.rmsnorm(x, norms(2)[0], c["eps"]), *qkvo(2), pos, Hq, Hkv, D, inv, c["window"]))
+    x = decay(x)
+    # layer 0 again: queries from here, keys and values as the first step stored them
+    wq, wk, wv, wo = qkvo(0)
+    cos, sin = plain.rope_cos_sin(pos, inv)
+    k0 = plain.apply_rope((xn0 @ wk.T).reshape(T, Hkv, D), cos, sin)
+    v0 = (xn0 @ wv.T).reshape(T, Hkv, D)
+    q = plain.apply_rope((plain.rmsnorm(x, norms(0)[0], c["eps"]) @ wq.T).reshape(T, Hq, D), cos, sin)
+    x = mlp(0, x + plain.attention_scores_softmax_values(q, k0, v0, pos, pos).reshape(T, Hq * D) @ wo.T)
+    return plain.lm_head(x, w["toy.norm.weight"], w["toy.embed.weight"], c["eps"])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_architecture_registered_from_the_test(dtype):
+    from hipinfer_b200.config import config_from_dict, get_architecture
+    from hipinfer_b200.engine import ModelRunner
+    from hipinfer_b200.parts import spec_param_specs
+    from hipinfer_b200.weights import random_weights
+
+    _register_toy()
+    cfg = config_from_dict(TOY)
+    spec = get_architecture("ToyForCausalLM").build_spec(cfg)
+    tensors = random_weights(spec_param_specs(spec), seed=9, std=0.08, norm_std=0.1, dtype=torch.bfloat16)
+    assert "toy.layers.1.decay.weight" in tensors and "toy.layers.1.self_attn.q_proj.weight" not in tensors
+    runner = ModelRunner(cfg, {k: v.to(DEV) for k, v in tensors.items()}, dtype=dtype, num_pages=40, max_model_len=256,
+                         max_num_seqs=4, cuda_graphs=False)   # the toy mixer reads host mirrors of the batch
+    m = runner.model
+    assert [(g.kind, g.n_layers, g.window) for g in m.cache_groups] == [("full", 1, 0), ("window", 1, 40)]
+    assert [p and (p.group, p.slot, p.write) for p in m.cache_plan] == [(0, 0, True), None, (1, 0, True), None, (0, 0, False)]
+    assert sorted(m.state_specs) == [(1, "h"), (3, "h")]                       # the layer that runs twice has two states
+    w = {k: v.float() for k, v in tensors.items()}
+    requests = {f"t{i}": tiny.random_tokens(n, 200, 60 + i) for i, n in enumerate([150, 33, 90, 64, 7, 120])}
+    ref = {rid: toy_plain(TOY, w, toks) for rid, toks in requests.items()}
+    st = tiny.RunnerStepper(runner)
+    for name, plan in (("whole", tiny.plan_whole(requests)), ("portions", tiny.plan_portions(requests)),
+                       ("mixed", tiny.plan_mixed(requests, 3))):
+        got = tiny.run_plan(st, requests, plan)
+        for rid in requests:
+            tiny.assert_logits_close(got[rid], ref[rid], dtype, f"toy {name} {rid}")
+        runner.cache.check()
+        assert runner.cache.free_pages() == [40, 40] and runner.cache.slots.free_count == 4
+    # the window group gives pages back while a long request is still running; the full group does not
+    from hipinfer_b200.engine import StepEntry
+    runner.step([StepEntry("long", requests["t0"], [])])
+    held = [sum(1 for p in t if p >= 0) for t in runner.cache.get("long").tables]
+    assert held == [10, 4]            # 150 tokens fill 10 pages; keys 111..149 are still visible: pages 6..9
+    runner.end("long")
+
+
+def test_unknown_part_kind_is_named():
+    from hipinfer_b200.parts import BuildContext, PartSpec, build_part
+
+    with pytest.raises(KeyError, match="no mixer of kind 'nope'"):
+        build_part("mixer", PartSpec("nope", {}), BuildContext.meta())
