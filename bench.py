@@ -92,7 +92,7 @@ def build_engine(layers: int, max_batch: int, total_steps: int):
     from hipinfer_b200 import Engine
 
     cfg = dict(MODEL, num_hidden_layers=layers)
-    pages_per_seq = -(-(PROMPT_LEN + total_steps + 2 * PAGE) // PAGE)
+    pages_per_seq = -(-(PROMPT_LEN + total_steps + 2 * max_batch + 4 * PAGE) // PAGE)
     return Engine(config=cfg, random_weights=0, std=0.02, dtype="bfloat16", max_batch=max_batch, max_seq=CONTEXT_LEN,
                   max_prefill=PREFILL_TOKENS, page_size=PAGE, num_pages=max_batch * pages_per_seq + 8)
 
@@ -158,8 +158,10 @@ def decode_e2e(eng, batch: int, steps: int, warmup: int):
     memory every step, sampled tokens read back every step. Wall clock around synchronised ends."""
     import torch
 
+    # requests that finish their prompt early decode while the others are still being prefilled
+    # (at most 2 * batch steps): leave enough tokens that nobody finishes inside the timed steps
     for p in prompts(batch, 2):
-        eng.add_request(p, warmup + steps + 1)
+        eng.add_request(p, warmup + steps + 2 * batch + 8)
     while any(not r.decoding for r in eng.scheduler.running) or eng.scheduler.waiting:
         eng.step()
     for _ in range(warmup):
@@ -170,7 +172,10 @@ def decode_e2e(eng, batch: int, steps: int, warmup: int):
         eng.step()
     torch.cuda.synchronize()
     dt = time.perf_counter() - t0
-    eng.run()
+    assert len(eng.scheduler.running) == batch, "a request finished inside the timed steps"
+    for r in list(eng.scheduler.running):          # the measurement is over: drop the requests
+        eng.scheduler.running.remove(r)
+        eng.runner.end(r.request_id)
     groups = len(eng.runner.cache.groups)
     width = -(-CONTEXT_LEN // PAGE)
     n_int = 3 * batch + 4 * batch + batch + groups * batch * width + groups * batch

@@ -11,17 +11,28 @@
 
 constexpr int AD_THREADS = 128;
 
+// Byte offset of 16-byte chunk c of key row `row` in a [keys][D] bf16 tile, swizzled so that both
+// a thread-per-row walk and a lanes-across-a-row walk are free of bank conflicts.
+template <int D> __device__ __forceinline__ uint32_t ad_swz(int row, int c) {
+  constexpr int CH = D / 8;
+  return (uint32_t)(row * (D * 2) + ((c ^ (CH == 4 ? ((row >> 1) & 3) : (row & 7))) << 4));
+}
+
 template <int D, int G>
 __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc,
     const int* __restrict__ bt, int bt_stride, const int* __restrict__ row_req, const int* __restrict__ pos,
     __nv_bfloat16* __restrict__ out, float* __restrict__ part_acc, float* __restrict__ part_ml, int Hq, int Hkv,
     int page_size, int window, float scale, int chunk, int S, const int* __restrict__ q_len, int row_limit) {
-  extern __shared__ float smem[];
-  float* qs = smem;                 // [G][D], scaled
-  float* sc = qs + G * D;           // [G][chunk]
-  float* ml = sc + G * chunk;       // [G][2]
-  float* red = ml + 2 * G;          // [4 warps][G][D]
+  constexpr int CH = D / 8;
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  // the whole key chunk and the whole value chunk are requested at once (cp.async), so a block
+  // has up to 2 * chunk * D * 2 bytes in flight; scores and sums follow
+  const uint32_t sK = hb_smem_u32(smem_raw), sV = sK + chunk * D * 2;
+  float* qs = (float*)(smem_raw + 2 * chunk * D * 2);  // [G][D], scaled
+  float* sc = qs + G * D;                              // [G][chunk]
+  float* ml = sc + G * chunk;                          // [G][2]
+  float* red = ml + 2 * G;                             // [4 warps][G][D]
   hb_pdl_launch();
   hb_pdl_wait();
   const int t = blockIdx.z, h = blockIdx.y, s = blockIdx.x;
@@ -32,22 +43,33 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
   if (s < s_lo || s > s_hi) return;
   const int k0 = max(s * chunk, lo), k1 = min((s + 1) * chunk, p + 1), nk = k1 - k0;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int* table = bt + (size_t)row_req[t] * bt_stride;
+  for (int i = tid; i < nk * CH; i += AD_THREADS) {
+    const int r = i / CH, c = i - r * CH, kp = k0 + r;
+    const size_t page = table[kp / page_size];
+    hb_cp_async16(sK + ad_swz<D>(r, c), kc + ((page * Hkv + h) * page_size + kp % page_size) * D + c * 8);
+  }
+  hb_cp_async_commit();
+  for (int i = tid; i < nk * CH; i += AD_THREADS) {
+    const int r = i / CH, c = i - r * CH, kp = k0 + r;
+    const size_t page = table[kp / page_size];
+    hb_cp_async16(sV + ad_swz<D>(r, c), vc + ((page * Hkv + h) * page_size + kp % page_size) * D + c * 8);
+  }
+  hb_cp_async_commit();
   const __nv_bfloat16* qrow = q + ((size_t)t * Hq + (size_t)h * G) * D;
   for (int i = tid; i < G * D; i += AD_THREADS) qs[i] = __bfloat162float(qrow[i]) * scale;
+  hb_cp_async_wait<1>();
   __syncthreads();
-  const int* table = bt + (size_t)row_req[t] * bt_stride;
 
   // scores: one key per thread, all G heads from one pass over the key's D elements
   for (int j = tid; j < nk; j += AD_THREADS) {
-    const int kp = k0 + j;
-    const size_t page = table[kp / page_size];
-    const uint4* kr = (const uint4*)(kc + ((page * Hkv + h) * page_size + kp % page_size) * D);
     float a[G];
 #pragma unroll
     for (int g = 0; g < G; g++) a[g] = 0.f;
 #pragma unroll
-    for (int i = 0; i < D / 8; i++) {
-      const uint4 kv = kr[i];
+    for (int i = 0; i < CH; i++) {
+      uint4 kv;
+      asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(kv.x), "=r"(kv.y), "=r"(kv.z), "=r"(kv.w) : "r"(sK + ad_swz<D>(j, i)));
       const __nv_bfloat162* k2 = (const __nv_bfloat162*)&kv;
       float kf[8];
 #pragma unroll
@@ -82,10 +104,11 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
     l = hb_warp_sum(l);
     if (lane == 0) { ml[2 * g] = m; ml[2 * g + 1] = l; }
   }
+  hb_cp_async_wait<0>();
   __syncthreads();
 
-  // values: D/8 lanes share a key's row with 16-byte loads, so a warp takes 32 / (D/8) keys per pass
-  // and each value is read once for all G heads; lanes, then warps, are summed in a fixed order
+  // values: D/8 lanes share a key's row, so a warp takes 32 / (D/8) keys per pass and each value
+  // is read once for all G heads; lanes, then warps, are summed in a fixed order
   constexpr int TPK = D / 8, KPW = 32 / TPK;
   const int kq = lane / TPK, dc = lane % TPK;
   float acc[G][8];
@@ -95,9 +118,8 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
     for (int e = 0; e < 8; e++) acc[g][e] = 0.f;
 #pragma unroll 4
   for (int j = warp * KPW + kq; j < nk; j += 4 * KPW) {
-    const int kp = k0 + j;
-    const size_t page = table[kp / page_size];
-    const uint4 raw = *(const uint4*)(vc + ((page * Hkv + h) * page_size + kp % page_size) * D + dc * 8);
+    uint4 raw;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(raw.x), "=r"(raw.y), "=r"(raw.z), "=r"(raw.w) : "r"(sV + ad_swz<D>(j, dc)));
     const __nv_bfloat162* v2 = (const __nv_bfloat162*)&raw;
     float vf[8];
 #pragma unroll
@@ -145,6 +167,13 @@ static int launch_decode(int G, dim3 grid, size_t smem, cudaStream_t st, const _
                          int chunk, int S, const int* q_len, int row_limit) {
 #define HB_AD_CASE(GG)                                                                                              \
   case GG:                                                                                                          \
+    {                                                                                                               \
+      static bool configured = false;                                                                               \
+      if (!configured) {                                                                                            \
+        cudaFuncSetAttribute(attn_decode_kernel<D, GG>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);   \
+        configured = true;                                                                                          \
+      }                                                                                                             \
+    }                                                                                                               \
     hb_launch(attn_decode_kernel<D, GG>, grid, AD_THREADS, smem, st, q, kc, vc, bt, bt_stride, row_req, pos, out, pa, pm, \
               Hq, Hkv, page_size, window, scale, chunk, S, q_len, row_limit);                                        \
     return 0;
@@ -174,8 +203,8 @@ HB_EXPORT int hb_attn_decode(const void* q, const void* kc, const void* vc, cons
   if (T > 65535 || Hkv > 65535) HB_FAIL("hb_attn_decode: %d rows / %d kv heads are beyond the grid limit", T, Hkv);
   const int G = Hq / Hkv, S = max_pos / chunk + 1;
   if (S > 1 && !workspace) HB_FAIL("hb_attn_decode: rows that span %d chunks need a workspace", S);
-  const size_t smem = ((size_t)G * D + (size_t)G * chunk + 2 * G + 4 * (size_t)G * D) * sizeof(float);
-  if (smem > 48 * 1024) HB_FAIL("hb_attn_decode: %zu bytes of shared memory", smem);
+  const size_t smem = 2 * (size_t)chunk * D * 2 + ((size_t)G * D + (size_t)G * chunk + 2 * G + 4 * (size_t)G * D) * sizeof(float);
+  if (smem > 200 * 1024) HB_FAIL("hb_attn_decode: %zu bytes of shared memory (chunk %d, head_dim %d)", smem, chunk, D);
   float* pa = workspace;
   float* pm = workspace ? workspace + (size_t)T * Hq * S * D : nullptr;
   dim3 grid(S, Hkv, T);
