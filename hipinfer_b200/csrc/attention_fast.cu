@@ -2,37 +2,39 @@
 //
 // attn_decode_kernel: rows with few queries (decode tokens, short portions). One block per
 // (key chunk, kv head, row); the G query heads of the kv head share one pass over its keys and
-// values (src/kernels.cuh:1501-1508 does the same on a contiguous cache), 16-byte loads, each
-// key read once for all G heads, each value read once for all G heads. Keys are cut into chunks
-// of ABSOLUTE positions, so the split of a row depends on its position alone. Scores, softmax
-// and the value sums are fp32; partial (acc, max, sum) of rows that span several chunks go to a
-// workspace and are merged in ascending chunk order by attn_merge_kernel of the core library.
+// values. Keys are cut into chunks of ABSOLUTE positions, so the split of a row depends on its
+// position alone. Softmax and the value sums are fp32; partial (acc, max, sum) of rows that span
+// several chunks go to a workspace and are merged in ascending chunk order by attn_merge_kernel
+// of the core library.
 #include "tc_common.cuh"
 
-constexpr int AD_THREADS = 128;
+#ifndef HB_AD_THREADS
+#define HB_AD_THREADS 128
+#endif
+constexpr int AD_THREADS = HB_AD_THREADS, AD_WARPS = AD_THREADS / 32;
 
-// Byte offset of 16-byte chunk c of key row `row` in a [keys][D] bf16 tile, swizzled so that both
-// a thread-per-row walk and a lanes-across-a-row walk are free of bank conflicts.
+// Byte offset of 16-byte chunk c of key row `row` in a [keys][D] bf16 tile (D = 64 or 128): the
+// swizzle that makes ldmatrix of eight consecutive rows free of bank conflicts.
 template <int D> __device__ __forceinline__ uint32_t ad_swz(int row, int c) {
-  constexpr int CH = D / 8;
-  return (uint32_t)(row * (D * 2) + ((c ^ (CH == 4 ? ((row >> 1) & 3) : (row & 7))) << 4));
+  return (uint32_t)(row * (D * 2) + ((c ^ (row & 7)) << 4));
 }
 
+// One block = one (key chunk, kv head, row). The chunk's keys and values are requested at once
+// with cp.async into swizzled shared memory; each warp then takes 64 keys: S = Q K^T and
+// O = P V on warp MMAs with the G query heads of the kv head as the rows of the 16-row tile
+// (src/kernels.cuh:1681-1869 does the same on a contiguous cache), softmax in fp32 in the exp2
+// domain, P rounded to bf16 before P V. The warps' (max, sum, O) are combined in warp order.
 template <int D, int G>
 __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc,
     const int* __restrict__ bt, int bt_stride, const int* __restrict__ row_req, const int* __restrict__ pos,
     __nv_bfloat16* __restrict__ out, float* __restrict__ part_acc, float* __restrict__ part_ml, int Hq, int Hkv,
-    int page_size, int window, float scale, int chunk, int S, const int* __restrict__ q_len, int row_limit) {
-  constexpr int CH = D / 8;
+    int page_size, int window, float scale_log2, int chunk, int S, const int* __restrict__ q_len, int row_limit) {
+  constexpr int CH = D / 8, KS = D / 16, NT_O = D / 8, WK = 64;  // WK: keys per warp pass
   extern __shared__ __align__(128) uint8_t smem_raw[];
-  // the whole key chunk and the whole value chunk are requested at once (cp.async), so a block
-  // has up to 2 * chunk * D * 2 bytes in flight; scores and sums follow
-  const uint32_t sK = hb_smem_u32(smem_raw), sV = sK + chunk * D * 2;
-  float* qs = (float*)(smem_raw + 2 * chunk * D * 2);  // [G][D], scaled
-  float* sc = qs + G * D;                              // [G][chunk]
-  float* ml = sc + G * chunk;                          // [G][2]
-  float* red = ml + 2 * G;                             // [4 warps][G][D]
+  const uint32_t sK = hb_smem_u32(smem_raw), sV = sK + chunk * D * 2, sQ = sV + chunk * D * 2;
+  float* red_o = (float*)(smem_raw + 2 * chunk * D * 2 + 16 * D * 2);  // [warps][G][D]
+  float* red_ml = red_o + AD_WARPS * G * D;                             // [warps][G][2]
   hb_pdl_launch();
   hb_pdl_wait();
   const int t = blockIdx.z, h = blockIdx.y, s = blockIdx.x;
@@ -42,121 +44,135 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
   const int s_lo = lo / chunk, s_hi = p / chunk;
   if (s < s_lo || s > s_hi) return;
   const int k0 = max(s * chunk, lo), k1 = min((s + 1) * chunk, p + 1), nk = k1 - k0;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, tq = lane & 3;
   const int* table = bt + (size_t)row_req[t] * bt_stride;
-  for (int i = tid; i < nk * CH; i += AD_THREADS) {
+  const int rows_pad = (nk + WK - 1) / WK * WK;  // rows the warps will touch; the tail is zeroed
+  for (int i = tid; i < rows_pad * CH; i += AD_THREADS) {
     const int r = i / CH, c = i - r * CH, kp = k0 + r;
-    const size_t page = table[kp / page_size];
-    hb_cp_async16(sK + ad_swz<D>(r, c), kc + ((page * Hkv + h) * page_size + kp % page_size) * D + c * 8);
+    const uint32_t off = ad_swz<D>(r, c);
+    if (r < nk) {
+      const size_t page = table[kp / page_size];
+      const size_t src = ((page * Hkv + h) * page_size + kp % page_size) * D + c * 8;
+      hb_cp_async16(sK + off, kc + src);
+      hb_cp_async16(sV + off, vc + src);
+    } else {
+      asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(sK + off), "r"(0u) : "memory");
+      asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(sV + off), "r"(0u) : "memory");
+    }
   }
   hb_cp_async_commit();
-  for (int i = tid; i < nk * CH; i += AD_THREADS) {
-    const int r = i / CH, c = i - r * CH, kp = k0 + r;
-    const size_t page = table[kp / page_size];
-    hb_cp_async16(sV + ad_swz<D>(r, c), vc + ((page * Hkv + h) * page_size + kp % page_size) * D + c * 8);
-  }
-  hb_cp_async_commit();
-  const __nv_bfloat16* qrow = q + ((size_t)t * Hq + (size_t)h * G) * D;
-  for (int i = tid; i < G * D; i += AD_THREADS) qs[i] = __bfloat162float(qrow[i]) * scale;
-  hb_cp_async_wait<1>();
-  __syncthreads();
-
-  // scores: one key per thread, all G heads from one pass over the key's D elements
-  for (int j = tid; j < nk; j += AD_THREADS) {
-    float a[G];
-#pragma unroll
-    for (int g = 0; g < G; g++) a[g] = 0.f;
-#pragma unroll
-    for (int i = 0; i < CH; i++) {
-      uint4 kv;
-      asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(kv.x), "=r"(kv.y), "=r"(kv.z), "=r"(kv.w) : "r"(sK + ad_swz<D>(j, i)));
-      const __nv_bfloat162* k2 = (const __nv_bfloat162*)&kv;
-      float kf[8];
-#pragma unroll
-      for (int e = 0; e < 4; e++) {
-        const float2 f = __bfloat1622float2(k2[e]);
-        kf[2 * e] = f.x;
-        kf[2 * e + 1] = f.y;
-      }
-#pragma unroll
-      for (int g = 0; g < G; g++) {
-        const float4 q0 = *(const float4*)(qs + g * D + i * 8), q1 = *(const float4*)(qs + g * D + i * 8 + 4);
-        a[g] = fmaf(q0.x, kf[0], a[g]); a[g] = fmaf(q0.y, kf[1], a[g]);
-        a[g] = fmaf(q0.z, kf[2], a[g]); a[g] = fmaf(q0.w, kf[3], a[g]);
-        a[g] = fmaf(q1.x, kf[4], a[g]); a[g] = fmaf(q1.y, kf[5], a[g]);
-        a[g] = fmaf(q1.z, kf[6], a[g]); a[g] = fmaf(q1.w, kf[7], a[g]);
-      }
-    }
-#pragma unroll
-    for (int g = 0; g < G; g++) sc[g * chunk + j] = a[g];
-  }
-  __syncthreads();
-  for (int g = warp; g < G; g += 4) {
-    float m = -INFINITY;
-    for (int j = lane; j < nk; j += 32) m = fmaxf(m, sc[g * chunk + j]);
-    m = hb_warp_max(m);
-    float l = 0.f;
-    for (int j = lane; j < nk; j += 32) {
-      const float e = expf(sc[g * chunk + j] - m);
-      sc[g * chunk + j] = e;
-      l += e;
-    }
-    l = hb_warp_sum(l);
-    if (lane == 0) { ml[2 * g] = m; ml[2 * g + 1] = l; }
+  // Q tile [16][D]: rows 0..G-1 are the heads of this kv head, the rest zero
+  for (int i = tid; i < 16 * CH; i += AD_THREADS) {
+    const int r = i / CH, c = i - r * CH;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < G) v = *(const uint4*)(q + ((size_t)t * Hq + (size_t)h * G + r) * D + c * 8);
+    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(sQ + ad_swz<D>(r, c)), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
   }
   hb_cp_async_wait<0>();
   __syncthreads();
 
-  // values: D/8 lanes share a key's row, so a warp takes 32 / (D/8) keys per pass and each value
-  // is read once for all G heads; lanes, then warps, are summed in a fixed order
-  constexpr int TPK = D / 8, KPW = 32 / TPK;
-  const int kq = lane / TPK, dc = lane % TPK;
-  float acc[G][8];
+  float m_run = -INFINITY, l_run = 0.f;  // of row g (a head when g < G), over this warp's keys
+  float o[NT_O][4];
 #pragma unroll
-  for (int g = 0; g < G; g++)
+  for (int i = 0; i < NT_O; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  uint32_t qf[KS][4];
+  {
+    const int mi = lane >> 3, r = lane & 7;
 #pragma unroll
-    for (int e = 0; e < 8; e++) acc[g][e] = 0.f;
-#pragma unroll 4
-  for (int j = warp * KPW + kq; j < nk; j += 4 * KPW) {
-    uint4 raw;
-    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(raw.x), "=r"(raw.y), "=r"(raw.z), "=r"(raw.w) : "r"(sV + ad_swz<D>(j, dc)));
-    const __nv_bfloat162* v2 = (const __nv_bfloat162*)&raw;
-    float vf[8];
+    for (int kk = 0; kk < KS; kk++) hb_ldmatrix_x4(qf[kk], sQ + ad_swz<D>((mi & 1) * 8 + r, kk * 2 + (mi >> 1)));
+  }
+  for (int kb = warp * WK; kb < nk; kb += AD_WARPS * WK) {
+    const uint32_t tK = sK + kb * D * 2, tV = sV + kb * D * 2;  // 64 rows are a whole number of 8-row swizzle groups
+    float sc[8][4];
 #pragma unroll
-    for (int e = 0; e < 4; e++) {
-      const float2 f = __bfloat1622float2(v2[e]);
-      vf[2 * e] = f.x;
-      vf[2 * e + 1] = f.y;
+    for (int i = 0; i < 8; i++) sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.f;
+    {
+      const int mi = lane >> 3, r = lane & 7;
+#pragma unroll
+      for (int kk = 0; kk < KS; kk++) {
+#pragma unroll
+        for (int np = 0; np < 4; np++) {
+          uint32_t b[4];
+          hb_ldmatrix_x4(b, tK + ad_swz<D>(np * 16 + (mi >> 1) * 8 + r, kk * 2 + (mi & 1)));
+          hb_mma_16816(sc[2 * np], qf[kk], b);
+          hb_mma_16816(sc[2 * np + 1], qf[kk], b + 2);
+        }
+      }
     }
+    float mx = -INFINITY;
 #pragma unroll
-    for (int g = 0; g < G; g++) {
-      const float pj = sc[g * chunk + j];
+    for (int i = 0; i < 8; i++)
 #pragma unroll
-      for (int e = 0; e < 8; e++) acc[g][e] = fmaf(pj, vf[e], acc[g][e]);
+      for (int e = 0; e < 2; e++) {
+        if (kb + i * 8 + 2 * tq + e >= nk) sc[i][e] = -INFINITY;
+        mx = fmaxf(mx, sc[i][e]);
+      }
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float mn = fmaxf(m_run, mx * scale_log2);   // finite: the pass has at least one key
+    const float corr = exp2f(m_run - mn);
+    m_run = mn;
+    float sum = 0.f;
+    uint32_t pf[4][4];
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      const float p0 = exp2f(sc[i][0] * scale_log2 - mn), p1 = exp2f(sc[i][1] * scale_log2 - mn);
+      sum += p0 + p1;
+      pf[i >> 1][(i & 1) * 2] = hb_pack_bf16(p0, p1);
+      pf[i >> 1][(i & 1) * 2 + 1] = 0u;  // rows 8..15 of the tile are padding
+    }
+    l_run = l_run * corr + sum;
+#pragma unroll
+    for (int i = 0; i < NT_O; i++) { o[i][0] *= corr; o[i][1] *= corr; }
+    {
+      const int mi = lane >> 3, r = lane & 7;
+#pragma unroll
+      for (int j2 = 0; j2 < 4; j2++) {
+#pragma unroll
+        for (int cp = 0; cp < NT_O / 2; cp++) {
+          uint32_t b[4];
+          hb_ldmatrix_x4_trans(b, tV + ad_swz<D>(j2 * 16 + (mi & 1) * 8 + r, cp * 2 + (mi >> 1)));
+          hb_mma_16816(o[2 * cp], pf[j2], b);
+          hb_mma_16816(o[2 * cp + 1], pf[j2], b + 2);
+        }
+      }
     }
   }
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+  if (g < G) {
 #pragma unroll
-  for (int g = 0; g < G; g++)
-#pragma unroll
-    for (int e = 0; e < 8; e++) {
-      float a = acc[g][e];
-#pragma unroll
-      for (int o = TPK; o < 32; o <<= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
-      if (kq == 0) red[(warp * G + g) * D + dc * 8 + e] = a;
+    for (int i = 0; i < NT_O; i++) {
+      red_o[(warp * G + g) * D + i * 8 + 2 * tq] = o[i][0];
+      red_o[(warp * G + g) * D + i * 8 + 2 * tq + 1] = o[i][1];
     }
+    if (tq == 0) { red_ml[(warp * G + g) * 2] = m_run; red_ml[(warp * G + g) * 2 + 1] = l_run; }
+  }
   __syncthreads();
+  // the warps' partial results, in warp order; (max, sum) leave in the natural-log domain
   const bool whole = s_lo == s_hi;
   for (int i = tid; i < G * D; i += AD_THREADS) {
-    const int g = i / D;
-    const float a = ((red[i] + red[G * D + i]) + red[2 * G * D + i]) + red[3 * G * D + i];
-    const size_t head = (size_t)t * Hq + (size_t)h * G + g;
-    if (whole) out[head * D + (i - g * D)] = __float2bfloat16_rn(a / ml[2 * g + 1]);
-    else part_acc[(head * S + s) * D + (i - g * D)] = a;
-  }
-  if (!whole && tid < G) {
-    const size_t head = (size_t)t * Hq + (size_t)h * G + tid;
-    part_ml[(head * S + s) * 2] = ml[2 * tid];
-    part_ml[(head * S + s) * 2 + 1] = ml[2 * tid + 1];
+    const int gg = i / D, d = i - gg * D;
+    float m = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < AD_WARPS; w++) m = fmaxf(m, red_ml[(w * G + gg) * 2]);
+    float a = 0.f, l = 0.f;
+#pragma unroll
+    for (int w = 0; w < AD_WARPS; w++) {
+      const float f = exp2f(red_ml[(w * G + gg) * 2] - m);  // 0 for a warp without keys
+      a += red_o[(w * G + gg) * D + d] * f;
+      l += red_ml[(w * G + gg) * 2 + 1] * f;
+    }
+    const size_t head = (size_t)t * Hq + (size_t)h * G + gg;
+    if (whole) {
+      out[head * D + d] = __float2bfloat16_rn(a / l);
+    } else {
+      part_acc[(head * S + s) * D + d] = a;
+      if (d == 0) {
+        part_ml[(head * S + s) * 2] = m * 0.6931471805599453f;
+        part_ml[(head * S + s) * 2 + 1] = l;
+      }
+    }
   }
 }
 
@@ -184,9 +200,9 @@ static int launch_decode(int G, dim3 grid, size_t smem, cudaStream_t st, const _
   return 1;
 }
 
-// Does the decode kernel take these sizes? (head_dim 32, 64 or 128; group up to 8)
+// Does the decode kernel take these sizes? (head_dim 64 or 128; group up to 8)
 HB_EXPORT int hb_attn_decode_supported(int Hq, int Hkv, int D) {
-  return Hkv > 0 && Hq % Hkv == 0 && Hq / Hkv <= 8 && (D == 32 || D == 64 || D == 128);
+  return Hkv > 0 && Hq % Hkv == 0 && Hq / Hkv <= 8 && (D == 64 || D == 128);
 }
 
 // Partials layout as hb_attn_rows of the core library: workspace = part_acc [T, Hq, S, D] then
@@ -203,16 +219,16 @@ HB_EXPORT int hb_attn_decode(const void* q, const void* kc, const void* vc, cons
   if (T > 65535 || Hkv > 65535) HB_FAIL("hb_attn_decode: %d rows / %d kv heads are beyond the grid limit", T, Hkv);
   const int G = Hq / Hkv, S = max_pos / chunk + 1;
   if (S > 1 && !workspace) HB_FAIL("hb_attn_decode: rows that span %d chunks need a workspace", S);
-  const size_t smem = 2 * (size_t)chunk * D * 2 + ((size_t)G * D + (size_t)G * chunk + 2 * G + 4 * (size_t)G * D) * sizeof(float);
+  if (chunk % 64) HB_FAIL("hb_attn_decode: chunk %d must be a multiple of 64", chunk);
+  const size_t smem = 2 * (size_t)chunk * D * 2 + 16 * (size_t)D * 2 + AD_WARPS * (size_t)G * (D + 2) * sizeof(float);
   if (smem > 200 * 1024) HB_FAIL("hb_attn_decode: %zu bytes of shared memory (chunk %d, head_dim %d)", smem, chunk, D);
   float* pa = workspace;
   float* pm = workspace ? workspace + (size_t)T * Hq * S * D : nullptr;
   dim3 grid(S, Hkv, T);
   const __nv_bfloat16 *qq = (const __nv_bfloat16*)q, *kk = (const __nv_bfloat16*)kc, *vv = (const __nv_bfloat16*)vc;
   int r = 1;
-  if (D == 32) r = launch_decode<32>(G, grid, smem, st, qq, kk, vv, bt, bt_stride, row_req, pos, (__nv_bfloat16*)out, pa, pm, Hq, Hkv, page_size, window, scale, chunk, S, q_len, row_limit);
-  else if (D == 64) r = launch_decode<64>(G, grid, smem, st, qq, kk, vv, bt, bt_stride, row_req, pos, (__nv_bfloat16*)out, pa, pm, Hq, Hkv, page_size, window, scale, chunk, S, q_len, row_limit);
-  else if (D == 128) r = launch_decode<128>(G, grid, smem, st, qq, kk, vv, bt, bt_stride, row_req, pos, (__nv_bfloat16*)out, pa, pm, Hq, Hkv, page_size, window, scale, chunk, S, q_len, row_limit);
+  if (D == 64) r = launch_decode<64>(G, grid, smem, st, qq, kk, vv, bt, bt_stride, row_req, pos, (__nv_bfloat16*)out, pa, pm, Hq, Hkv, page_size, window, scale * 1.4426950408889634f, chunk, S, q_len, row_limit);
+  else if (D == 128) r = launch_decode<128>(G, grid, smem, st, qq, kk, vv, bt, bt_stride, row_req, pos, (__nv_bfloat16*)out, pa, pm, Hq, Hkv, page_size, window, scale * 1.4426950408889634f, chunk, S, q_len, row_limit);
   if (r) HB_FAIL("hb_attn_decode: no kernel for group %d", G);
   HB_CHECK_LAUNCH("hb_attn_decode");
   return 0;

@@ -166,8 +166,8 @@ import plain_llama as plain
 from test_gpu_kernels_plain import _paged_setup
 
 
-@pytest.mark.parametrize("Hq,Hkv,D,ps,window", [(8, 2, 64, 16, 0), (3, 1, 32, 8, 0), (10, 2, 128, 16, 0), (8, 8, 64, 32, 0),
-                                                (8, 1, 64, 16, 0), (6, 2, 32, 16, 40), (4, 2, 64, 16, 300)])
+@pytest.mark.parametrize("Hq,Hkv,D,ps,window", [(8, 2, 64, 16, 0), (3, 1, 128, 8, 0), (10, 2, 128, 16, 0), (8, 8, 64, 32, 0),
+                                                (8, 1, 64, 16, 0), (6, 2, 64, 16, 40), (4, 2, 64, 16, 300), (7, 1, 64, 16, 0)])
 def test_attention_decode(Hq, Hkv, D, ps, window):
     lens = [700, 37, 1, 300]
     kc, vc, bt, ks, vs = _paged_setup(lens, Hkv, D, ps, torch.bfloat16, 21)
