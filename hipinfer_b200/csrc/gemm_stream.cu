@@ -18,9 +18,11 @@
 enum { ST_F32 = 0, ST_BF16 = 1, ST_ADD_F32 = 2, ST_SWIGLU_BF16 = 3 };
 constexpr int ST_ROWS = 128, ST_BK = 64, ST_W_BYTES = ST_ROWS * ST_BK * 2;
 
-template <int NT> struct StreamCfg {
+// DEEP: the pipeline of a product that is not split along K (many column blocks): six stages,
+// two CTAs per SM; otherwise four (three for 64 tokens) and three CTAs per SM.
+template <int NT, bool DEEP> struct StreamCfg {
   static constexpr int STAGE = ST_W_BYTES + NT * ST_BK * 2;
-  static constexpr int STAGES = NT <= 32 ? 4 : 3;
+  static constexpr int STAGES = DEEP ? (NT <= 32 ? 6 : 4) : (NT <= 32 ? 4 : 3);
   static constexpr int BAR = STAGES * STAGE;
   static constexpr int TOTAL = BAR + 256 + 1024;
   static constexpr int TMEM_COLS = NT < 32 ? 32 : NT;
@@ -38,12 +40,29 @@ __device__ __forceinline__ void stream_store(int epi, void* C, long ldc, int m, 
   }
 }
 
-template <int NT>
+#ifdef HB_STREAM_TIMING
+__device__ unsigned long long g_stream_stamps[16];
+__device__ __forceinline__ void hb_stamp(int i) {
+  if (blockIdx.x == 0 && blockIdx.y == 0) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    g_stream_stamps[i] = t;
+  }
+}
+HB_EXPORT int hb_stream_stamps(unsigned long long* out) {
+  return cudaMemcpyFromSymbol(out, g_stream_stamps, sizeof(g_stream_stamps)) == cudaSuccess ? 0 : -1;
+}
+#define HB_STAMP(i) hb_stamp(i)
+#else
+#define HB_STAMP(i)
+#endif
+
+template <int NT, bool DEEP>
 __global__ void __launch_bounds__(192) gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w,
                                                           const __grid_constant__ CUtensorMap map_x, void* C, long ldc,
                                                           int M, int N, int K, int kslice, float* ws, int* counters,
                                                           int epi, int* status) {
-  using S = StreamCfg<NT>;
+  using S = StreamCfg<NT, DEEP>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t* full = (uint64_t*)(smem + S::BAR);
@@ -54,6 +73,7 @@ __global__ void __launch_bounds__(192) gemm_stream_kernel(const __grid_constant_
   int* is_last = (int*)(tmem_slot + 2);
 
   hb_pdl_launch();
+  if (threadIdx.x == 0) HB_STAMP(0);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nb = blockIdx.x, sp = blockIdx.y, ksplit = gridDim.y, NP = gridDim.x * ST_ROWS;
   const int n0 = nb * ST_ROWS, k_begin = sp * kslice, k_end = min(K, k_begin + kslice);
@@ -74,6 +94,7 @@ __global__ void __launch_bounds__(192) gemm_stream_kernel(const __grid_constant_
   __syncthreads();
   hb_tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) HB_STAMP(1);
 
   if (warp == 4) {
     if (lane == 0) {
@@ -85,6 +106,7 @@ __global__ void __launch_bounds__(192) gemm_stream_kernel(const __grid_constant_
         hb_tma_load_2d(smem + kb * S::STAGE, &map_w, &full[kb], k_begin + kb * ST_BK, n0);
       }
       hb_pdl_wait();
+      HB_STAMP(2);
       for (int kb = 0; kb < pre; kb++)
         hb_tma_load_2d(smem + kb * S::STAGE + ST_W_BYTES, &map_x, &full[kb], k_begin + kb * ST_BK, 0);
       for (int kb = pre; kb < num_kb; kb++) {
@@ -102,6 +124,8 @@ __global__ void __launch_bounds__(192) gemm_stream_kernel(const __grid_constant_
       for (int kb = 0; kb < num_kb; kb++) {
         const uint32_t s = kb % S::STAGES, ph = (kb / S::STAGES) & 1;
         if (!hb_mbar_wait(&full[s], ph, abort_flag)) { ok = false; break; }
+        if (kb == 0) HB_STAMP(3);
+        if (kb == num_kb - 1) HB_STAMP(4);
         hb_tc_fence_after();
         const uint64_t dw = hb_umma_desc_k128(hb_smem_u32(smem + s * S::STAGE));
         const uint64_t dx = hb_umma_desc_k128(hb_smem_u32(smem + s * S::STAGE + ST_W_BYTES));
@@ -114,6 +138,7 @@ __global__ void __launch_bounds__(192) gemm_stream_kernel(const __grid_constant_
   } else {
     // epilogue warps: lane = output column n0 + 32 * warp + lane, v[m] = token m
     const bool ok = hb_mbar_wait(done, 0, abort_flag);
+    if (threadIdx.x == 0) HB_STAMP(5);
     hb_tc_fence_after();
     hb_pdl_wait();  // before the first access to memory that earlier kernels wrote or still read
     float v[NT];
@@ -136,8 +161,10 @@ __global__ void __launch_bounds__(192) gemm_stream_kernel(const __grid_constant_
     hb_tc_fence_before();
   }
 
+  if (threadIdx.x == 0) HB_STAMP(6);
   __threadfence();
   __syncthreads();
+  if (threadIdx.x == 0) HB_STAMP(7);
   if (warp == 5) {
     __syncwarp();
     hb_tmem_dealloc(tmem_base, S::TMEM_COLS);
@@ -150,6 +177,7 @@ __global__ void __launch_bounds__(192) gemm_stream_kernel(const __grid_constant_
 
   if (threadIdx.x == 0) *is_last = atomicAdd(&counters[nb], 1) == ksplit - 1;
   __syncthreads();
+  if (threadIdx.x == 0) HB_STAMP(8);
   if (!*is_last) return;
   __threadfence();
   // four consecutive columns per thread, the slices' loads issued four at a time, added in slice order
@@ -188,6 +216,7 @@ __global__ void __launch_bounds__(192) gemm_stream_kernel(const __grid_constant_
     stream_store(epi, C, ldc, m, n + 3, N, acc.w, up.w, gate);
   }
   if (threadIdx.x == 0) counters[nb] = 0;
+  if (threadIdx.x == 0) HB_STAMP(9);
 }
 
 // The split of K for an [N, K] weight: a function of the weight's shape alone.
@@ -214,11 +243,11 @@ HB_EXPORT int hb_gemm_stream_plan(int N, int K, int* kslice, int* ksplit, long* 
   return 0;
 }
 
-template <int NT>
+template <int NT, bool DEEP>
 static int launch_stream(const CUtensorMap& mw, const CUtensorMap& mx, void* C, long ldc, int M, int N, int K, int kslice,
                          int ksplit, int n_blocks, float* ws, int* counters, int epi, int* status, cudaStream_t s) {
-  using S = StreamCfg<NT>;
-  auto kern = gemm_stream_kernel<NT>;
+  using S = StreamCfg<NT, DEEP>;
+  auto kern = gemm_stream_kernel<NT, DEEP>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
@@ -254,9 +283,17 @@ HB_EXPORT int hb_gemm_stream(const void* A, long lda, const void* W, long ldw, v
   if (hb_make_tensor_map_bf16(&mw, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, ST_ROWS)) return -1;
   if (hb_make_tensor_map_bf16(&mx, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, (uint32_t)NT)) return -1;
   int r;
-  if (NT == 16) r = launch_stream<16>(mw, mx, C, ldc, M, N, K, kslice, ksplit, n_blocks, ws, counters, epi, status, s);
-  else if (NT == 32) r = launch_stream<32>(mw, mx, C, ldc, M, N, K, kslice, ksplit, n_blocks, ws, counters, epi, status, s);
-  else r = launch_stream<64>(mw, mx, C, ldc, M, N, K, kslice, ksplit, n_blocks, ws, counters, epi, status, s);
+#define HB_ST_ARGS mw, mx, C, ldc, M, N, K, kslice, ksplit, n_blocks, ws, counters, epi, status, s
+  if (ksplit == 1) {
+    if (NT == 16) r = launch_stream<16, true>(HB_ST_ARGS);
+    else if (NT == 32) r = launch_stream<32, true>(HB_ST_ARGS);
+    else r = launch_stream<64, true>(HB_ST_ARGS);
+  } else {
+    if (NT == 16) r = launch_stream<16, false>(HB_ST_ARGS);
+    else if (NT == 32) r = launch_stream<32, false>(HB_ST_ARGS);
+    else r = launch_stream<64, false>(HB_ST_ARGS);
+  }
+#undef HB_ST_ARGS
   if (r) return r;
   HB_CHECK_LAUNCH("hb_gemm_stream");
   return 0;
