@@ -23,13 +23,16 @@ _SIGS = {
     "hb_gemm_skinny_plan": [_i, _i, _p, _p, _p, _p],
     "hb_gemm_stream": [_p, _l, _p, _l, _p, _l, _i, _i, _i, _i, _p, _l, _p, _i, _p, _p],
     "hb_gemm_stream_plan": [_i, _i, _p, _p, _p, _p],
+    "hb_gemm_stream_fused": [_p, _l, _p, _p, _i, _f, _p, _l, _i, _i, _i, _i, _p, _l, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p, _l,
+                             _p, _i, _p, _p],
+    "hb_gemm_stream_fused_supported": [_i, _i, _i],
     "hb_attn_decode": [_p, _p, _p, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _i, _p, _i, _p],
     "hb_flash_prefill": [_p, _p, _p, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p],
     "hb_flash_prefill_supported": [_i, _i, _i],
     "hb_attn_decode_supported": [_i, _i, _i],
 }
 _fns = {}
-_LAUNCHES = {"hb_gemm_tc": 1, "hb_gemm_skinny": 1, "hb_gemm_stream": 1, "hb_attn_decode": 1, "hb_flash_prefill": 1}
+_LAUNCHES = {"hb_gemm_stream_fused": 1, "hb_gemm_tc": 1, "hb_gemm_skinny": 1, "hb_gemm_stream": 1, "hb_attn_decode": 1, "hb_flash_prefill": 1}
 _status = None
 
 EPI_F32, EPI_BF16, EPI_ADD_F32, EPI_SWIGLU_BF16 = 0, 1, 2, 3
@@ -181,6 +184,59 @@ def linear_swiglu(a, w, act_out, group) -> bool:
     if group != 16 or act_out.dtype != torch.bfloat16 or not _tc_ok(a, w.t) or w.shape[0] % 32:
         return False
     _gemm(a, w.t, act_out, EPI_SWIGLU_BF16)
+    return True
+
+
+# Norm / rotation / activation fused into the decode products (csrc/gemm_stream_fused.cu): "0" off,
+# "qkv" or "ffn" only that one, "1" both. Off by default: inside a CUDA graph with programmatic
+# dependent launch the separate small kernels cost about what the fused kernels' in-CTA norm pass
+# costs (measured at Llama-3.2-1B shape: batch 8 6,355 tok/s unfused, 6,343 with qkv fused, 6,157
+# with both; batch 16 is slower fused), so the simpler path is the default.
+_FUSE_ENV = os.environ.get("HIPINFER_B200_FUSE", "0")
+FUSE = _FUSE_ENV != "0"
+
+
+def _fused_ok(x, norm_w, w, M) -> bool:
+    N, K = w.shape
+    return (FUSE and not PLAIN_ONLY and SMALL_IMPL == "stream" and w.dtype == torch.bfloat16 and x.dtype == torch.float32
+            and x.stride(1) == 1 and x.stride(0) % 4 == 0 and x.data_ptr() % 16 == 0 and norm_w.data_ptr() % 16 == 0
+            and norm_w.dtype in (torch.float32, torch.bfloat16) and norm_w.is_contiguous() and x.shape[1] == K
+            and w.stride(0) % 8 == 0 and w.data_ptr() % 16 == 0 and bool(_fn("hb_gemm_stream_fused_supported")(M, N, K)))
+
+
+def _fused_call(x, rows, norm_w, eps, w, M, mode, out, pos, slot_map, table, kc, vc, Hq, Hkv, D, page_size):
+    N, K = w.shape
+    _, ksplit, _, n_blocks = stream_plan(N, K)
+    ws, cnt = _skinny_scratch(x.device, ksplit * n_blocks * 128 * 16, n_blocks)
+    p = lambda t: None if t is None else t.data_ptr()
+    _call("hb_gemm_stream_fused", x.data_ptr(), x.stride(0), p(rows), norm_w.data_ptr(),
+          0 if norm_w.dtype == torch.float32 else 1, float(eps), w.data_ptr(), w.stride(0), M, N, K, mode, out.data_ptr(),
+          out.stride(0), p(pos), p(slot_map), p(table), p(kc), p(vc), Hq, Hkv, D, page_size, ws.data_ptr(), ws.numel(),
+          cnt.data_ptr(), cnt.numel(), status_word().data_ptr(), _stream())
+
+
+def norm_linear_swiglu(x, rows, norm_w, eps, w, act_out, group) -> bool:
+    """act_out = SwiGLU(RMSNorm(x[rows]) w^T) in one kernel (up to 16 rows); False if not applicable."""
+    M = act_out.shape[0]
+    if _FUSE_ENV == "qkv":
+        return False
+    if group != 16 or act_out.dtype != torch.bfloat16 or w.shape[0] % 32 or not _fused_ok(x, norm_w, w.t, M):
+        return False
+    _fused_call(x, rows, norm_w, eps, w.t, M, 0, act_out, None, None, None, None, None, 0, 0, 0, 0)
+    return True
+
+
+def norm_qkv_rope(x, norm_w, eps, w, positions, slot_map, table, q_out, k_cache, v_cache, n_heads, n_kv_heads, head_dim,
+                  rotary_dim, page_size) -> bool:
+    """RMSNorm, the fused q/k/v product, rotary and the cache write in one kernel (up to 16 rows)."""
+    M = q_out.shape[0]
+    if _FUSE_ENV == "ffn":
+        return False
+    if (rotary_dim != head_dim or 128 % head_dim or w.shape[0] % 128 or q_out.dtype != torch.bfloat16
+            or (k_cache is not None and k_cache.dtype != torch.bfloat16) or not _fused_ok(x, norm_w, w.t, M)):
+        return False
+    _fused_call(x, None, norm_w, eps, w.t, M, 1, q_out, positions, slot_map, table, k_cache, v_cache, n_heads, n_kv_heads,
+                head_dim, page_size)
     return True
 
 

@@ -291,6 +291,23 @@ def linear_swiglu(a: torch.Tensor, w_gate_up: Weight, act_out: torch.Tensor, gro
     return swiglu(gu, act_out, group)
 
 
+def norm_linear_swiglu(x, norm_weight, eps, w_gate_up: Weight, act_out, group: int, rows=None) -> bool:
+    """act_out = SwiGLU(RMSNorm(x) w^T) as ONE kernel where the fast library has it (a few bfloat16
+    rows); False when it does not apply, and the caller runs the parts one after the other."""
+    from . import fast
+
+    return x.is_cuda and fast.norm_linear_swiglu(x, rows, norm_weight, eps, w_gate_up, act_out, group)
+
+
+def norm_qkv_rope(x, norm_weight, eps, w_qkv: Weight, positions, slot_map, table, q_out, k_cache, v_cache, n_heads,
+                  n_kv_heads, head_dim, rotary_dim, page_size) -> bool:
+    """RMSNorm, q/k/v product, rotation and cache write as ONE kernel where the fast library has it."""
+    from . import fast
+
+    return x.is_cuda and fast.norm_qkv_rope(x, norm_weight, eps, w_qkv, positions, slot_map, table, q_out, k_cache,
+                                            v_cache, n_heads, n_kv_heads, head_dim, rotary_dim, page_size)
+
+
 def attention(q, k_cache, v_cache, batch, group: int, out, n_heads, n_kv_heads, head_dim, page_size, window, scale):
     """Attention of the step's rows over their requests' pages of cache group `group`."""
     from . import fast

@@ -55,6 +55,22 @@ class AttentionMixer(Mixer):
     def cache_need(self):
         return CacheNeed("window" if self.window else "full", self.n_kv_heads, self.head_dim, self.window)
 
+    def forward_prenorm(self, norm, x, batch, cache, state):
+        """The same, given the norm part instead of normalised rows: for a few rows the norm, the
+        q/k/v product, the rotation and the cache write run as one kernel."""
+        from .norm import RMSNorm
+        from .rotary import RotaryEmbedding
+
+        T = x.shape[0]
+        if type(norm) is RMSNorm and type(self.position) is RotaryEmbedding and T <= 16:
+            q = torch.empty(T, self.n_heads * self.head_dim, dtype=self.ctx.dtype, device=x.device)
+            slot_map = batch.slot_maps[cache.group] if cache.write else None
+            if ops.norm_qkv_rope(x, norm.weight, norm.eps, self.wqkv, batch.positions, slot_map, self.position.table, q,
+                                 cache.k, cache.v, self.n_heads, self.n_kv_heads, self.head_dim,
+                                 self.position.rotary_dim, self.ctx.page_size):
+                return self._attend_and_project(q, x, batch, cache)
+        self.forward(norm.forward(x), x, batch, cache, state)
+
     def forward(self, xn, x, batch, cache, state):
         T = xn.shape[0]
         Hq, Hkv, D = self.n_heads, self.n_kv_heads, self.head_dim
@@ -63,7 +79,12 @@ class AttentionMixer(Mixer):
         q = torch.empty(T, Hq * D, dtype=self.ctx.dtype, device=xn.device)
         slot_map = batch.slot_maps[cache.group] if cache.write else None
         self.position.rotate_and_store(qkv, batch.positions, slot_map, q, cache.k, cache.v, Hq, Hkv)
-        att = torch.empty(T, Hq * D, dtype=self.ctx.dtype, device=xn.device)
+        self._attend_and_project(q, x, batch, cache)
+
+    def _attend_and_project(self, q, x, batch, cache):
+        T = q.shape[0]
+        Hq, Hkv, D = self.n_heads, self.n_kv_heads, self.head_dim
+        att = torch.empty(T, Hq * D, dtype=self.ctx.dtype, device=q.device)
         ops.attention(q, cache.k, cache.v, batch, cache.group, att, Hq, Hkv, D, self.ctx.page_size, self.window,
                       self.scale)
         ops.linear(att, self.wo, x, accumulate=True)

@@ -28,8 +28,16 @@ class PreNormBlock(Part):
         return sum(p.weight_bytes() for p in self.parts)
 
     def forward(self, x, batch, cache, state):
-        self.mixer.forward(self.mixer_norm.forward(x), x, batch, cache, state)
-        self.feed_forward.forward(self.feed_forward_norm.forward(x), x, batch)
+        # a part may take the norm itself (forward_prenorm) to fuse it into its first kernel;
+        # a part without that method gets the normalised rows
+        if hasattr(self.mixer, "forward_prenorm"):
+            self.mixer.forward_prenorm(self.mixer_norm, x, batch, cache, state)
+        else:
+            self.mixer.forward(self.mixer_norm.forward(x), x, batch, cache, state)
+        if hasattr(self.feed_forward, "forward_prenorm"):
+            self.feed_forward.forward_prenorm(self.feed_forward_norm, x, batch)
+        else:
+            self.feed_forward.forward(self.feed_forward_norm.forward(x), x, batch)
 
 
 register_part("block", "pre_norm", PreNormBlock)
