@@ -198,7 +198,7 @@ FUSE = _FUSE_ENV != "0"
 
 def _fused_ok(x, norm_w, w, M) -> bool:
     N, K = w.shape
-    return (FUSE and not PLAIN_ONLY and SMALL_IMPL == "stream" and w.dtype == torch.bfloat16 and x.dtype == torch.float32
+    return (not PLAIN_ONLY and SMALL_IMPL == "stream" and w.dtype == torch.bfloat16 and x.dtype == torch.float32
             and x.stride(1) == 1 and x.stride(0) % 4 == 0 and x.data_ptr() % 16 == 0 and norm_w.data_ptr() % 16 == 0
             and norm_w.dtype in (torch.float32, torch.bfloat16) and norm_w.is_contiguous() and x.shape[1] == K
             and w.stride(0) % 8 == 0 and w.data_ptr() % 16 == 0 and bool(_fn("hb_gemm_stream_fused_supported")(M, N, K)))
@@ -218,8 +218,6 @@ def _fused_call(x, rows, norm_w, eps, w, M, mode, out, pos, slot_map, table, kc,
 def norm_linear_swiglu(x, rows, norm_w, eps, w, act_out, group) -> bool:
     """act_out = SwiGLU(RMSNorm(x[rows]) w^T) in one kernel (up to 16 rows); False if not applicable."""
     M = act_out.shape[0]
-    if _FUSE_ENV == "qkv":
-        return False
     if group != 16 or act_out.dtype != torch.bfloat16 or w.shape[0] % 32 or not _fused_ok(x, norm_w, w.t, M):
         return False
     _fused_call(x, rows, norm_w, eps, w.t, M, 0, act_out, None, None, None, None, None, 0, 0, 0, 0)
@@ -230,8 +228,6 @@ def norm_qkv_rope(x, norm_w, eps, w, positions, slot_map, table, q_out, k_cache,
                   rotary_dim, page_size) -> bool:
     """RMSNorm, the fused q/k/v product, rotary and the cache write in one kernel (up to 16 rows)."""
     M = q_out.shape[0]
-    if _FUSE_ENV == "ffn":
-        return False
     if (rotary_dim != head_dim or 128 % head_dim or w.shape[0] % 128 or q_out.dtype != torch.bfloat16
             or (k_cache is not None and k_cache.dtype != torch.bfloat16) or not _fused_ok(x, norm_w, w.t, M)):
         return False

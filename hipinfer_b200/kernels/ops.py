@@ -296,7 +296,8 @@ def norm_linear_swiglu(x, norm_weight, eps, w_gate_up: Weight, act_out, group: i
     rows); False when it does not apply, and the caller runs the parts one after the other."""
     from . import fast
 
-    return x.is_cuda and fast.norm_linear_swiglu(x, rows, norm_weight, eps, w_gate_up, act_out, group)
+    return (x.is_cuda and fast._FUSE_ENV in ("1", "ffn")
+            and fast.norm_linear_swiglu(x, rows, norm_weight, eps, w_gate_up, act_out, group))
 
 
 def norm_qkv_rope(x, norm_weight, eps, w_qkv: Weight, positions, slot_map, table, q_out, k_cache, v_cache, n_heads,
@@ -304,7 +305,7 @@ def norm_qkv_rope(x, norm_weight, eps, w_qkv: Weight, positions, slot_map, table
     """RMSNorm, q/k/v product, rotation and cache write as ONE kernel where the fast library has it."""
     from . import fast
 
-    return x.is_cuda and fast.norm_qkv_rope(x, norm_weight, eps, w_qkv, positions, slot_map, table, q_out, k_cache,
+    return x.is_cuda and fast._FUSE_ENV in ("1", "qkv") and fast.norm_qkv_rope(x, norm_weight, eps, w_qkv, positions, slot_map, table, q_out, k_cache,
                                             v_cache, n_heads, n_kv_heads, head_dim, rotary_dim, page_size)
 
 
