@@ -173,12 +173,10 @@ def decode_e2e(eng, batch: int, steps: int, warmup: int):
     torch.cuda.synchronize()
     dt = time.perf_counter() - t0
     assert len(eng.scheduler.running) == batch, "a request finished inside the timed steps"
-    for r in list(eng.scheduler.running):          # the measurement is over: drop the requests
-        eng.scheduler.running.remove(r)
-        eng.runner.end(r.request_id)
+    eng.abort_all()                                # the measurement is over: drop the requests
     groups = len(eng.runner.cache.groups)
     width = -(-CONTEXT_LEN // PAGE)
-    n_int = 3 * batch + 4 * batch + batch + groups * batch * width + groups * batch
+    n_int = 4 * batch + 4 * batch + batch + groups * batch * width + groups * batch
     return dt / (steps - 1) * 1e3, n_int * 4, batch * 4
 
 

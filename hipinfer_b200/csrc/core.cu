@@ -658,6 +658,24 @@ HB_EXPORT int hb_sample(const float* logits, long ld, int rows, int V, const flo
 }
 
 // ---------------------------------------------------------------------------------------
+// tokens[i] = src[map[i]] where map[i] >= 0: rows of a step whose token was sampled on the
+// device by the step before and has not been to the host.
+// ---------------------------------------------------------------------------------------
+__global__ void feed_tokens_kernel(int* __restrict__ tokens, const int* __restrict__ src, const int* __restrict__ map, int n) {
+  hb_pdl_launch();
+  hb_pdl_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n && map[i] >= 0) tokens[i] = src[map[i]];
+}
+
+HB_EXPORT int hb_feed_tokens(int* tokens, const int* src, const int* map, int n, cudaStream_t s) {
+  if (n <= 0) return 0;
+  hb_launch(feed_tokens_kernel, (n + 127) / 128, 128, 0, s, tokens, src, map, n);
+  HB_CHECK_LAUNCH("hb_feed_tokens");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------
 // Element-type conversion of a dense array (weights of another storage type, test helpers).
 // ---------------------------------------------------------------------------------------
 template <typename TI, typename TO>

@@ -33,7 +33,7 @@ class Engine:
     def __init__(self, path: Optional[str] = None, max_batch: int = 8, max_seq: int = 2048, max_prefill: int = 1024,
                  dtype: str = "bfloat16", device: str = "cuda:0", config: Union[ModelConfig, dict, None] = None,
                  random_weights: Optional[int] = None, std: float = 0.02, page_size: int = 16,
-                 num_pages: Optional[int] = None):
+                 num_pages: Optional[int] = None, pipeline: bool = True):
         kw = dict(dtype=dtype, device=device, page_size=page_size, num_pages=num_pages, max_model_len=max_seq,
                   max_num_seqs=max_batch)
         if path is not None:
@@ -58,6 +58,11 @@ class Engine:
             setattr(self, ours, getattr(c, theirs, None))
         self.weight_bytes = r.model.step_weight_bytes()
         self.kv_bytes_per_token = r.storage.bytes_per_token()
+        # pipeline: a step is launched before the tokens of the step before it have been read
+        # back, so the host prepares step i + 1 while the device runs step i (see step())
+        self.pipeline = bool(pipeline)
+        self._pending = None
+        self._unreported: List[Request] = []
         self._ids = itertools.count()
         self._slots: Dict[int, dict] = {}
         self._last_logits: Dict[int, torch.Tensor] = {}
@@ -77,7 +82,95 @@ class Engine:
         return rid
 
     def step(self) -> List[Request]:
-        """One scheduler step: schedule, run the batch, sample, record. Returns requests finished in it."""
+        """One scheduler step: schedule, run the batch, sample, record. Returns requests whose
+        last token has arrived on the host.
+
+        With `pipeline` the sampled tokens stay on the device and feed the next step there; the
+        step is recorded with placeholders, the NEXT step is scheduled and launched, and only then
+        are this step's tokens read back. The host's work for a step thus overlaps the device's
+        work for the step before. Finishing by length needs no token value; a stop token is
+        noticed one step late, and the extra token is dropped."""
+        if not self.pipeline:
+            return self._step_sync()
+        done: List[Request] = []
+        sched = self.scheduler.schedule() if self.scheduler.has_work() else []
+        if not sched:
+            if self.scheduler.has_work() and self._pending is None:
+                raise RuntimeError("the scheduler has work but could schedule nothing")
+            return self._collect()
+        if self._pending is not None and any(self._inner_placeholder(s) for s in sched):
+            done += self._collect()            # a portion needs a token value that is still on the device
+        older = self._pending
+        self._pending = self._launch(sched, older)
+        if older is not None:
+            done += self._collect(older)
+        return done
+
+    PLACEHOLDER = -1
+
+    def _inner_placeholder(self, s) -> bool:
+        toks = s.request.tokens
+        part = toks[s.start:s.start + s.n]
+        if self.PLACEHOLDER not in part:
+            return False
+        return part.count(self.PLACEHOLDER) > 1 or part[-1] != self.PLACEHOLDER or s.start + s.n != len(toks)
+
+    def _launch(self, sched, older):
+        """Run the batch and sample on the device; record the step with placeholders."""
+        entries, token_map, row = [], [], 0
+        src = {id(req): i for i, (req, _) in enumerate(older["slots"])} if older is not None else {}
+        for s in sched:
+            part = list(s.request.tokens[s.start:s.start + s.n])
+            tm = [-1] * s.n
+            if part[-1] == self.PLACEHOLDER:
+                part[-1] = 0
+                tm[-1] = src[id(s.request)]
+            entries.append(StepEntry(s.request.request_id, part, [s.n - 1] if s.samples else []))
+            token_map += tm
+            row += s.n
+        feed = older is not None and any(t >= 0 for t in token_map)
+        logits = self.runner.step(entries, device_tokens=older["tokens_dev"] if feed else None,
+                                  token_map=token_map if feed else None)
+        samplers = [s for s in sched if s.samples]
+        pending = dict(slots=[], tokens_dev=None, host=None, event=None)
+        if samplers:
+            tokens_dev = self.sampler.sample_device(logits, [s.request.params for s in samplers],
+                                                    [s.start + s.n for s in samplers])
+            host = torch.empty(len(samplers), dtype=torch.int32, pin_memory=True)
+            host.copy_(tokens_dev, non_blocking=True)
+            event = torch.cuda.Event()
+            event.record()
+            pending.update(tokens_dev=tokens_dev, host=host, event=event)
+        self.scheduler.update(sched, [self.PLACEHOLDER] * len(samplers))
+        pending["slots"] = [(s.request, len(s.request.output) - 1) for s in samplers]
+        self._unreported += [s.request for s in samplers if s.request.status == "finished"]
+        return pending
+
+    def _collect(self, pending=None) -> List[Request]:
+        """Read a launched step's tokens, put them in the place of their placeholders, apply the
+        stop conditions that need a token's value, and report requests that are complete."""
+        if pending is None:
+            pending, self._pending = self._pending, None
+        if pending is not None and pending["event"] is not None:
+            pending["event"].synchronize()
+            eos = self.scheduler.eos
+            for (req, idx), tok in zip(pending["slots"], pending["host"].tolist()):
+                if idx >= len(req.output):
+                    continue                   # cut off by a stop token found earlier
+                req.output[idx] = tok
+                p = req.params
+                if tok in p.stop_token_ids or (not p.ignore_eos and tok in eos):
+                    del req.output[idx + 1:]
+                    if req.status != "finished":
+                        self.scheduler.finish(req, "stop")
+                        self._unreported.append(req)
+                    else:
+                        req.finish_reason = "stop"
+        done = [r for r in self._unreported if self.PLACEHOLDER not in r.output]
+        self._unreported = [r for r in self._unreported if self.PLACEHOLDER in r.output]
+        return done
+
+    def _step_sync(self) -> List[Request]:
         sched = self.scheduler.schedule()
         if not sched:
             if self.scheduler.has_work():
@@ -94,10 +187,18 @@ class Engine:
     def run(self) -> Dict[object, List[int]]:
         """Step until every added request has finished; {request id: produced tokens}."""
         out = {}
-        while self.scheduler.has_work():
+        while self.scheduler.has_work() or self._pending is not None or self._unreported:
             for req in self.step():
                 out[req.request_id] = list(req.output)
         return out
+
+    def abort_all(self) -> None:
+        """Drop every request: wait for a step in flight, then free all pages and state slots."""
+        self._collect()
+        self._unreported = []
+        for req in list(self.scheduler.running) + list(self.scheduler.waiting):
+            self.scheduler.finish(req, "aborted")
+        self.scheduler.waiting.clear()
 
     def generate(self, prompt, n_new: int, graph: bool = True, temperature: float = 0.0, seed: int = 0):
         """n_new tokens after `prompt` (the first comes from the prompt's last position).

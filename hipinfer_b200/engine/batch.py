@@ -37,6 +37,7 @@ class StepBatch:
     req_ctx_len: torch.Tensor     # int32 [R]  tokens in the cache before this step
     req_state_slot: torch.Tensor  # int32 [R]
     want_rows: torch.Tensor       # int32 [W]
+    token_map: torch.Tensor       # int32 [T]  >= 0: the row's token is that entry of a device buffer (see runner.step)
     block_tables: List[torch.Tensor]  # per cache group int32 [R, pages]
     slot_maps: List[torch.Tensor]     # per cache group int32 [T]
     # host mirrors, for launch geometry and for parts that loop over requests
@@ -52,7 +53,8 @@ class StepBatch:
 def build_step_batch(entries: Sequence[StepEntry], ctx_lens: Sequence[int], state_slots: Sequence[int],
                      tables: Sequence[Sequence[Sequence[int]]], slot_maps: Sequence[Sequence[Sequence[int]]],
                      n_groups: int, device, table_widths: Optional[Sequence[int]] = None,
-                     static: Optional[torch.Tensor] = None, max_pos: Optional[int] = None) -> StepBatch:
+                     static: Optional[torch.Tensor] = None, max_pos: Optional[int] = None,
+                     token_map: Optional[Sequence[int]] = None) -> StepBatch:
     """entries[r] runs at positions ctx_lens[r].. ; tables[r][g] is the request's block table of
     group g AFTER room was made for this step; slot_maps[r][g][i] the cache slot of its i-th token.
     `table_widths` fixes the block tables' widths and `static` is a device buffer to fill instead
@@ -70,7 +72,7 @@ def build_step_batch(entries: Sequence[StepEntry], ctx_lens: Sequence[int], stat
     if table_widths is not None:
         assert all(w <= tw for w, tw in zip(widths, table_widths)), "a block table is wider than the graph was made for"
         widths = list(table_widths)
-    n_int = 3 * T + 4 * R + W + sum(R * w for w in widths) + n_groups * T
+    n_int = 4 * T + 4 * R + W + sum(R * w for w in widths) + n_groups * T
     host = torch.empty(max(n_int, 1), dtype=torch.int32, pin_memory=torch.device(device).type == "cuda")
     buf = host.numpy()
     off = 0
@@ -86,6 +88,7 @@ def build_step_batch(entries: Sequence[StepEntry], ctx_lens: Sequence[int], stat
     pos = [ctx_lens[r] + i for r in range(R) for i in range(q_len[r])]
     rowreq = [r for r in range(R) for _ in range(q_len[r])]
     o_tok, o_pos, o_rr = put(toks, T), put(pos, T), put(rowreq, T)
+    o_map = put(list(token_map) if token_map is not None else -1, T)
     o_qs, o_ql, o_cl, o_ss = put(q_start, R), put(q_len, R), put(list(ctx_lens), R), put(list(state_slots), R)
     o_w = put(want_rows, W)
     o_bt = []
@@ -111,7 +114,7 @@ def build_step_batch(entries: Sequence[StepEntry], ctx_lens: Sequence[int], stat
     return StepBatch(
         n_rows=T, n_requests=R, n_want=W, tokens=view(o_tok, T), positions=view(o_pos, T), row_request=view(o_rr, T),
         req_q_start=view(o_qs, R), req_q_len=view(o_ql, R), req_ctx_len=view(o_cl, R), req_state_slot=view(o_ss, R),
-        want_rows=view(o_w, W),
+        want_rows=view(o_w, W), token_map=view(o_map, T),
         block_tables=[view(o_bt[g], R * widths[g]).view(R, widths[g]) for g in range(n_groups)],
         slot_maps=[view(o_sm[g], T) for g in range(n_groups)],
         h_q_start=q_start, h_q_len=q_len, h_ctx_len=list(ctx_lens), h_state_slot=list(state_slots),

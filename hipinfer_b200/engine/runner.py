@@ -107,13 +107,15 @@ class ModelRunner:
                 if not (0 <= int(w) < n):
                     raise StepError(f"request {e.request_id!r}: want {w} is outside its {n} tokens")
 
-    def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None,
+             token_map: Optional[Sequence[int]] = None) -> torch.Tensor:
         """Run one batch; float32 logits [number of wanted places, vocab] on the device.
         Raises OutOfPages (nothing changed) when the cache cannot hold the new tokens.
         `device_tokens` (int32 [rows], on the device) replaces the entries' token values, which
         are then placeholders: tokens sampled on the device feed the next step without a trip to
         the host (the reference keeps token and position on the device for the same reason,
-        README.md:510-512)."""
+        README.md:510-512). With `token_map` (one int per row) only rows with an entry >= 0 take
+        their token from device_tokens[entry]; the others keep the value the entry gives."""
         entries = list(entries)
         self.check_entries(entries)
         if not entries:
@@ -143,11 +145,11 @@ class ModelRunner:
             slot_maps.append(self.cache.append(e.request_id, len(e.tokens)))
             tables.append(self._table_rows(rc))
         if self.cuda_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
-            logits = self._graph_step(entries, ctx_lens, slots, tables, slot_maps, device_tokens)
+            logits = self._graph_step(entries, ctx_lens, slots, tables, slot_maps, device_tokens, token_map)
         else:
-            batch = build_step_batch(entries, ctx_lens, slots, tables, slot_maps, len(self.cache.groups), self.device)
-            if device_tokens is not None:
-                batch.tokens.copy_(device_tokens, non_blocking=True)
+            batch = build_step_batch(entries, ctx_lens, slots, tables, slot_maps, len(self.cache.groups), self.device,
+                                     token_map=token_map)
+            self._feed(batch.tokens, batch.token_map, device_tokens, token_map)
             logits = self.model.forward(batch, self.storage)
         for e in entries:
             if self.cache.release_behind_window(e.request_id):
@@ -171,7 +173,17 @@ class ModelRunner:
             out.append(arr[:len(table)])
         return out
 
-    def _graph_step(self, entries, ctx_lens, slots, tables, slot_maps, device_tokens=None) -> torch.Tensor:
+    @staticmethod
+    def _feed(tokens, map_dev, device_tokens, token_map):
+        if device_tokens is None:
+            return
+        if token_map is None:
+            tokens.copy_(device_tokens, non_blocking=True)
+        else:
+            from ..kernels import ops
+            ops.feed_tokens(tokens, device_tokens, map_dev)
+
+    def _graph_step(self, entries, ctx_lens, slots, tables, slot_maps, device_tokens=None, token_map=None) -> torch.Tensor:
         """A decode-only step through the CUDA graph for this many requests (captured at first use).
         The graph's batch lives in one static device buffer that each step overwrites; launch
         geometry is made for the longest sequence, so blocks beyond a row's keys return at once.
@@ -180,11 +192,10 @@ class ModelRunner:
         g = self._graphs.get(R)
         args = dict(n_groups=G, device=self.device, table_widths=self._table_widths, max_pos=self.max_model_len - 1)
         if g is None:
-            n_int = 3 * R + 4 * R + R + sum(R * w for w in self._table_widths) + G * R
+            n_int = 4 * R + 4 * R + R + sum(R * w for w in self._table_widths) + G * R
             static = torch.zeros(n_int, dtype=torch.int32, device=self.device)
-            batch = build_step_batch(entries, ctx_lens, slots, tables, slot_maps, static=static, **args)
-            if device_tokens is not None:
-                batch.tokens.copy_(device_tokens, non_blocking=True)
+            batch = build_step_batch(entries, ctx_lens, slots, tables, slot_maps, static=static, token_map=token_map, **args)
+            self._feed(batch.tokens, batch.token_map, device_tokens, token_map)
             self.model.forward(batch, self.storage)            # warm-up: allocations, plans, lazy set-up
             torch.cuda.synchronize()
             from ..kernels import library
@@ -193,11 +204,10 @@ class ModelRunner:
             with torch.cuda.graph(graph):
                 logits = self.model.forward(batch, self.storage)
             g = self._graphs[R] = dict(graph=graph, static=static, logits=logits, tokens=batch.tokens,
-                                       launches=library.launches[0] - before)
+                                       token_map=batch.token_map, launches=library.launches[0] - before)
         else:
-            build_step_batch(entries, ctx_lens, slots, tables, slot_maps, static=g["static"], **args)
-            if device_tokens is not None:
-                g["tokens"].copy_(device_tokens, non_blocking=True)
+            build_step_batch(entries, ctx_lens, slots, tables, slot_maps, static=g["static"], token_map=token_map, **args)
+            self._feed(g["tokens"], g["token_map"], device_tokens, token_map)
         g["graph"].replay()
         from ..kernels import library
         library.launches[0] += g["launches"]

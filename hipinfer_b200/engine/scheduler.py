@@ -162,6 +162,15 @@ class Scheduler:
             admitted += 1
         return out
 
+    def finish(self, req: Request, reason: str) -> None:
+        """End a running request now (a stop condition noticed outside update): free its cache."""
+        req.status, req.finish_reason = FINISHED, reason
+        if req in self.running:
+            self.running.remove(req)
+        if self.cache.has_request(req.request_id):
+            self.cache.free_request(req.request_id)
+        self.finished.append(req)
+
     # ---------------------------------------------------------------- after the step
     def update(self, scheduled: Sequence[Scheduled], sampled: Sequence[int]) -> List[Request]:
         """Record a step's result. `sampled` has one token per entry with samples=True, in order.

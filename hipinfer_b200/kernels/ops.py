@@ -31,6 +31,7 @@ _SIGS = {
         "hb_attn_merge": [_p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p, _p, _i, _p],
         "hb_sample": [_p, _l, _i, _i, _p, _p, _p, _p, _p, _p],
         "hb_convert": [_p, _i, _p, _i, _l, _p],
+        "hb_feed_tokens": [_p, _p, _p, _i, _p],
     },
 }
 _fn_cache = {}
@@ -236,6 +237,14 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], seed: Opti
     _call("core", "hb_sample", logits.data_ptr(), logits.stride(0), R, V, _ptr(temperature), _ptr(seed),
           _ptr(position), out.data_ptr(), _ptr(ws), _stream())
     return out
+
+
+def feed_tokens(tokens: torch.Tensor, src: torch.Tensor, token_map: torch.Tensor) -> torch.Tensor:
+    """tokens[i] = src[token_map[i]] where token_map[i] >= 0 (all int32 on the device)."""
+    _need_cuda(tokens, src, token_map)
+    assert tokens.dtype == src.dtype == token_map.dtype == torch.int32 and token_map.numel() == tokens.numel()
+    _call("core", "hb_feed_tokens", tokens.data_ptr(), src.data_ptr(), token_map.data_ptr(), tokens.numel(), _stream())
+    return tokens
 
 
 def convert(src: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:

@@ -36,16 +36,22 @@ class Sampler:
     def __init__(self, device):
         self.device = device
 
-    def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], positions: Sequence[int]) -> List[int]:
-        """One token per row of float32 logits [R, V]; positions[r] is the position the new token will take."""
+    def sample_device(self, logits: torch.Tensor, params: Sequence[SamplingParams], positions: Sequence[int]
+                      ) -> torch.Tensor:
+        """One token per row of float32 logits [R, V], left on the device (int32 [R]);
+        positions[r] is the position the new token will take."""
         R = logits.shape[0]
-        if R == 0:
-            return []
         if all(p.temperature == 0 for p in params):
-            return ops.sample(logits, None, None, None).cpu().tolist()
+            return ops.sample(logits, None, None, None)
         host = torch.empty(3, R, dtype=torch.int32, pin_memory=True)
         host[0] = torch.tensor([p.temperature for p in params], dtype=torch.float32).view(torch.int32)
         host[1] = torch.tensor([p.seed & 0x7FFFFFFF for p in params], dtype=torch.int32)
         host[2] = torch.tensor(list(positions), dtype=torch.int32)
         dev = host.to(self.device, non_blocking=True)
-        return ops.sample(logits, dev[0].view(torch.float32), dev[1], dev[2]).cpu().tolist()
+        return ops.sample(logits, dev[0].view(torch.float32), dev[1], dev[2])
+
+    def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], positions: Sequence[int]) -> List[int]:
+        """The same, brought to the host (this waits for the device)."""
+        if logits.shape[0] == 0:
+            return []
+        return self.sample_device(logits, params, positions).cpu().tolist()

@@ -145,6 +145,32 @@ def test_first_tokens_of_a_sequence(folders, which, dtype):
     tiny.assert_logits_close(two, ref, dtype, "two and two")
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_pipelined_steps_match_synchronous_ones(folders, dtype):
+    """Launching a step before the tokens of the one before it have been read back changes
+    nothing: same tokens, a stop token ends a request at the same place, pages all come back."""
+    from hipinfer_b200 import Engine
+
+    folder, cfg, w = folders["c"]
+    prompts = [tiny.random_tokens(n, cfg["vocab_size"], 90 + i) for i, n in enumerate((40, 3, 70, 21, 9))]
+    outs = {}
+    for pipeline in (False, True):
+        eng = Engine(folder, dtype=dtype, max_batch=3, max_seq=256, max_prefill=32, num_pages=20, pipeline=pipeline)
+        free = eng.generate(prompts, 25, temperature=0.7, seed=3)
+        stop = free[0][7]                                   # a token the first request produces on the way
+        ids = [eng.add_request(p, 25, temperature=0.7, seed=3, stop_token_ids=[stop]) for p in prompts]
+        res = eng.run()
+        outs[pipeline] = (free, [res[i] for i in ids])
+        eng.runner.cache.check()
+        assert eng.runner.cache.free_pages() == [20] and eng.runner.cache.slots.free_count == 3
+        eng.close()
+        first = res[ids[0]]
+        assert first[-1] == stop and stop not in first[:-1] and len(first) <= 8
+        for i, f in zip(ids, free):                          # a stopped request is a prefix of the free one
+            assert res[i] == f[:len(res[i])] and (len(res[i]) == 25 or res[i][-1] == stop)
+    assert outs[False] == outs[True]
+
+
 def test_slot_calls_and_bad_arguments(folders):
     """prefill / decode / history / logits / prefill_logits as in the reference's binding
     (scripts/hipinfer.py:392-440), and ValueError for bad arguments (386-390)."""
