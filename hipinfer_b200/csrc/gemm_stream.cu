@@ -61,7 +61,7 @@ template <int NT, bool DEEP>
 __global__ void __launch_bounds__(192) gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w,
                                                           const __grid_constant__ CUtensorMap map_x, void* C, long ldc,
                                                           int M, int N, int K, int kslice, float* ws, int* counters,
-                                                          int epi, int* status) {
+                                                          int epi, int* status, int defer) {
   using S = StreamCfg<NT, DEEP>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -173,7 +173,7 @@ __global__ void __launch_bounds__(192) gemm_stream_kernel(const __grid_constant_
     if (threadIdx.x == 0) atomicExch(status, 1);
     __nanosleep(100000);
   }
-  if (ksplit == 1) return;
+  if (ksplit == 1 || defer) return;  // defer: stream_reduce_kernel adds the slices, with the whole GPU
 
   if (threadIdx.x == 0) *is_last = atomicAdd(&counters[nb], 1) == ksplit - 1;
   __syncthreads();
@@ -219,6 +219,50 @@ __global__ void __launch_bounds__(192) gemm_stream_kernel(const __grid_constant_
   if (threadIdx.x == 0) HB_STAMP(9);
 }
 
+// The slices' partial sums added in slice order and the epilogue applied, four columns per thread,
+// over the whole output at once. With many token rows this is much more work than one CTA per
+// column block should do at the end of the product kernel, so it runs as a kernel of its own.
+__global__ void __launch_bounds__(256) stream_reduce_kernel(const float* __restrict__ ws, void* C, long ldc, int M, int N,
+                                                            int NP, int NT, int ksplit, int epi) {
+  hb_pdl_launch();
+  hb_pdl_wait();
+  const int per_row = NP >> 2;
+  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long)M * per_row) return;
+  const int m = (int)(idx / per_row), n = (int)(idx - (long)m * per_row) * 4;
+  const bool gate = (n & 16) == 0, swiglu = epi == ST_SWIGLU_BF16;
+  if (n >= N || (swiglu && !gate)) return;
+  const size_t slice_stride = (size_t)NT * NP;
+  const float* p = ws + (size_t)m * NP + n;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f), up = acc;
+  int sl = 0;
+  for (; sl + 4 <= ksplit; sl += 4) {
+    float4 a[4], u[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      a[j] = __ldcg((const float4*)(p + (sl + j) * slice_stride));
+      if (swiglu) u[j] = __ldcg((const float4*)(p + (sl + j) * slice_stride + 16));
+    }
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      acc.x += a[j].x; acc.y += a[j].y; acc.z += a[j].z; acc.w += a[j].w;
+      if (swiglu) { up.x += u[j].x; up.y += u[j].y; up.z += u[j].z; up.w += u[j].w; }
+    }
+  }
+  for (; sl < ksplit; sl++) {
+    const float4 a = __ldcg((const float4*)(p + sl * slice_stride));
+    acc.x += a.x; acc.y += a.y; acc.z += a.z; acc.w += a.w;
+    if (swiglu) {
+      const float4 u = __ldcg((const float4*)(p + sl * slice_stride + 16));
+      up.x += u.x; up.y += u.y; up.z += u.z; up.w += u.w;
+    }
+  }
+  stream_store(epi, C, ldc, m, n, N, acc.x, up.x, gate);
+  stream_store(epi, C, ldc, m, n + 1, N, acc.y, up.y, gate);
+  stream_store(epi, C, ldc, m, n + 2, N, acc.z, up.z, gate);
+  stream_store(epi, C, ldc, m, n + 3, N, acc.w, up.w, gate);
+}
+
 // The split of K for an [N, K] weight: a function of the weight's shape alone.
 static void stream_plan(int N, int K, int sms, int* kslice, int* ksplit) {
   const int n_blocks = (N + ST_ROWS - 1) / ST_ROWS;
@@ -246,6 +290,7 @@ HB_EXPORT int hb_gemm_stream_plan(int N, int K, int* kslice, int* ksplit, long* 
 template <int NT, bool DEEP>
 static int launch_stream(const CUtensorMap& mw, const CUtensorMap& mx, void* C, long ldc, int M, int N, int K, int kslice,
                          int ksplit, int n_blocks, float* ws, int* counters, int epi, int* status, cudaStream_t s) {
+  const int defer = ksplit > 1 && NT > 16;   // many token rows: the slices are added by a kernel of its own
   using S = StreamCfg<NT, DEEP>;
   auto kern = gemm_stream_kernel<NT, DEEP>;
   static bool configured = false;
@@ -255,8 +300,15 @@ static int launch_stream(const CUtensorMap& mw, const CUtensorMap& mx, void* C, 
     configured = true;
   }
   cudaError_t e = hb_launch(kern, dim3(n_blocks, ksplit), 192, S::TOTAL, s, mw, mx, C, ldc, M, N, K, kslice, ws, counters,
-                            epi, status);
+                            epi, status, defer);
   if (e != cudaSuccess) HB_FAIL("hb_gemm_stream: %s", cudaGetErrorString(e));
+  if (defer) {
+    const int NP = n_blocks * ST_ROWS;
+    const long items = (long)M * (NP / 4);
+    e = hb_launch(stream_reduce_kernel, (unsigned)((items + 255) / 256), 256, 0, s, (const float*)ws, C, ldc, M, N, NP, NT,
+                  ksplit, epi);
+    if (e != cudaSuccess) HB_FAIL("hb_gemm_stream: %s", cudaGetErrorString(e));
+  }
   return 0;
 }
 
