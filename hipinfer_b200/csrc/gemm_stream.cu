@@ -290,7 +290,7 @@ HB_EXPORT int hb_gemm_stream_plan(int N, int K, int* kslice, int* ksplit, long* 
 template <int NT, bool DEEP>
 static int launch_stream(const CUtensorMap& mw, const CUtensorMap& mx, void* C, long ldc, int M, int N, int K, int kslice,
                          int ksplit, int n_blocks, float* ws, int* counters, int epi, int* status, cudaStream_t s) {
-  const int defer = ksplit > 1 && NT > 16;   // many token rows: the slices are added by a kernel of its own
+  const int defer = ksplit > 1 && M >= 8;  // from 8 token rows on (measured) the slices are added by a kernel of its own
   using S = StreamCfg<NT, DEEP>;
   auto kern = gemm_stream_kernel<NT, DEEP>;
   static bool configured = false;
