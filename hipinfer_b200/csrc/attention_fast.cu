@@ -110,13 +110,13 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
     const float mn = fmaxf(m_run, mx * scale_log2);   // finite: the pass has at least one key
-    const float corr = exp2f(m_run - mn);
+    const float corr = hb_exp2(m_run - mn);
     m_run = mn;
     float sum = 0.f;
     uint32_t pf[4][4];
 #pragma unroll
     for (int i = 0; i < 8; i++) {
-      const float p0 = exp2f(sc[i][0] * scale_log2 - mn), p1 = exp2f(sc[i][1] * scale_log2 - mn);
+      const float p0 = hb_exp2(sc[i][0] * scale_log2 - mn), p1 = hb_exp2(sc[i][1] * scale_log2 - mn);
       sum += p0 + p1;
       pf[i >> 1][(i & 1) * 2] = hb_pack_bf16(p0, p1);
       pf[i >> 1][(i & 1) * 2 + 1] = 0u;  // rows 8..15 of the tile are padding
@@ -159,7 +159,7 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
     float a = 0.f, l = 0.f;
 #pragma unroll
     for (int w = 0; w < AD_WARPS; w++) {
-      const float f = exp2f(red_ml[(w * G + gg) * 2] - m);  // 0 for a warp without keys
+      const float f = hb_exp2(red_ml[(w * G + gg) * 2] - m);  // 0 for a warp without keys
       a += red_o[(w * G + gg) * D + d] * f;
       l += red_ml[(w * G + gg) * 2 + 1] * f;
     }

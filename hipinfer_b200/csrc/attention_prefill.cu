@@ -13,6 +13,9 @@
 // Requests whose portion has fewer than `min_rows` rows are left to the row kernel.
 #include "tc_common.cuh"
 
+#ifndef HB_FP_MINB
+#define HB_FP_MINB 4
+#endif
 constexpr int FP_BQ = 64, FP_BKV = 64, FP_THREADS = 128;
 
 template <int D> __device__ __forceinline__ uint32_t fp_swz(int row, int chunk) {
@@ -39,14 +42,15 @@ __device__ __forceinline__ void fp_load_tile(uint32_t tile, const __nv_bfloat16*
 }
 
 template <int D>
-__global__ void __launch_bounds__(FP_THREADS) flash_prefill_kernel(
+__global__ void __launch_bounds__(FP_THREADS, HB_FP_MINB) flash_prefill_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc,
     const int* __restrict__ bt, int bt_stride, const int* __restrict__ q_start, const int* __restrict__ q_len,
     const int* __restrict__ ctx_len, __nv_bfloat16* __restrict__ out, int Hq, int Hkv, int page_size, int window,
     float scale_log2, int min_rows) {
   constexpr int CH = D / 8, KS = D / 16, NT_O = D / 8, TILE = FP_BKV * D * 2;
   extern __shared__ __align__(128) uint8_t smem[];
-  const int req = blockIdx.z, hq = blockIdx.y, qt = blockIdx.x;
+  // the last query tiles of a portion have the most keys to walk: they are started first
+  const int req = blockIdx.z, hq = blockIdx.y, qt = gridDim.x - 1 - blockIdx.x;
   const int n_rows = q_len[req];
   if (n_rows < min_rows || qt * FP_BQ >= n_rows) return;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
@@ -135,14 +139,14 @@ __global__ void __launch_bounds__(FP_THREADS) flash_prefill_kernel(
     mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
     const float mn_a = fmaxf(m0, mx_a * scale_log2), mn_b = fmaxf(m1, mx_b * scale_log2);
     const float sub_a = mn_a == -INFINITY ? 0.f : mn_a, sub_b = mn_b == -INFINITY ? 0.f : mn_b;
-    const float corr_a = exp2f(m0 - sub_a), corr_b = exp2f(m1 - sub_b);
+    const float corr_a = hb_exp2(m0 - sub_a), corr_b = hb_exp2(m1 - sub_b);
     m0 = mn_a; m1 = mn_b;
     float sum_a = 0.f, sum_b = 0.f;
     uint32_t pf[4][4];  // P as A-fragments: 4 steps of 16 keys
 #pragma unroll
     for (int i = 0; i < 8; i++) {
-      const float p0 = exp2f(s[i][0] * scale_log2 - sub_a), p1 = exp2f(s[i][1] * scale_log2 - sub_a);
-      const float p2 = exp2f(s[i][2] * scale_log2 - sub_b), p3 = exp2f(s[i][3] * scale_log2 - sub_b);
+      const float p0 = hb_exp2(s[i][0] * scale_log2 - sub_a), p1 = hb_exp2(s[i][1] * scale_log2 - sub_a);
+      const float p2 = hb_exp2(s[i][2] * scale_log2 - sub_b), p3 = hb_exp2(s[i][3] * scale_log2 - sub_b);
       sum_a += p0 + p1;
       sum_b += p2 + p3;
       pf[i >> 1][(i & 1) * 2] = hb_pack_bf16(p0, p1);

@@ -179,3 +179,11 @@ __device__ __forceinline__ uint32_t hb_pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *(uint32_t*)&v;
 }
+
+// 2^x by the special-function unit alone (2 ulp; -inf gives 0): the softmax of the tensor-core
+// attention kernels, whose probabilities are rounded to bf16 anyway.
+__device__ __forceinline__ float hb_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
