@@ -213,6 +213,45 @@ def prefill_flops(layers: int) -> float:
     return linear + attention + 2.0 * V * H
 
 
+def breakdown(layers: int, batch: int) -> int:
+    """Per-kernel device time of decode steps at `batch` (a table on stdout, not the JSON line):
+    ten graph-replayed steps under torch's CUPTI profiler, launches made ordinary
+    (HIPINFER_B200_PDL=0 is set here) so that kernels do not overlap and their times add up."""
+    os.environ["HIPINFER_B200_PDL"] = "0"
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+
+    from hipinfer_b200.engine import StepEntry
+    from hipinfer_b200.kernels import ops
+
+    eng = build_engine(layers, max(batch, 2), 64)
+    runner = eng.runner
+    ids = [("bd", i) for i in range(batch)]
+    first = [ops.sample(runner.step([StepEntry(rid, p, [PROMPT_LEN - 1])]), None, None, None)
+             for rid, p in zip(ids, prompts(batch, 1))]
+    tokens = torch.cat(first).contiguous()
+    entries = [StepEntry(rid, [0], [0]) for rid in ids]
+
+    def one():
+        ops.sample(runner.step(entries, device_tokens=tokens), None, None, None, out=tokens)
+
+    for _ in range(5):
+        one()
+    torch.cuda.synchronize()
+    n = 10
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(n):
+            one()
+        torch.cuda.synchronize()
+    rows = [(e.key, e.device_time_total / n, e.count / n) for e in prof.key_averages() if e.device_time_total > 0]
+    total = sum(r[1] for r in rows)
+    print(f"decode step at batch {batch}, context {PROMPT_LEN}+: {total:.1f} us of kernel time per step (launches do not overlap)")
+    for name, us, cnt in sorted(rows, key=lambda r: -r[1]):
+        print(f"{us:9.1f} us  {100 * us / total:5.1f} %  {cnt:6.1f} launches  {us / cnt:7.2f} us each  {name[:70]}")
+    eng.close()
+    return 0
+
+
 def reference_arm(a) -> int:
     """The unmodified reference through its own API. It is installed offline into baseline/_ref by
     the one pip command the contract names; where that cannot be done this arm says so."""
@@ -239,12 +278,15 @@ def main() -> int:
                     help="fewer layers than the configuration has (both numbers are reported)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 decode points")
+    ap.add_argument("--breakdown", action="store_true", help="print per-kernel times of a decode step and exit")
     a = ap.parse_args()
     if a.impl == "reference":
         return reference_arm(a)
     if a.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {a.gpus} is not supported")
         return 2
+    if a.breakdown:
+        return breakdown(a.layers, a.batch)
     if a.warmup < 3:
         a.warmup = 3
     import torch
