@@ -69,8 +69,10 @@ class ModelRunner:
         spec = get_architecture(config.architecture).build_spec(config)
         from ..parts.spec import spec_param_specs
 
+        dt = kw.get("dtype", "bfloat16")
+        exact = (DTYPES[dt] if isinstance(dt, str) else dt) == torch.float32
         tensors = load_weights(folder, spec_param_specs(spec), device=kw.get("device", "cuda:0"),
-                               ignore=_ignorable(spec))
+                               ignore=_ignorable(spec), half_as=torch.float32 if exact else torch.bfloat16)
         return cls(config, tensors, **kw)
 
     @classmethod

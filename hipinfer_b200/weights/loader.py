@@ -54,10 +54,13 @@ class WeightError(ValueError):
         super().__init__("\n".join(lines))
 
 
-def storage_dtype(dt: torch.dtype) -> torch.dtype:
-    """The dtype a stored tensor is kept in."""
-    if dt in (torch.float16, torch.bfloat16):
+def storage_dtype(dt: torch.dtype, half_as: torch.dtype = torch.bfloat16) -> torch.dtype:
+    """The dtype a stored tensor is kept in. `half_as` is where IEEE half goes: bfloat16 (the
+    rule), or float32 for the 32-bit engine, which would otherwise lose three bits of every weight."""
+    if dt == torch.bfloat16:
         return torch.bfloat16
+    if dt == torch.float16:
+        return half_as
     if dt in (torch.float32, torch.float64):
         return torch.float32
     return torch.int32
@@ -75,8 +78,8 @@ def check_names(folder: str, specs: Sequence[ParamSpec], have: Dict[str, Tuple[i
         raise WeightError(folder, sorted(missing), sorted(unexpected), sorted(wrong))
 
 
-def load_weights(folder: str, specs: Sequence[ParamSpec], device="cpu", ignore: Iterable[str] = ()
-                 ) -> Dict[str, torch.Tensor]:
+def load_weights(folder: str, specs: Sequence[ParamSpec], device="cpu", ignore: Iterable[str] = (),
+                 half_as: torch.dtype = torch.bfloat16) -> Dict[str, torch.Tensor]:
     """{name: tensor on `device`} for every spec, after the whole-list check."""
     try:
         files = ModelFiles(folder)
@@ -90,7 +93,7 @@ def load_weights(folder: str, specs: Sequence[ParamSpec], device="cpu", ignore: 
             if s.name not in have:
                 continue
             t = files.get(s.name)
-            out[s.name] = t.to(storage_dtype(t.dtype)).to(device)
+            out[s.name] = t.to(storage_dtype(t.dtype, half_as)).to(device)
         return out
     finally:
         files.close()

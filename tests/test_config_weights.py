@@ -101,6 +101,8 @@ def test_storage_policy(tmp_path):
     assert w["h"].dtype == torch.bfloat16 and w["b"].dtype == torch.bfloat16
     assert w["f"].dtype == torch.float32 and torch.equal(w["f"], t["f"])
     assert w["i"].dtype == torch.int32 and w["i"].tolist() == [0, 1, 2, 3]
+    exact = load_weights(str(tmp_path), [ParamSpec(k, (4,)) for k in t], half_as=torch.float32)   # the 32-bit engine
+    assert exact["h"].dtype == torch.float32 and torch.equal(exact["h"], t["h"].float()) and exact["b"].dtype == torch.bfloat16
 
 
 def test_random_model_folder_and_seed(tmp_path):
