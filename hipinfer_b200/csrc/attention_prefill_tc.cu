@@ -1,0 +1,318 @@
+// Causal flash attention of prompt portions on the 5th-generation tensor cores (head_dim 64).
+//
+// One CTA = 128 consecutive query rows of one request and one query head; it walks the
+// request's keys in tiles of 128 ABSOLUTE positions. Six warps:
+//   warp 4 (one thread)  TMA: the Q tile once, then per tile the K pages and the V pages, each
+//                        page one box of the cache's tensor map (128-byte swizzle, no multicast);
+//   warp 5 (one thread)  tcgen05.mma: S = Q K^T into tensor memory, and, once the softmax
+//                        warps have written P, O_tile = P V (V is read as an MN-major operand
+//                        straight from its [key][d] page layout);
+//   warps 0-3            softmax: a thread owns one query ROW: it reads its row of S from
+//                        tensor memory (no shuffles for max or sum), masks on absolute positions,
+//                        exponentiates in the exp2 domain in fp32, writes P as bf16 into shared
+//                        memory in the swizzled K-major layout the tensor core reads, and keeps
+//                        the output row in registers: o = o * 2^(m_old - m_new) + O_tile.
+// S and the output tile are double-buffered in tensor memory and K, V in shared memory: the
+// scores of tile i + 1 are computed while the softmax of tile i runs, and the output tile of
+// tile i is added one tile late, so a softmax thread never waits for the tensor core. Because tiles are cut at absolute
+// positions and a row's running max and sum are its own, a row's result does not depend on how
+// the prompt was cut or on what else is in the batch. Replaces flash_prefill_mma_kernel of the
+// reference (src/kernels.cuh:1335-1482). Every wait is bounded.
+#include "tc_common.cuh"
+
+constexpr int FT_BM = 128, FT_BN = 128, FT_D = 64;
+constexpr int FT_TILE = 128 * 64 * 2;  // one [128][64] bf16 tile: 16 KB
+
+// MN-major operand with the 128-byte swizzle: 64 contiguous elements of the MN dimension per row,
+// eight K rows per 1,024-byte group (stride SBO); further MN atoms would lie LBO apart (one here).
+__device__ __forceinline__ uint64_t ft_desc_mn128(uint32_t smem_addr) {
+  return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)(FT_TILE >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
+         ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// kind::f16 instruction descriptor as hb_umma_idesc_bf16, with B read MN-major.
+__host__ __device__ constexpr uint32_t ft_idesc_b_mn(int M, int N) { return hb_umma_idesc_bf16(M, N) | (1u << 16); }
+
+#ifdef HB_FT_TIMING
+__device__ unsigned long long g_ft_stamps[256];
+__device__ __forceinline__ void ft_stamp(int i) {
+  if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && i < 256) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    g_ft_stamps[i] = t;
+  }
+}
+HB_EXPORT int hb_ft_stamps(unsigned long long* out) {
+  return cudaMemcpyFromSymbol(out, g_ft_stamps, sizeof(g_ft_stamps)) == cudaSuccess ? 0 : -1;
+}
+#define FT_STAMP(i) ft_stamp(i)
+#else
+#define FT_STAMP(i)
+#endif
+
+struct FtBars {
+  uint64_t q_full, k_full[2], k_free[2], v_full[2], v_free[2], s_full[2], s_free[2], o_full[2], o_free[2], p_full, p_free;
+  uint32_t tmem_slot;
+  int abort_flag;
+};
+
+// Buffers that alternate tile by tile: index i & 1, phase (i >> 1) & 1.
+#define FT_B(i) ((i) & 1)
+#define FT_PH(i) (((i) >> 1) & 1)
+
+__global__ void __launch_bounds__(192, 1) flash_prefill_tc_kernel(
+    const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+    const __grid_constant__ CUtensorMap map_v, const int* __restrict__ bt, int bt_stride, const int* __restrict__ q_start,
+    const int* __restrict__ q_len, const int* __restrict__ ctx_len, __nv_bfloat16* __restrict__ out, int Hq, int Hkv,
+    int page_size, int window, float scale_log2, int min_rows, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* sQ = smem;                  // [128][64]
+  uint8_t* sK = sQ + FT_TILE;          // two stages of [128 keys][64]
+  uint8_t* sV = sK + 2 * FT_TILE;      // two stages of [128 keys][64]
+  uint8_t* sP = sV + 2 * FT_TILE;      // two K blocks of [128 rows][64 keys]
+  FtBars* bar = (FtBars*)(sP + 2 * FT_TILE);
+  volatile int* abort_flag = &bar->abort_flag;
+
+  // the last query tiles of a portion have the most keys to walk: they are started first
+  const int req = blockIdx.z, hq = blockIdx.y, qt = gridDim.x - 1 - blockIdx.x;
+  const int n_rows = q_len[req];
+  if (n_rows < min_rows || qt * FT_BM >= n_rows) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = hq / (Hq / Hkv);
+  const int row0 = q_start[req] + qt * FT_BM, rows_here = min(FT_BM, n_rows - qt * FT_BM);
+  const int p_first = ctx_len[req] + qt * FT_BM, p_last = p_first + rows_here - 1;
+  const int lo = window > 0 ? max(0, p_first - window + 1) : 0;
+  const int kt_lo = lo / FT_BN, kt_hi = p_last / FT_BN, n_tiles = kt_hi - kt_lo + 1;
+  const int* table = bt + (size_t)req * bt_stride;
+
+  if (threadIdx.x == 0) {
+    hb_mbar_init(&bar->q_full, 1);
+    for (int b = 0; b < 2; b++) {
+      hb_mbar_init(&bar->k_full[b], 1); hb_mbar_init(&bar->k_free[b], 1);
+      hb_mbar_init(&bar->v_full[b], 1); hb_mbar_init(&bar->v_free[b], 1);
+      hb_mbar_init(&bar->s_full[b], 1); hb_mbar_init(&bar->s_free[b], 128);
+      hb_mbar_init(&bar->o_full[b], 1); hb_mbar_init(&bar->o_free[b], 128);
+    }
+    hb_mbar_init(&bar->p_full, 128); hb_mbar_init(&bar->p_free, 1);
+    bar->abort_flag = 0;
+    hb_fence_barrier_init();
+  }
+  // masked keys of a last, ragged tile are never loaded: what the tensor core reads in their place
+  // must be finite (P is exactly 0 there, and 0 * NaN would poison the row)
+  for (int i = threadIdx.x; i < 4 * FT_TILE / 16; i += 192) ((uint4*)sK)[i] = make_uint4(0, 0, 0, 0);
+  if (warp == 5) {
+    hb_tmem_alloc(&bar->tmem_slot, 512);
+    hb_tmem_relinquish();
+  }
+  if (warp == 4 && lane == 0) { hb_tma_prefetch_desc(&map_q); hb_tma_prefetch_desc(&map_k); hb_tma_prefetch_desc(&map_v); }
+  hb_fence_proxy_async();
+  hb_tc_fence_before();
+  __syncthreads();
+  hb_tc_fence_after();
+  const uint32_t tmem_s = bar->tmem_slot, tmem_o = tmem_s + 2 * FT_BN;  // S: 2 x 128 columns, O: 2 x 64
+
+  if (warp == 4) {  // ---------------- TMA: lane l brings page l of the tile (the page ids come in one load)
+    if (lane == 0) {
+      hb_mbar_expect_tx(&bar->q_full, FT_TILE);
+      hb_tma_load_2d(sQ, &map_q, &bar->q_full, hq * FT_D, row0);
+    }
+    for (int i = 0; i < n_tiles; i++) {
+      const int k_base = (kt_lo + i) * FT_BN, b = FT_B(i);
+      const int first_page = max(k_base, lo) / page_size, last_page = min(k_base + FT_BN - 1, p_last) / page_size;
+      const int np = last_page - first_page + 1;
+      const uint32_t bytes = (uint32_t)np * page_size * FT_D * 2;
+      const int pg = first_page + lane;
+      const int row = lane < np ? (table[pg] * Hkv + h) * page_size : 0;
+      const int off = b * FT_TILE + (pg * page_size - k_base) * FT_D * 2;
+      int ok = 1;
+      if (lane == 0) {
+        ok = hb_mbar_wait(&bar->k_free[b], FT_PH(i) ^ 1, abort_flag);
+        if (ok) hb_mbar_expect_tx(&bar->k_full[b], bytes);
+      }
+      if (!__shfl_sync(0xffffffffu, ok, 0)) break;
+      if (lane < np) hb_tma_load_2d(sK + off, &map_k, &bar->k_full[b], 0, row);
+      if (lane == 0) {
+        ok = hb_mbar_wait(&bar->v_free[b], FT_PH(i) ^ 1, abort_flag);
+        if (ok) hb_mbar_expect_tx(&bar->v_full[b], bytes);
+      }
+      if (!__shfl_sync(0xffffffffu, ok, 0)) break;
+      if (lane < np) hb_tma_load_2d(sV + off, &map_v, &bar->v_full[b], 0, row);
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {  // ---------------- tensor cores: S_i is issued before O_{i-1}, so it overlaps the softmax of tile i - 1
+      constexpr uint32_t idesc_s = hb_umma_idesc_bf16(FT_BM, FT_BN), idesc_o = ft_idesc_b_mn(FT_BM, FT_D);
+      bool ok = hb_mbar_wait(&bar->q_full, 0, abort_flag);
+      for (int i = 0; i <= n_tiles && ok; i++) {
+        if (i < n_tiles) {
+          const int b = FT_B(i);
+          if (!hb_mbar_wait(&bar->k_full[b], FT_PH(i), abort_flag) || !hb_mbar_wait(&bar->s_free[b], FT_PH(i) ^ 1, abort_flag)) break;
+          hb_tc_fence_after();
+          const uint64_t dq = hb_umma_desc_k128(hb_smem_u32(sQ)), dk = hb_umma_desc_k128(hb_smem_u32(sK + b * FT_TILE));
+#pragma unroll
+          for (int k = 0; k < FT_D / 16; k++) hb_umma_bf16(tmem_s + b * FT_BN, dq + 2 * k, dk + 2 * k, idesc_s, k != 0);
+          hb_umma_commit(&bar->s_full[b]);
+          hb_umma_commit(&bar->k_free[b]);
+        }
+        if (i > 0) {
+          const int j = i - 1, b = FT_B(j);
+          if (!hb_mbar_wait(&bar->p_full, j & 1, abort_flag) || !hb_mbar_wait(&bar->v_full[b], FT_PH(j), abort_flag) ||
+              !hb_mbar_wait(&bar->o_free[b], FT_PH(j) ^ 1, abort_flag))
+            break;
+          hb_tc_fence_after();
+#pragma unroll
+          for (int k = 0; k < FT_BN / 16; k++) {
+            const uint64_t dp = hb_umma_desc_k128(hb_smem_u32(sP + (k >> 2) * FT_TILE)) + 2 * (k & 3);
+            const uint64_t dv = ft_desc_mn128(hb_smem_u32(sV + b * FT_TILE + k * 16 * FT_D * 2));
+            hb_umma_bf16(tmem_o + b * FT_D, dp, dv, idesc_o, k != 0);
+          }
+          hb_umma_commit(&bar->o_full[b]);
+          hb_umma_commit(&bar->v_free[b]);
+          hb_umma_commit(&bar->p_free);
+        }
+      }
+    }
+  } else {  // ---------------- softmax: thread = query row
+    const int r = warp * 32 + lane;
+    const int qp = p_first + min(r, rows_here - 1);  // rows past the portion's end are computed, never stored
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    float o[FT_D];
+#pragma unroll
+    for (int d = 0; d < FT_D; d++) o[d] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f, corr_prev = 0.f;
+    bool ok = true;
+    for (int i = 0; i <= n_tiles && ok; i++) {
+      float corr = 1.f;
+      if (i < n_tiles) {
+        const int b = FT_B(i), k_base = (kt_lo + i) * FT_BN;
+        const bool need_mask = k_base + FT_BN - 1 > p_first || (window > 0 && k_base < p_last - window + 1);
+        if (threadIdx.x == 0) FT_STAMP(1 + 6 * i);
+        if (!hb_mbar_wait(&bar->s_full[b], FT_PH(i), abort_flag)) break;
+        if (threadIdx.x == 0) FT_STAMP(2 + 6 * i);
+        hb_tc_fence_after();
+        uint32_t sr[128];  // the whole row of S: both halves requested, one wait
+        hb_tmem_ld64_nowait(tmem_s + b * FT_BN + lane_base, sr);
+        hb_tmem_ld64_nowait(tmem_s + b * FT_BN + lane_base + 64, sr + 64);
+        hb_tmem_ld_wait();
+        hb_tmem_ld_fence64(sr);
+        hb_tmem_ld_fence64(sr + 64);
+        hb_tc_fence_before();
+        hb_mbar_arrive(&bar->s_free[b]);  // S is in registers: the scores of tile i + 2 may overwrite it
+        if (threadIdx.x == 0) FT_STAMP(3 + 6 * i);
+        // a softmax warp is alone on its scheduler: four independent chains for the maximum and
+        // for the sum instead of one, and the mask only on the tiles that need one
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        if (need_mask) {
+          const int hi_j = qp - k_base, lo_j = window > 0 ? qp - window - k_base : -1;  // visible iff lo_j < j <= hi_j
+#pragma unroll
+          for (int j = 0; j < 128; j++) {
+            const float v = (j <= hi_j && j > lo_j) ? __uint_as_float(sr[j]) : -INFINITY;
+            sr[j] = __float_as_uint(v);
+            mx4[j & 3] = fmaxf(mx4[j & 3], v);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 128; j++) mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(sr[j]));
+        }
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+        const float m_new = fmaxf(m_run, mx * scale_log2);
+        const float sub = m_new == -INFINITY ? 0.f : m_new;
+        corr = hb_exp2(m_run - sub);
+        m_run = m_new;
+        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int j = 0; j < 128; j += 2) {  // masked scores are -inf: 2^-inf = 0
+          const float p0 = hb_exp2(fmaf(__uint_as_float(sr[j]), scale_log2, -sub));
+          const float p1 = hb_exp2(fmaf(__uint_as_float(sr[j + 1]), scale_log2, -sub));
+          sum4[(j >> 1) & 3] += p0 + p1;
+          sr[j >> 1] = hb_pack_bf16(p0, p1);
+        }
+        const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+        l_run = l_run * corr + sum;
+        if (threadIdx.x == 0) FT_STAMP(4 + 6 * i);
+        if (!hb_mbar_wait(&bar->p_free, (i & 1) ^ 1, abort_flag)) break;
+        // 128 keys = sixteen 16-byte chunks of this row: eight in each K block of P
+#pragma unroll
+        for (int cc = 0; cc < 16; cc++) {
+          const uint32_t dst = hb_smem_u32(sP + (cc >> 3) * FT_TILE) + r * 128 + (((cc & 7) ^ (r & 7)) << 4);
+          asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(sr[4 * cc]), "r"(sr[4 * cc + 1]),
+                       "r"(sr[4 * cc + 2]), "r"(sr[4 * cc + 3]) : "memory");
+        }
+        hb_fence_proxy_async();
+        hb_mbar_arrive(&bar->p_full);
+        if (threadIdx.x == 0) FT_STAMP(5 + 6 * i);
+      }
+      if (i > 0) {  // the output tile of the tile before: o = o * corr_{i-1} + O_{i-1}
+        const int j = i - 1, b = FT_B(j);
+        if (!hb_mbar_wait(&bar->o_full[b], FT_PH(j), abort_flag)) break;
+        if (threadIdx.x == 0) FT_STAMP(6 + 6 * i);
+        hb_tc_fence_after();
+        uint32_t orr[64];
+        hb_tmem_ld64_nowait(tmem_o + b * FT_D + lane_base, orr);
+        hb_tmem_ld_wait();
+        hb_tmem_ld_fence64(orr);
+        hb_tc_fence_before();
+        hb_mbar_arrive(&bar->o_free[b]);
+#pragma unroll
+        for (int d = 0; d < FT_D; d++) o[d] = fmaf(o[d], corr_prev, __uint_as_float(orr[d]));
+      }
+      corr_prev = corr;
+      if (i == n_tiles && r < rows_here) {
+        const float inv = 1.f / l_run;
+        __nv_bfloat16* dst = out + ((size_t)(row0 + r) * Hq + hq) * FT_D;
+#pragma unroll
+        for (int d = 0; d < FT_D; d += 8) {
+          uint4 w;
+          w.x = hb_pack_bf16(o[d] * inv, o[d + 1] * inv); w.y = hb_pack_bf16(o[d + 2] * inv, o[d + 3] * inv);
+          w.z = hb_pack_bf16(o[d + 4] * inv, o[d + 5] * inv); w.w = hb_pack_bf16(o[d + 6] * inv, o[d + 7] * inv);
+          *(uint4*)(dst + d) = w;
+        }
+      }
+    }
+  }
+
+  hb_tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    if (threadIdx.x == 0) atomicExch(status, 1);
+    __nanosleep(100000);
+  }
+  if (warp == 5) {
+    __syncwarp();
+    hb_tmem_dealloc(tmem_s, 512);
+  }
+}
+
+HB_EXPORT int hb_flash_prefill_tc_supported(int Hq, int Hkv, int D, int page_size) {
+  return Hkv > 0 && Hq % Hkv == 0 && D == FT_D && page_size >= 8 && page_size <= FT_BN && (page_size & (page_size - 1)) == 0;
+}
+
+// q, out [T, Hq, 64] bf16; caches [num_pages, Hkv, page_size, 64] bf16; per request q_start, q_len,
+// ctx_len and a block table row, as hb_flash_prefill. Requests with fewer than min_rows rows are
+// skipped. `status` is set to 1 if a bounded wait ran out.
+HB_EXPORT int hb_flash_prefill_tc(const void* q, const void* kc, const void* vc, long num_pages, const int* bt, int bt_stride,
+                                  const int* q_start, const int* q_len, const int* ctx_len, void* out, int T, int R,
+                                  int max_q_len, int Hq, int Hkv, int D, int page_size, int window, float scale,
+                                  int min_rows, int* status, cudaStream_t st) {
+  if (R <= 0 || max_q_len <= 0 || T <= 0) return 0;
+  if (!hb_flash_prefill_tc_supported(Hq, Hkv, D, page_size))
+    HB_FAIL("hb_flash_prefill_tc: %d/%d heads of %d with pages of %d are not supported", Hq, Hkv, D, page_size);
+  if (R > 65535 || Hq > 65535) HB_FAIL("hb_flash_prefill_tc: %d requests / %d heads are beyond the grid limit", R, Hq);
+  if (!status) HB_FAIL("hb_flash_prefill_tc: no status word");
+  CUtensorMap mq, mk, mv;
+  if (hb_make_tensor_map_bf16(&mq, q, (uint64_t)T, (uint64_t)Hq * D, (uint64_t)Hq * D, FT_BM)) return -1;
+  const uint64_t rows = (uint64_t)num_pages * Hkv * page_size;
+  if (hb_make_tensor_map_bf16(&mk, kc, rows, (uint64_t)D, (uint64_t)D, (uint32_t)page_size)) return -1;
+  if (hb_make_tensor_map_bf16(&mv, vc, rows, (uint64_t)D, (uint64_t)D, (uint32_t)page_size)) return -1;
+  const size_t smem = 7 * (size_t)FT_TILE + sizeof(FtBars) + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(flash_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) HB_FAIL("hb_flash_prefill_tc: %s", cudaGetErrorString(e));
+    configured = true;
+  }
+  dim3 grid((max_q_len + FT_BM - 1) / FT_BM, Hq, R);
+  flash_prefill_tc_kernel<<<grid, 192, smem, st>>>(mq, mk, mv, bt, bt_stride, q_start, q_len, ctx_len, (__nv_bfloat16*)out, Hq,
+                                                   Hkv, page_size, window, scale * 1.4426950408889634f, min_rows, status);
+  HB_CHECK_LAUNCH("hb_flash_prefill_tc");
+  return 0;
+}

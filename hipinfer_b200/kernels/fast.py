@@ -29,10 +29,12 @@ _SIGS = {
     "hb_attn_decode": [_p, _p, _p, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _i, _p, _i, _p],
     "hb_flash_prefill": [_p, _p, _p, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p],
     "hb_flash_prefill_supported": [_i, _i, _i],
+    "hb_flash_prefill_tc": [_p, _p, _p, _l, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p, _p],
+    "hb_flash_prefill_tc_supported": [_i, _i, _i, _i],
     "hb_attn_decode_supported": [_i, _i, _i],
 }
 _fns = {}
-_LAUNCHES = {"hb_gemm_stream_fused": 1, "hb_gemm_tc": 1, "hb_gemm_skinny": 1, "hb_gemm_stream": 1, "hb_attn_decode": 1, "hb_flash_prefill": 1}
+_LAUNCHES = {"hb_gemm_stream_fused": 1, "hb_gemm_tc": 1, "hb_gemm_skinny": 1, "hb_gemm_stream": 1, "hb_attn_decode": 1, "hb_flash_prefill": 1, "hb_flash_prefill_tc": 1}
 _status = None
 
 EPI_F32, EPI_BF16, EPI_ADD_F32, EPI_SWIGLU_BF16 = 0, 1, 2, 3
@@ -273,6 +275,23 @@ def flash_prefill(q, k_cache, v_cache, block_table, q_start, q_len, ctx_len, out
     return out
 
 
+FLASH_IMPL = os.environ.get("HIPINFER_B200_FLASH", "tc")      # "tc": tcgen05 where it applies; "mma": warp MMAs only
+
+
+def flash_prefill_tc_supported(n_heads, n_kv_heads, head_dim, page_size) -> bool:
+    return bool(_fn("hb_flash_prefill_tc_supported")(n_heads, n_kv_heads, head_dim, page_size))
+
+
+def flash_prefill_tc(q, k_cache, v_cache, block_table, q_start, q_len, ctx_len, out, max_q_len, n_heads, n_kv_heads,
+                     head_dim, page_size, window, scale, min_rows=1):
+    """The tcgen05 flash kernel for prompt portions (see csrc/attention_prefill_tc.cu); arguments as flash_prefill."""
+    _call("hb_flash_prefill_tc", q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), k_cache.shape[0],
+          block_table.data_ptr(), block_table.stride(0), q_start.data_ptr(), q_len.data_ptr(), ctx_len.data_ptr(),
+          out.data_ptr(), q.shape[0], q_len.numel(), int(max_q_len), n_heads, n_kv_heads, head_dim, page_size, int(window),
+          float(scale), int(min_rows), status_word().data_ptr(), _stream())
+    return out
+
+
 FLASH_MIN_ROWS = 16     # portions of at least this many rows go to the flash kernel, shorter ones to the row kernel
 
 
@@ -283,8 +302,10 @@ def attention(q, k_cache, v_cache, batch, group, out, n_heads, n_kv_heads, head_
     need_rows = not use_flash or min(batch.h_q_len) < FLASH_MIN_ROWS
     bt = batch.block_tables[group]
     if use_flash:
-        flash_prefill(q, k_cache, v_cache, bt, batch.req_q_start, batch.req_q_len, batch.req_ctx_len, out,
-                      batch.max_q_len, n_heads, n_kv_heads, head_dim, page_size, window, scale, FLASH_MIN_ROWS)
+        tc = FLASH_IMPL == "tc" and flash_prefill_tc_supported(n_heads, n_kv_heads, head_dim, page_size)
+        (flash_prefill_tc if tc else flash_prefill)(q, k_cache, v_cache, bt, batch.req_q_start, batch.req_q_len,
+                                                    batch.req_ctx_len, out, batch.max_q_len, n_heads, n_kv_heads,
+                                                    head_dim, page_size, window, scale, FLASH_MIN_ROWS)
     if need_rows:
         attention_decode(q, k_cache, v_cache, bt, batch.row_request, batch.positions, out, n_heads, n_kv_heads,
                          head_dim, page_size, window, scale, batch.max_pos,

@@ -45,7 +45,7 @@ def timeit(fn, iters, flush):
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
-    ap.add_argument("kernel", choices=["gemm_tc", "gemm_stream", "gemm_skinny", "attn_decode", "flash_prefill", "rmsnorm"])
+    ap.add_argument("kernel", choices=["gemm_tc", "gemm_stream", "gemm_skinny", "attn_decode", "flash_prefill", "flash_prefill_tc", "rmsnorm"])
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=16384)
     ap.add_argument("--k", type=int, default=2048)
@@ -109,7 +109,8 @@ def main(argv=None) -> int:
             flops = 4.0 * R * ctx * Hq * D
         else:
             qs, ql, cl = i32([0]), i32(q_len), i32(ctx_len)
-            fn = lambda: fast.flash_prefill(q, kc, vc, bt, qs, ql, cl, o, T, Hq, Hkv, D, ps, 0, scale)
+            impl = fast.flash_prefill_tc if a.kernel == "flash_prefill_tc" else fast.flash_prefill
+            fn = lambda: impl(q, kc, vc, bt, qs, ql, cl, o, T, Hq, Hkv, D, ps, 0, scale)
             nbytes = 2 * ctx * Hkv * D * 2 + 2 * T * Hq * D * 2
             flops = 4.0 * Hq * D * (T * (T + 1) / 2)
         ms = timeit(fn, a.iters, a.flush)

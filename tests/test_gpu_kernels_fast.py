@@ -203,9 +203,15 @@ def test_attention_decode_far_key_stands_out():
     assert float((out.float().cpu().reshape(Hq, D)[0] - vs[0][far, 0]).abs().max()) < 0.05
 
 
+FLASH = ["flash_prefill", "flash_prefill_tc"]
+
+
+@pytest.mark.parametrize("impl", FLASH)
 @pytest.mark.parametrize("Hq,Hkv,D,ps,window", [(8, 2, 64, 16, 0), (3, 1, 128, 16, 0), (4, 4, 64, 8, 0), (6, 2, 64, 16, 100),
-                                                (2, 1, 128, 32, 0)])
-def test_flash_prefill(Hq, Hkv, D, ps, window):
+                                                (2, 1, 128, 32, 0), (5, 1, 64, 32, 0)])
+def test_flash_prefill(Hq, Hkv, D, ps, window, impl):
+    if impl == "flash_prefill_tc" and not fast().flash_prefill_tc_supported(Hq, Hkv, D, ps):
+        pytest.skip("the tcgen05 kernel takes head_dim 64")
     """Portions of several requests in one launch: a whole prompt from position 0 with a ragged
     last tile, a portion in the middle of a sequence that starts inside a page and inside a key
     tile, a long portion behind a long context, and a short portion that must be left alone."""
@@ -219,8 +225,9 @@ def test_flash_prefill(Hq, Hkv, D, ps, window):
     out = torch.full((T, Hq * D), 7.0, dtype=torch.bfloat16, device=DEV)
     starts = [sum(qn[:i]) for i in range(4)]
     i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
-    fast().flash_prefill(q, kc, vc, bt, i32(starts), i32(qn), i32(ctx), out, max(qn), Hq, Hkv, D, ps, window,
-                         1.0 / math.sqrt(D), min_rows=16)
+    getattr(fast(), impl)(q, kc, vc, bt, i32(starts), i32(qn), i32(ctx), out, max(qn), Hq, Hkv, D, ps, window,
+                          1.0 / math.sqrt(D), min_rows=16)
+    sync_check()
     got = out.float().cpu().reshape(T, Hq, D)
     for r in range(3):
         pos = list(range(ctx[r], ctx[r] + qn[r]))
@@ -231,7 +238,8 @@ def test_flash_prefill(Hq, Hkv, D, ps, window):
     assert bool((got[starts[3]:] == 7.0).all()), "the short portion was touched"
 
 
-def test_flash_prefill_far_key_and_cutting():
+@pytest.mark.parametrize("impl", FLASH)
+def test_flash_prefill_far_key_and_cutting(impl):
     """A far key made to stand out comes through; the same rows cut into two portions give the same bits."""
     Hq, Hkv, D, ps = 4, 2, 64, 16
     n = 600
@@ -244,14 +252,17 @@ def test_flash_prefill_far_key_and_cutting():
     ks[0][far, 0] = kc[page, 0, off].float().cpu()
     i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
     whole = torch.empty(n, Hq * D, dtype=torch.bfloat16, device=DEV)
-    fast().flash_prefill(q, kc, vc, bt, i32([0]), i32([n]), i32([0]), whole, n, Hq, Hkv, D, ps, 0, 1 / math.sqrt(D))
+    flash = getattr(fast(), impl)
+    flash(q, kc, vc, bt, i32([0]), i32([n]), i32([0]), whole, n, Hq, Hkv, D, ps, 0, 1 / math.sqrt(D))
+    sync_check()
     ref = plain.attention_scores_softmax_values(qf, ks[0], vs[0], list(range(n)), list(range(n)))
     torch.testing.assert_close(whole.float().cpu().reshape(n, Hq, D), ref, rtol=2e-2, atol=2e-2)
     assert float((whole.float().cpu().reshape(n, Hq, D)[row, 0] - vs[0][far, 0]).abs().max()) < 0.05
     cut = 333
     tail = torch.empty(n - cut, Hq * D, dtype=torch.bfloat16, device=DEV)
-    fast().flash_prefill(q[cut:].contiguous(), kc, vc, bt, i32([0]), i32([n - cut]), i32([cut]), tail, n - cut, Hq, Hkv, D,
-                         ps, 0, 1 / math.sqrt(D))
+    flash(q[cut:].contiguous(), kc, vc, bt, i32([0]), i32([n - cut]), i32([cut]), tail, n - cut, Hq, Hkv, D, ps, 0,
+          1 / math.sqrt(D))
+    sync_check()
     assert torch.equal(tail, whole[cut:])
 
 
