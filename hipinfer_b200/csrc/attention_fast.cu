@@ -19,47 +19,109 @@ template <int D> __device__ __forceinline__ uint32_t ad_swz(int row, int c) {
   return (uint32_t)(row * (D * 2) + ((c ^ (row & 7)) << 4));
 }
 
+// Rows [r_lo, r_hi) of the tile (row r = key k0 + r) by cp.async, page by page: the page
+// numbers of four pages are read first, then every thread copies its 16-byte pieces of them.
+template <int D>
+__device__ __forceinline__ void ad_load_rows(const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc,
+                                             const int* __restrict__ table, int Hkv, int h, int page_size, int k0,
+                                             int r_lo, int r_hi, uint32_t sK, uint32_t sV, int tid) {
+  constexpr int CH = D / 8;
+  if (r_lo >= r_hi) return;
+  const int pg_lo = (k0 + r_lo) / page_size, pg_hi = (k0 + r_hi - 1) / page_size, pieces = page_size * CH;
+  for (int pg0 = pg_lo; pg0 <= pg_hi; pg0 += 4) {
+    int pid[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) pid[j] = pg0 + j <= pg_hi ? __ldg(table + pg0 + j) : 0;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      if (pg0 + j > pg_hi) break;
+      const size_t base = ((size_t)pid[j] * Hkv + h) * page_size * D;
+      const int r_page = (pg0 + j) * page_size - k0;   // tile row of the page's first key
+      for (int i = tid; i < pieces; i += AD_THREADS) {
+        const int rr = i / CH, c = i % CH, r = r_page + rr;
+        if (r < r_lo || r >= r_hi) continue;
+        const uint32_t off = ad_swz<D>(r, c);
+        hb_cp_async16(sK + off, kc + base + (size_t)rr * D + c * 8);
+        hb_cp_async16(sV + off, vc + base + (size_t)rr * D + c * 8);
+      }
+    }
+  }
+}
+
+#ifdef HB_AD_TIMING
+// A timing build: every block of the last launch leaves its time stamps (entry, loads asked for,
+// the wait over, tile in shared memory, end) and the SM it ran on.
+__device__ unsigned long long g_ad_stamps[8192 * 6];
+__device__ __forceinline__ void ad_stamp(int i) {
+  const unsigned b = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+  if (threadIdx.x == 0 && b < 8192) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    if (i == 5) { unsigned sm; asm volatile("mov.u32 %0, %%smid;" : "=r"(sm)); t = sm; }
+    g_ad_stamps[b * 6 + i] = t;
+  }
+}
+HB_EXPORT int hb_ad_stamps(unsigned long long* out) {
+  return cudaMemcpyFromSymbol(out, g_ad_stamps, sizeof(g_ad_stamps)) == cudaSuccess ? 0 : -1;
+}
+#define AD_STAMP(i) ad_stamp(i)
+#else
+#define AD_STAMP(i)
+#endif
+
 // One block = one (key chunk, kv head, row). The chunk's keys and values are requested at once
 // with cp.async into swizzled shared memory; each warp then takes 64 keys: S = Q K^T and
 // O = P V on warp MMAs with the G query heads of the kv head as the rows of the 16-row tile
 // (src/kernels.cuh:1681-1869 does the same on a contiguous cache), softmax in fp32 in the exp2
 // domain, P rounded to bf16 before P V. The warps' (max, sum, O) are combined in warp order.
+//
+// Keys below ctx_len[request] were written by earlier steps, and the step's positions and block
+// tables by a copy that ended before the step's first kernel began: a block asks for those keys
+// and values BEFORE it waits for the kernel ahead of it (which writes this step's keys), so that
+// under programmatic dependent launch the cache streams in while the projections still run.
+// A row that spans several chunks is finished by the block that ends last (a counter per
+// (row, kv head), left at zero again): it adds the chunks' partials in ascending chunk order.
 template <int D, int G>
 __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc,
     const int* __restrict__ bt, int bt_stride, const int* __restrict__ row_req, const int* __restrict__ pos,
     __nv_bfloat16* __restrict__ out, float* __restrict__ part_acc, float* __restrict__ part_ml, int Hq, int Hkv,
-    int page_size, int window, float scale_log2, int chunk, int S, const int* __restrict__ q_len, int row_limit) {
+    int page_size, int window, float scale_log2, int chunk, int S, const int* __restrict__ q_len, int row_limit,
+    const int* __restrict__ ctx_len, int* __restrict__ counters) {
   constexpr int CH = D / 8, KS = D / 16, NT_O = D / 8, WK = 64;  // WK: keys per warp pass
   extern __shared__ __align__(128) uint8_t smem_raw[];
   const uint32_t sK = hb_smem_u32(smem_raw), sV = sK + chunk * D * 2, sQ = sV + chunk * D * 2;
   float* red_o = (float*)(smem_raw + 2 * chunk * D * 2 + 16 * D * 2);  // [warps][G][D]
   float* red_ml = red_o + AD_WARPS * G * D;                             // [warps][G][2]
+  __shared__ int is_last;
   hb_pdl_launch();
-  hb_pdl_wait();
+  AD_STAMP(0);
+  AD_STAMP(5);
   const int t = blockIdx.z, h = blockIdx.y, s = blockIdx.x;
-  if (q_len && q_len[row_req[t]] >= row_limit) return;  // a long portion: the flash kernel's
+  const int rq = row_req[t];
   const int p = pos[t];
   const int lo = window > 0 ? max(0, p - window + 1) : 0;
   const int s_lo = lo / chunk, s_hi = p / chunk;
-  if (s < s_lo || s > s_hi) return;
-  const int k0 = max(s * chunk, lo), k1 = min((s + 1) * chunk, p + 1), nk = k1 - k0;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, tq = lane & 3;
-  const int* table = bt + (size_t)row_req[t] * bt_stride;
-  const int rows_pad = (nk + WK - 1) / WK * WK;  // rows the warps will touch; the tail is zeroed
-  for (int i = tid; i < rows_pad * CH; i += AD_THREADS) {
-    const int r = i / CH, c = i - r * CH, kp = k0 + r;
-    const uint32_t off = ad_swz<D>(r, c);
-    if (r < nk) {
-      const size_t page = table[kp / page_size];
-      const size_t src = ((page * Hkv + h) * page_size + kp % page_size) * D + c * 8;
-      hb_cp_async16(sK + off, kc + src);
-      hb_cp_async16(sV + off, vc + src);
-    } else {
-      asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(sK + off), "r"(0u) : "memory");
-      asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(sV + off), "r"(0u) : "memory");
-    }
+  if ((q_len && q_len[rq] >= row_limit) || s < s_lo || s > s_hi) {  // a long portion (the flash kernel's), or no keys here
+    if ((blockIdx.x | blockIdx.y | blockIdx.z) == 0) hb_pdl_wait();  // the grid never ends before the one ahead of it
+    return;
   }
+  const int k0 = max(s * chunk, lo), k1 = min((s + 1) * chunk, p + 1), nk = k1 - k0;
+  const int n_old = ctx_len ? max(0, min(k1, ctx_len[rq]) - k0) : 0;   // rows of the tile from earlier steps
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, tq = lane & 3;
+  const int* table = bt + (size_t)rq * bt_stride;
+  const int rows_pad = (nk + WK - 1) / WK * WK;  // rows the warps will touch; the tail is zeroed
+  for (int i = nk * CH + tid; i < rows_pad * CH; i += AD_THREADS) {
+    const uint32_t off = ad_swz<D>(i / CH, i % CH);
+    asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(sK + off), "r"(0u) : "memory");
+    asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(sV + off), "r"(0u) : "memory");
+  }
+  ad_load_rows<D>(kc, vc, table, Hkv, h, page_size, k0, 0, n_old, sK, sV, tid);
+  hb_cp_async_commit();
+  AD_STAMP(1);
+  hb_pdl_wait();
+  AD_STAMP(2);
+  ad_load_rows<D>(kc, vc, table, Hkv, h, page_size, k0, n_old, nk, sK, sV, tid);   // this step's keys
   hb_cp_async_commit();
   // Q tile [16][D]: rows 0..G-1 are the heads of this kv head, the rest zero
   for (int i = tid; i < 16 * CH; i += AD_THREADS) {
@@ -70,6 +132,7 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
   }
   hb_cp_async_wait<0>();
   __syncthreads();
+  AD_STAMP(3);
 
   float m_run = -INFINITY, l_run = 0.f;  // of row g (a head when g < G), over this warp's keys
   float o[NT_O][4];
@@ -174,13 +237,40 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
       }
     }
   }
+  AD_STAMP(4);
+  if (whole) return;
+  // the block of this (row, kv head) that ends last adds the chunks, lowest first
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    int* cnt = counters + (size_t)t * Hkv + h;
+    const int last = atomicAdd(cnt, 1) == s_hi - s_lo;
+    if (last) *cnt = 0;
+    is_last = last;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  for (int i = tid; i < G * D; i += AD_THREADS) {
+    const int gg = i / D, d = i - gg * D;
+    const size_t head = (size_t)t * Hq + (size_t)h * G + gg;
+    float m = -INFINITY;
+    for (int c = s_lo; c <= s_hi; c++) m = fmaxf(m, __ldcg(part_ml + (head * S + c) * 2));
+    float a = 0.f, l = 0.f;
+    for (int c = s_lo; c <= s_hi; c++) {
+      const float f = expf(__ldcg(part_ml + (head * S + c) * 2) - m);
+      l += __ldcg(part_ml + (head * S + c) * 2 + 1) * f;
+      a += __ldcg(part_acc + (head * S + c) * D + d) * f;
+    }
+    out[head * D + d] = __float2bfloat16_rn(a / l);
+  }
 }
 
 template <int D>
 static int launch_decode(int G, dim3 grid, size_t smem, cudaStream_t st, const __nv_bfloat16* q, const __nv_bfloat16* kc,
                          const __nv_bfloat16* vc, const int* bt, int bt_stride, const int* row_req, const int* pos,
                          __nv_bfloat16* out, float* pa, float* pm, int Hq, int Hkv, int page_size, int window, float scale,
-                         int chunk, int S, const int* q_len, int row_limit) {
+                         int chunk, int S, const int* q_len, int row_limit, const int* ctx_len, int* counters) {
 #define HB_AD_CASE(GG)                                                                                              \
   case GG:                                                                                                          \
     {                                                                                                               \
@@ -191,7 +281,7 @@ static int launch_decode(int G, dim3 grid, size_t smem, cudaStream_t st, const _
       }                                                                                                             \
     }                                                                                                               \
     hb_launch(attn_decode_kernel<D, GG>, grid, AD_THREADS, smem, st, q, kc, vc, bt, bt_stride, row_req, pos, out, pa, pm, \
-              Hq, Hkv, page_size, window, scale, chunk, S, q_len, row_limit);                                        \
+              Hq, Hkv, page_size, window, scale, chunk, S, q_len, row_limit, ctx_len, counters);                     \
     return 0;
   switch (G) {
     HB_AD_CASE(1) HB_AD_CASE(2) HB_AD_CASE(3) HB_AD_CASE(4) HB_AD_CASE(5) HB_AD_CASE(6) HB_AD_CASE(7) HB_AD_CASE(8)
@@ -206,19 +296,21 @@ HB_EXPORT int hb_attn_decode_supported(int Hq, int Hkv, int D) {
 }
 
 // Partials layout as hb_attn_rows of the core library: workspace = part_acc [T, Hq, S, D] then
-// part_ml [T, Hq, S, 2], S = max_pos / chunk + 1; rows spanning several chunks are finished by
-// hb_attn_merge (core library) with the same chunk. With q_len given, rows of requests whose
-// portion has row_limit rows or more are skipped (the flash kernel computes those).
+// part_ml [T, Hq, S, 2], S = max_pos / chunk + 1; `counters` are T * Hkv ints that are zero
+// between calls (needed when S > 1). With q_len given, rows of requests whose portion has
+// row_limit rows or more are skipped (the flash kernel computes those). ctx_len (per request,
+// or null): the tokens that were in the cache before this step; their keys may be read before
+// the kernel ahead in the stream has ended.
 HB_EXPORT int hb_attn_decode(const void* q, const void* kc, const void* vc, const int* bt, int bt_stride,
-                             const int* row_req, const int* pos, void* out, float* workspace, int T, int Hq, int Hkv,
-                             int D, int page_size, int window, float scale, int chunk, int max_pos, const int* q_len,
-                             int row_limit, cudaStream_t st) {
+                             const int* row_req, const int* pos, void* out, float* workspace, int* counters, int T,
+                             int Hq, int Hkv, int D, int page_size, int window, float scale, int chunk, int max_pos,
+                             const int* q_len, int row_limit, const int* ctx_len, cudaStream_t st) {
   if (T <= 0) return 0;
   if (!hb_attn_decode_supported(Hq, Hkv, D)) HB_FAIL("hb_attn_decode: %d/%d heads of %d are not supported", Hq, Hkv, D);
   if (chunk <= 0 || chunk % 32) HB_FAIL("hb_attn_decode: chunk %d must be a positive multiple of 32", chunk);
   if (T > 65535 || Hkv > 65535) HB_FAIL("hb_attn_decode: %d rows / %d kv heads are beyond the grid limit", T, Hkv);
   const int G = Hq / Hkv, S = max_pos / chunk + 1;
-  if (S > 1 && !workspace) HB_FAIL("hb_attn_decode: rows that span %d chunks need a workspace", S);
+  if (S > 1 && (!workspace || !counters)) HB_FAIL("hb_attn_decode: rows that span %d chunks need a workspace and counters", S);
   if (chunk % 64) HB_FAIL("hb_attn_decode: chunk %d must be a multiple of 64", chunk);
   const size_t smem = 2 * (size_t)chunk * D * 2 + 16 * (size_t)D * 2 + AD_WARPS * (size_t)G * (D + 2) * sizeof(float);
   if (smem > 200 * 1024) HB_FAIL("hb_attn_decode: %zu bytes of shared memory (chunk %d, head_dim %d)", smem, chunk, D);
@@ -227,8 +319,8 @@ HB_EXPORT int hb_attn_decode(const void* q, const void* kc, const void* vc, cons
   dim3 grid(S, Hkv, T);
   const __nv_bfloat16 *qq = (const __nv_bfloat16*)q, *kk = (const __nv_bfloat16*)kc, *vv = (const __nv_bfloat16*)vc;
   int r = 1;
-  if (D == 64) r = launch_decode<64>(G, grid, smem, st, qq, kk, vv, bt, bt_stride, row_req, pos, (__nv_bfloat16*)out, pa, pm, Hq, Hkv, page_size, window, scale * 1.4426950408889634f, chunk, S, q_len, row_limit);
-  else if (D == 128) r = launch_decode<128>(G, grid, smem, st, qq, kk, vv, bt, bt_stride, row_req, pos, (__nv_bfloat16*)out, pa, pm, Hq, Hkv, page_size, window, scale * 1.4426950408889634f, chunk, S, q_len, row_limit);
+  if (D == 64) r = launch_decode<64>(G, grid, smem, st, qq, kk, vv, bt, bt_stride, row_req, pos, (__nv_bfloat16*)out, pa, pm, Hq, Hkv, page_size, window, scale * 1.4426950408889634f, chunk, S, q_len, row_limit, ctx_len, counters);
+  else if (D == 128) r = launch_decode<128>(G, grid, smem, st, qq, kk, vv, bt, bt_stride, row_req, pos, (__nv_bfloat16*)out, pa, pm, Hq, Hkv, page_size, window, scale * 1.4426950408889634f, chunk, S, q_len, row_limit, ctx_len, counters);
   if (r) HB_FAIL("hb_attn_decode: no kernel for group %d", G);
   HB_CHECK_LAUNCH("hb_attn_decode");
   return 0;

@@ -26,7 +26,7 @@ _SIGS = {
     "hb_gemm_stream_fused": [_p, _l, _p, _p, _i, _f, _p, _l, _i, _i, _i, _i, _p, _l, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p, _l,
                              _p, _i, _p, _p],
     "hb_gemm_stream_fused_supported": [_i, _i, _i],
-    "hb_attn_decode": [_p, _p, _p, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _i, _p, _i, _p],
+    "hb_attn_decode": [_p, _p, _p, _p, _i, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _i, _p, _i, _p, _p],
     "hb_flash_prefill": [_p, _p, _p, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p],
     "hb_flash_prefill_supported": [_i, _i, _i],
     "hb_flash_prefill_tc": [_p, _p, _p, _l, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p, _p],
@@ -241,19 +241,38 @@ def norm_qkv_rope(x, norm_w, eps, w, positions, slot_map, table, q_out, k_cache,
 DECODE_CHUNK = 256      # keys per split of the decode attention kernel (absolute positions)
 
 
+_attn_counters = {}
+
+
+def _decode_counters(device, n):
+    """Zeroed counters of the decode attention kernel (one per row and kv head; the kernel leaves them zero)."""
+    cnt = _attn_counters.get(device)
+    if cnt is None or cnt.numel() < n:
+        if cnt is not None:
+            _retired.append(cnt)     # a captured CUDA graph may still hold the old address
+        cnt = _attn_counters[device] = torch.zeros(max(n, 16384), dtype=torch.int32, device=device)
+    return cnt
+
+
 def attention_decode(q, k_cache, v_cache, block_table, row_request, positions, out, n_heads, n_kv_heads, head_dim,
-                     page_size, window, scale, max_pos, chunk=DECODE_CHUNK, q_len=None, row_limit=0):
-    """The bf16 row-attention kernel itself (see csrc/attention_fast.cu), with the core library's merge.
-    With q_len (int32 per request) rows of requests with row_limit rows or more are skipped."""
+                     page_size, window, scale, max_pos, chunk=DECODE_CHUNK, q_len=None, row_limit=0, ctx_len=None):
+    """The bf16 row-attention kernel itself (see csrc/attention_fast.cu); rows whose keys span several
+    chunks are finished inside it. With q_len (int32 per request) rows of requests with row_limit
+    rows or more are skipped. ctx_len (int32 per request): the tokens in the cache before this
+    step; with it the kernel asks for their keys before the kernel ahead of it has ended, so
+    positions, tables and ctx_len must then be in place before that kernel starts."""
     from . import ops
 
     T = q.shape[0]
     ws = ops.attention_workspace(T, n_heads, head_dim, max_pos, chunk, q.device)
+    cnt = None if ws is None else _decode_counters(q.device, T * n_kv_heads)
     _call("hb_attn_decode", q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_table.data_ptr(),
           block_table.stride(0), row_request.data_ptr(), positions.data_ptr(), out.data_ptr(),
-          None if ws is None else ws.data_ptr(), T, n_heads, n_kv_heads, head_dim, page_size, int(window), float(scale),
-          chunk, int(max_pos), None if q_len is None else q_len.data_ptr(), int(row_limit), _stream())
-    return ops.attention_merge(ws, positions, out, n_heads, head_dim, window, max_pos, chunk, row_request, q_len, row_limit)
+          None if ws is None else ws.data_ptr(), None if cnt is None else cnt.data_ptr(), T, n_heads, n_kv_heads,
+          head_dim, page_size, int(window), float(scale), chunk, int(max_pos),
+          None if q_len is None else q_len.data_ptr(), int(row_limit), None if ctx_len is None else ctx_len.data_ptr(),
+          _stream())
+    return out
 
 
 def attention_decode_supported(n_heads, n_kv_heads, head_dim) -> bool:
@@ -309,5 +328,6 @@ def attention(q, k_cache, v_cache, batch, group, out, n_heads, n_kv_heads, head_
     if need_rows:
         attention_decode(q, k_cache, v_cache, bt, batch.row_request, batch.positions, out, n_heads, n_kv_heads,
                          head_dim, page_size, window, scale, batch.max_pos,
-                         q_len=batch.req_q_len if use_flash else None, row_limit=FLASH_MIN_ROWS)
+                         q_len=batch.req_q_len if use_flash else None, row_limit=FLASH_MIN_ROWS,
+                         ctx_len=batch.req_ctx_len)
     return True

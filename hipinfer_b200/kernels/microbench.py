@@ -103,8 +103,8 @@ def main(argv=None) -> int:
         o = torch.empty_like(q)
         scale = 1.0 / math.sqrt(D)
         if a.kernel == "attn_decode":
-            rr, pos = i32(list(range(R))), i32([ctx - 1] * R)
-            fn = lambda: fast.attention_decode(q, kc, vc, bt, rr, pos, o, Hq, Hkv, D, ps, 0, scale, ctx - 1)
+            rr, pos, cl = i32(list(range(R))), i32([ctx - 1] * R), i32(ctx_len)
+            fn = lambda: fast.attention_decode(q, kc, vc, bt, rr, pos, o, Hq, Hkv, D, ps, 0, scale, ctx - 1, ctx_len=cl)
             nbytes = 2 * R * ctx * Hkv * D * 2
             flops = 4.0 * R * ctx * Hq * D
         else:

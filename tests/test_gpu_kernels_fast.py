@@ -179,6 +179,16 @@ def test_attention_decode(Hq, Hkv, D, ps, window):
     rr = torch.tensor([r for r, _ in rows], dtype=torch.int32, device=DEV)
     pos = torch.tensor([p for _, p in rows], dtype=torch.int32, device=DEV)
     fast().attention_decode(q, kc, vc, bt, rr, pos, out, Hq, Hkv, D, ps, window, 1.0 / math.sqrt(D), max(p for _, p in rows))
+    # the same with the keys of earlier steps asked for early (requests 1 and 3 have several rows:
+    # their new keys start at the first row's position): bit-identical
+    early = torch.full_like(out, 3.0)
+    ctx = torch.tensor([511, 30, 0, 255], dtype=torch.int32, device=DEV)
+    torch.cuda.synchronize()
+    for _ in range(2):      # twice: the counters are left at zero
+        fast().attention_decode(q, kc, vc, bt, rr, pos, early, Hq, Hkv, D, ps, window, 1.0 / math.sqrt(D),
+                                max(p for _, p in rows), ctx_len=ctx)
+        assert torch.equal(early, out)
+        early.fill_(3.0)
     got = out.float().cpu().reshape(T, Hq, D)
     for t, (r, p) in enumerate(rows):
         ref = plain.attention_scores_softmax_values(qf[t:t + 1], ks[r][:p + 1], vs[r][:p + 1], [p], list(range(p + 1)),
