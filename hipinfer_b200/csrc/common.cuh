@@ -57,6 +57,22 @@ __device__ __forceinline__ float hb_block_sum(float v, float* sh) {
   return t;
 }
 
+// Four consecutive elements as one 16-byte (fp32) or 8-byte (bf16) access.
+__device__ __forceinline__ float4 hb_load4(const float* p) { return *(const float4*)p; }
+__device__ __forceinline__ float4 hb_load4(const __nv_bfloat16* p) {
+  const uint2 r = *(const uint2*)p;
+  const float2 a = __bfloat1622float2(*(const __nv_bfloat162*)&r.x), b = __bfloat1622float2(*(const __nv_bfloat162*)&r.y);
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void hb_store4(float* p, float4 v) { *(float4*)p = v; }
+__device__ __forceinline__ void hb_store4(__nv_bfloat16* p, float4 v) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  uint2 r;
+  r.x = *(uint32_t*)&a;
+  r.y = *(uint32_t*)&b;
+  *(uint2*)p = r;
+}
+
 // Calls f.template operator()<TA, TB>() for the element types named by two dtype codes.
 #define HB_DISPATCH_2(da, db, NAME, ...)                                                     \
   do {                                                                                       \

@@ -60,21 +60,6 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const TW* __restrict
   for (int i = threadIdx.x; i < H; i += blockDim.x) yr[i] = hb_from_float<TO>(hb_to_float(w[i]) * (xr[i] * inv));
 }
 
-__device__ __forceinline__ float4 hb_load4(const float* p) { return *(const float4*)p; }
-__device__ __forceinline__ float4 hb_load4(const __nv_bfloat16* p) {
-  const uint2 r = *(const uint2*)p;
-  const float2 a = __bfloat1622float2(*(const __nv_bfloat162*)&r.x), b = __bfloat1622float2(*(const __nv_bfloat162*)&r.y);
-  return make_float4(a.x, a.y, b.x, b.y);
-}
-__device__ __forceinline__ void hb_store4(float* p, float4 v) { *(float4*)p = v; }
-__device__ __forceinline__ void hb_store4(__nv_bfloat16* p, float4 v) {
-  __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
-  uint2 r;
-  r.x = *(uint32_t*)&a;
-  r.y = *(uint32_t*)&b;
-  *(uint2*)p = r;
-}
-
 // The same with 16-byte accesses and the row held in registers between the two passes
 // (H a multiple of 4, at most 256 * 4 * NV elements). The sum runs over the same per-thread
 // partial sums whatever M is.

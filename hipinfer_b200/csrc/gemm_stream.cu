@@ -11,11 +11,14 @@
 // leave fp32 partials [slice][token][column]; the CTA that finishes a column block last adds
 // them in slice order and applies the epilogue (store fp32 / store bf16 / add into the fp32
 // residual / SwiGLU over gate and up columns interleaved by 16), then zeroes the counter.
+// Epilogue ST_SLICES leaves the slices where they are for the kernel that consumes the result
+// (the next norm, the rotation: gemm_stream_consumers.cu), which adds them in the same order:
+// one kernel and one round trip through memory less between two products.
 // It replaces gemv_kernel and gemm_skinny_kernel of the reference (src/kernels.cuh:164, 911).
 // All waits are bounded.
 #include "tc_common.cuh"
 
-enum { ST_F32 = 0, ST_BF16 = 1, ST_ADD_F32 = 2, ST_SWIGLU_BF16 = 3 };
+enum { ST_F32 = 0, ST_BF16 = 1, ST_ADD_F32 = 2, ST_SWIGLU_BF16 = 3, ST_SLICES = 4 };
 constexpr int ST_ROWS = 128, ST_BK = 64, ST_W_BYTES = ST_ROWS * ST_BK * 2;
 
 // DEEP: the pipeline of a product that is not split along K (many column blocks): six stages,
@@ -145,7 +148,7 @@ __global__ void __launch_bounds__(192) gemm_stream_kernel(const __grid_constant_
 #pragma unroll
     for (int c = 0; c < NT / 16; c++) hb_tmem_ld16(tmem_base + ((uint32_t)(warp * 32) << 16) + c * 16, v + 16 * c);
     const int n = n0 + warp * 32 + lane;
-    if (ksplit == 1) {
+    if (ksplit == 1 && epi != ST_SLICES) {
 #pragma unroll
       for (int m = 0; m < NT; m++) {
         if (m < M) {
@@ -283,14 +286,15 @@ HB_EXPORT int hb_gemm_stream_plan(int N, int K, int* kslice, int* ksplit, long* 
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   stream_plan(N, K, sms, kslice, ksplit);
   *n_blocks = (N + ST_ROWS - 1) / ST_ROWS;
-  *ws_floats_per_token = *ksplit > 1 ? (long)(*ksplit) * (*n_blocks) * ST_ROWS : 0;
+  *ws_floats_per_token = (long)(*ksplit) * (*n_blocks) * ST_ROWS;   // not needed when ksplit is 1, except for ST_SLICES
   return 0;
 }
 
 template <int NT, bool DEEP>
 static int launch_stream(const CUtensorMap& mw, const CUtensorMap& mx, void* C, long ldc, int M, int N, int K, int kslice,
                          int ksplit, int n_blocks, float* ws, int* counters, int epi, int* status, cudaStream_t s) {
-  const int defer = ksplit > 1 && M >= 8;  // from 8 token rows on (measured) the slices are added by a kernel of its own
+  // from 8 token rows on (measured) the slices are added by a kernel of its own; ST_SLICES leaves them to the consumer
+  const int defer = epi == ST_SLICES || (ksplit > 1 && M >= 8);
   using S = StreamCfg<NT, DEEP>;
   auto kern = gemm_stream_kernel<NT, DEEP>;
   static bool configured = false;
@@ -302,7 +306,7 @@ static int launch_stream(const CUtensorMap& mw, const CUtensorMap& mx, void* C, 
   cudaError_t e = hb_launch(kern, dim3(n_blocks, ksplit), 192, S::TOTAL, s, mw, mx, C, ldc, M, N, K, kslice, ws, counters,
                             epi, status, defer);
   if (e != cudaSuccess) HB_FAIL("hb_gemm_stream: %s", cudaGetErrorString(e));
-  if (defer) {
+  if (defer && epi != ST_SLICES) {
     const int NP = n_blocks * ST_ROWS;
     const long items = (long)M * (NP / 4);
     e = hb_launch(stream_reduce_kernel, (unsigned)((items + 255) / 256), 256, 0, s, (const float*)ws, C, ldc, M, N, NP, NT,
@@ -315,20 +319,21 @@ static int launch_stream(const CUtensorMap& mw, const CUtensorMap& mx, void* C, 
 // C per `epi` (0 fp32, 1 bf16, 2 fp32 +=, 3 bf16 SwiGLU [M, N/2]) for M <= 64. ws: at least
 // ksplit * n_blocks * 128 * NT floats when ksplit > 1 (NT = M rounded up to 16, 32 or 64);
 // counters: n_blocks ints, all zero (left zero). Calls sharing ws/counters must not overlap.
+// epi 4: C is not touched; ws keeps the slices [ksplit][NT][n_blocks * 128] (also when ksplit is 1).
 HB_EXPORT int hb_gemm_stream(const void* A, long lda, const void* W, long ldw, void* C, long ldc, int M, int N, int K,
                              int epi, float* ws, long ws_floats, int* counters, int n_counters, int* status,
                              cudaStream_t s) {
   if (M <= 0 || N <= 0) return 0;
   if (M > 64) HB_FAIL("hb_gemm_stream: M = %d is beyond 64 rows", M);
   if (K <= 0 || (K & 7)) HB_FAIL("hb_gemm_stream: K = %d must be a positive multiple of 8 (16-byte rows for TMA)", K);
-  if (epi < 0 || epi > 3) HB_FAIL("hb_gemm_stream: unknown epilogue %d", epi);
+  if (epi < 0 || epi > 4) HB_FAIL("hb_gemm_stream: unknown epilogue %d", epi);
   if (epi == ST_SWIGLU_BF16 && (N & 31)) HB_FAIL("hb_gemm_stream: SwiGLU needs N = %d to be a multiple of 32", N);
   if (!status) HB_FAIL("hb_gemm_stream: no status word");
   int kslice, ksplit, n_blocks;
   long per_token;
   hb_gemm_stream_plan(N, K, &kslice, &ksplit, &per_token, &n_blocks);
   const int NT = M <= 16 ? 16 : M <= 32 ? 32 : 64;
-  if (ksplit > 1 && (!ws || ws_floats < per_token * NT))
+  if ((ksplit > 1 || epi == ST_SLICES) && (!ws || ws_floats < per_token * NT))
     HB_FAIL("hb_gemm_stream: workspace of %ld floats, %ld needed", ws_floats, per_token * NT);
   if (ksplit > 1 && (!counters || n_counters < n_blocks)) HB_FAIL("hb_gemm_stream: %d counters, %d needed", n_counters, n_blocks);
   CUtensorMap mw, mx;
@@ -348,6 +353,21 @@ HB_EXPORT int hb_gemm_stream(const void* A, long lda, const void* W, long ldw, v
 #undef HB_ST_ARGS
   if (r) return r;
   HB_CHECK_LAUNCH("hb_gemm_stream");
+  return 0;
+}
+
+// Finish a product that was left as slices (epi 4): C per `epi` (0 to 3) from ws, for the same M, N, K.
+HB_EXPORT int hb_gemm_stream_finish(const float* ws, void* C, long ldc, int M, int N, int K, int epi, cudaStream_t s) {
+  if (M <= 0 || N <= 0) return 0;
+  if (epi < 0 || epi > 3) HB_FAIL("hb_gemm_stream_finish: unknown epilogue %d", epi);
+  int kslice, ksplit, n_blocks;
+  long per_token;
+  hb_gemm_stream_plan(N, K, &kslice, &ksplit, &per_token, &n_blocks);
+  const int NT = M <= 16 ? 16 : M <= 32 ? 32 : 64, NP = n_blocks * ST_ROWS;
+  const long items = (long)M * (NP / 4);
+  cudaError_t e = hb_launch(stream_reduce_kernel, (unsigned)((items + 255) / 256), 256, 0, s, ws, C, ldc, M, N, NP, NT,
+                            ksplit, epi);
+  if (e != cudaSuccess) HB_FAIL("hb_gemm_stream_finish: %s", cudaGetErrorString(e));
   return 0;
 }
 
@@ -388,6 +408,7 @@ HB_EXPORT int hb_gemm_stream_static(const void* A, long lda, const void* W, long
   long per_token;
   hb_gemm_stream_plan(N, K, &kslice, &ksplit, &per_token, &n_blocks);
   const int NT = M <= 16 ? 16 : M <= 32 ? 32 : 64;
+  if (ksplit == 1) per_token = 0;   // a product that is not split needs no scratch
   if (per_token * NT > (long)HB_STATIC_WS_FLOATS)
     HB_FAIL("hb_gemm_stream_static: M = %d, N = %d, K = %d need %ld floats of scratch; the static array holds %ld", M, N, K,
             per_token * NT, (long)HB_STATIC_WS_FLOATS);

@@ -23,9 +23,9 @@ _SIGS = {
     "hb_gemm_skinny_plan": [_i, _i, _p, _p, _p, _p],
     "hb_gemm_stream": [_p, _l, _p, _l, _p, _l, _i, _i, _i, _i, _p, _l, _p, _i, _p, _p],
     "hb_gemm_stream_plan": [_i, _i, _p, _p, _p, _p],
-    "hb_gemm_stream_fused": [_p, _l, _p, _p, _i, _f, _p, _l, _i, _i, _i, _i, _p, _l, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p, _l,
-                             _p, _i, _p, _p],
-    "hb_gemm_stream_fused_supported": [_i, _i, _i],
+    "hb_gemm_stream_finish": [_p, _p, _l, _i, _i, _i, _i, _p],
+    "hb_add_rmsnorm_slices": [_p, _l, _p, _i, _l, _l, _p, _p, _p, _i, _i, _f, _p],
+    "hb_rope_kv_slices": [_p, _i, _l, _l, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p],
     "hb_attn_decode": [_p, _p, _p, _p, _i, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _i, _p, _i, _p, _p],
     "hb_flash_prefill": [_p, _p, _p, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p],
     "hb_flash_prefill_supported": [_i, _i, _i],
@@ -34,10 +34,10 @@ _SIGS = {
     "hb_attn_decode_supported": [_i, _i, _i],
 }
 _fns = {}
-_LAUNCHES = {"hb_gemm_stream_fused": 1, "hb_gemm_tc": 1, "hb_gemm_skinny": 1, "hb_gemm_stream": 1, "hb_attn_decode": 1, "hb_flash_prefill": 1, "hb_flash_prefill_tc": 1}
+_LAUNCHES = {"hb_gemm_stream_finish": 1, "hb_add_rmsnorm_slices": 1, "hb_rope_kv_slices": 1, "hb_gemm_tc": 1, "hb_gemm_skinny": 1, "hb_gemm_stream": 1, "hb_attn_decode": 1, "hb_flash_prefill": 1, "hb_flash_prefill_tc": 1}
 _status = None
 
-EPI_F32, EPI_BF16, EPI_ADD_F32, EPI_SWIGLU_BF16 = 0, 1, 2, 3
+EPI_F32, EPI_BF16, EPI_ADD_F32, EPI_SWIGLU_BF16, EPI_SLICES = 0, 1, 2, 3, 4
 
 
 class KernelTimeout(RuntimeError):
@@ -126,10 +126,14 @@ def _skinny_scratch(device, ws_floats, n_counters):
     return sc
 
 
+_scratch_gen = [0]       # counts the products that wrote the shared scratch: slices left there are valid until the next one
+
+
 def gemm_skinny(a, w, out, epi):
     """The weight-streaming kernel itself (M <= 64): out per `epi` (see csrc/gemm_skinny.cu)."""
     M, K = a.shape
     N = w.shape[0]
+    _scratch_gen[0] += 1
     _, _, per_row, n_blocks = skinny_plan(N, K)
     mp = 8 if M <= 8 else 16 if M <= 16 else 32 if M <= 32 else 64
     ws, cnt = _skinny_scratch(a.device, per_row * mp, n_blocks)
@@ -155,12 +159,82 @@ def gemm_stream(a, w, out, epi):
     _, _, per_token, n_blocks = stream_plan(N, K)
     nt = 16 if M <= 16 else 32 if M <= 32 else 64
     ws, cnt = _skinny_scratch(a.device, per_token * nt, n_blocks)
+    _scratch_gen[0] += 1
     _call("hb_gemm_stream", a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0), M, N, K,
           epi, ws.data_ptr(), ws.numel(), cnt.data_ptr(), cnt.numel(), status_word().data_ptr(), _stream())
     return out
 
 
+class Slices:
+    """A small product a @ w.T left as the K slices it was computed in: fp32 [ksplit][rows][row_stride]
+    in the scratch that all small products share, so it has to be consumed (or finished) before
+    the next of them runs; `check()` raises if it was not."""
+    __slots__ = ("ws", "ksplit", "slice_stride", "row_stride", "M", "N", "K", "gen")
+
+    def check(self):
+        if self.gen != _scratch_gen[0]:
+            raise RuntimeError("a product left as slices was overwritten by a later product before it was consumed")
+
+
+def gemm_stream_slices(a, w) -> Slices:
+    """The swapped-operand kernel with the slices left for the consumer (see csrc/gemm_stream.cu, epilogue 4)."""
+    M, K = a.shape
+    N = w.shape[0]
+    _, ksplit, per_token, n_blocks = stream_plan(N, K)
+    nt = 16 if M <= 16 else 32 if M <= 32 else 64
+    ws, cnt = _skinny_scratch(a.device, per_token * nt, n_blocks)
+    _scratch_gen[0] += 1
+    _call("hb_gemm_stream", a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), None, 0, M, N, K, EPI_SLICES,
+          ws.data_ptr(), ws.numel(), cnt.data_ptr(), cnt.numel(), status_word().data_ptr(), _stream())
+    sl = Slices()
+    sl.ws, sl.ksplit, sl.row_stride, sl.slice_stride = ws, ksplit, n_blocks * 128, nt * n_blocks * 128
+    sl.M, sl.N, sl.K, sl.gen = M, N, K, _scratch_gen[0]
+    return sl
+
+
+def finish_slices(sl: Slices, out, epi):
+    """out per `epi` (0 to 3) from slices, as the product's own reduction would have left it."""
+    sl.check()
+    _call("hb_gemm_stream_finish", sl.ws.data_ptr(), out.data_ptr(), out.stride(0), sl.M, sl.N, sl.K, epi, _stream())
+    return out
+
+
+def add_rmsnorm_slices(x, sl: Slices, weight, eps, out, rows=None):
+    """x (fp32 residual rows) += slices, out (bf16) = RMSNorm of the sum times weight: one kernel
+    (csrc/gemm_stream_consumers.cu). With rows, out[i] is made from row rows[i] and x is left alone."""
+    sl.check()
+    M, H = out.shape
+    _call("hb_add_rmsnorm_slices", x.data_ptr(), x.stride(0), sl.ws.data_ptr(), sl.ksplit, sl.slice_stride, sl.row_stride,
+          weight.data_ptr(), out.data_ptr(), None if rows is None else rows.data_ptr(), M, H, float(eps), _stream())
+    return out
+
+
+def add_rmsnorm_slices_ok(x, sl: Slices, weight, out) -> bool:
+    H = out.shape[1]
+    return (x.dtype == torch.float32 and out.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and sl.N == H
+            and H % 4 == 0 and H <= 8192 and x.stride(0) % 4 == 0 and out.is_contiguous() and weight.is_contiguous()
+            and (x.data_ptr() | out.data_ptr() | weight.data_ptr()) % 16 == 0)
+
+
+def rope_kv_slices(sl: Slices, positions, slot_map, table, q_out, k_cache, v_cache, n_heads, n_kv_heads, head_dim, page_size):
+    """Rotation of q and k and the cache write on a q/k/v product left as slices (rotary over the whole head)."""
+    sl.check()
+    p = lambda t: None if t is None else t.data_ptr()
+    _call("hb_rope_kv_slices", sl.ws.data_ptr(), sl.ksplit, sl.slice_stride, sl.row_stride, positions.data_ptr(),
+          p(slot_map), table.data_ptr(), q_out.data_ptr(), p(k_cache), p(v_cache), sl.M, n_heads, n_kv_heads, head_dim,
+          page_size, _stream())
+    return q_out
+
+
+def linear_slices(a, w):
+    """a @ w.T as slices when the small-product kernel applies (a few bf16 rows), else None."""
+    if a.shape[0] > SKINNY_MAX_ROWS or SMALL_IMPL != "stream" or DEFER_OFF or not _tc_ok(a, w.t):
+        return None
+    return gemm_stream_slices(a, w.t)
+
+
 SMALL_IMPL = os.environ.get("HIPINFER_B200_SMALL_GEMM", "stream")   # "stream" (tcgen05) or "skinny" (mma.sync)
+DEFER_OFF = os.environ.get("HIPINFER_B200_DEFER", "1") == "0"        # "0": every product adds its own slices
 
 
 def _gemm(a, w, out, epi):
@@ -186,55 +260,6 @@ def linear_swiglu(a, w, act_out, group) -> bool:
     if group != 16 or act_out.dtype != torch.bfloat16 or not _tc_ok(a, w.t) or w.shape[0] % 32:
         return False
     _gemm(a, w.t, act_out, EPI_SWIGLU_BF16)
-    return True
-
-
-# Norm / rotation / activation fused into the decode products (csrc/gemm_stream_fused.cu): "0" off,
-# "qkv" or "ffn" only that one, "1" both. Off by default: inside a CUDA graph with programmatic
-# dependent launch the separate small kernels cost about what the fused kernels' in-CTA norm pass
-# costs (measured at Llama-3.2-1B shape: batch 8 6,355 tok/s unfused, 6,343 with qkv fused, 6,157
-# with both; batch 16 is slower fused), so the simpler path is the default.
-_FUSE_ENV = os.environ.get("HIPINFER_B200_FUSE", "0")
-FUSE = _FUSE_ENV != "0"
-
-
-def _fused_ok(x, norm_w, w, M) -> bool:
-    N, K = w.shape
-    return (not PLAIN_ONLY and SMALL_IMPL == "stream" and w.dtype == torch.bfloat16 and x.dtype == torch.float32
-            and x.stride(1) == 1 and x.stride(0) % 4 == 0 and x.data_ptr() % 16 == 0 and norm_w.data_ptr() % 16 == 0
-            and norm_w.dtype in (torch.float32, torch.bfloat16) and norm_w.is_contiguous() and x.shape[1] == K
-            and w.stride(0) % 8 == 0 and w.data_ptr() % 16 == 0 and bool(_fn("hb_gemm_stream_fused_supported")(M, N, K)))
-
-
-def _fused_call(x, rows, norm_w, eps, w, M, mode, out, pos, slot_map, table, kc, vc, Hq, Hkv, D, page_size):
-    N, K = w.shape
-    _, ksplit, _, n_blocks = stream_plan(N, K)
-    ws, cnt = _skinny_scratch(x.device, ksplit * n_blocks * 128 * 16, n_blocks)
-    p = lambda t: None if t is None else t.data_ptr()
-    _call("hb_gemm_stream_fused", x.data_ptr(), x.stride(0), p(rows), norm_w.data_ptr(),
-          0 if norm_w.dtype == torch.float32 else 1, float(eps), w.data_ptr(), w.stride(0), M, N, K, mode, out.data_ptr(),
-          out.stride(0), p(pos), p(slot_map), p(table), p(kc), p(vc), Hq, Hkv, D, page_size, ws.data_ptr(), ws.numel(),
-          cnt.data_ptr(), cnt.numel(), status_word().data_ptr(), _stream())
-
-
-def norm_linear_swiglu(x, rows, norm_w, eps, w, act_out, group) -> bool:
-    """act_out = SwiGLU(RMSNorm(x[rows]) w^T) in one kernel (up to 16 rows); False if not applicable."""
-    M = act_out.shape[0]
-    if group != 16 or act_out.dtype != torch.bfloat16 or w.shape[0] % 32 or not _fused_ok(x, norm_w, w.t, M):
-        return False
-    _fused_call(x, rows, norm_w, eps, w.t, M, 0, act_out, None, None, None, None, None, 0, 0, 0, 0)
-    return True
-
-
-def norm_qkv_rope(x, norm_w, eps, w, positions, slot_map, table, q_out, k_cache, v_cache, n_heads, n_kv_heads, head_dim,
-                  rotary_dim, page_size) -> bool:
-    """RMSNorm, the fused q/k/v product, rotary and the cache write in one kernel (up to 16 rows)."""
-    M = q_out.shape[0]
-    if (rotary_dim != head_dim or 128 % head_dim or w.shape[0] % 128 or q_out.dtype != torch.bfloat16
-            or (k_cache is not None and k_cache.dtype != torch.bfloat16) or not _fused_ok(x, norm_w, w.t, M)):
-        return False
-    _fused_call(x, None, norm_w, eps, w.t, M, 1, q_out, positions, slot_map, table, k_cache, v_cache, n_heads, n_kv_heads,
-                head_dim, page_size)
     return True
 
 

@@ -102,10 +102,17 @@ def embedding(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor) -> t
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
-            rows: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out[i] = weight * x[rows[i] or i] / rms; x float32 [*, H], out [M, H] float32 or bfloat16."""
+            rows: Optional[torch.Tensor] = None, pending: Optional["Pending"] = None) -> torch.Tensor:
+    """out[i] = weight * x[rows[i] or i] / rms; x float32 [*, H], out [M, H] float32 or bfloat16.
+    pending: a sum that has yet to be added into x; it is added first (in the same kernel where that applies)."""
     _need_cuda(x, weight, out, rows)
     M, H = out.shape
+    if pending is not None:
+        from . import fast
+
+        if pending.out is x and pending.accumulate and fast.add_rmsnorm_slices_ok(x, pending.slices, weight, out):
+            return fast.add_rmsnorm_slices(x, pending.slices, weight, eps, out, rows)
+        pending.finish()
     assert x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous() and x.shape[1] == H
     assert weight.numel() == H and weight.is_contiguous()
     if rows is not None:
@@ -155,10 +162,21 @@ def rope_table(inv_freq: torch.Tensor, n_pos: int) -> torch.Tensor:
 
 def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, slot_map: Optional[torch.Tensor], table: torch.Tensor,
                   q_out: torch.Tensor, k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], n_heads: int,
-                  n_kv_heads: int, head_dim: int, rotary_dim: int, page_size: int) -> torch.Tensor:
+                  n_kv_heads: int, head_dim: int, rotary_dim: int, page_size: int,
+                  pending: Optional["Pending"] = None) -> torch.Tensor:
     """Rotate q and k of qkv [T, (Hq + 2 Hkv) D]; q to q_out [T, Hq D]; k, v to their page slots
-    (cache layout [page, Hkv, page_size, D]); slot_map None: no cache write."""
+    (cache layout [page, Hkv, page_size, D]); slot_map None: no cache write. pending: qkv is not
+    written yet, its K slices are added here (in the same kernel where that applies)."""
     _need_cuda(qkv, positions, slot_map, table, q_out, k_cache, v_cache)
+    if pending is not None:
+        from . import fast
+
+        if (pending.out is qkv and not pending.accumulate and rotary_dim == head_dim and head_dim % 8 == 0
+                and q_out.dtype == torch.bfloat16 and q_out.is_contiguous()
+                and (slot_map is None or (k_cache.dtype == torch.bfloat16 and k_cache.is_contiguous() and v_cache.is_contiguous()))):
+            return fast.rope_kv_slices(pending.slices, positions, slot_map, table, q_out, k_cache, v_cache, n_heads,
+                                       n_kv_heads, head_dim, page_size)
+        pending.finish()
     _rows_contiguous(qkv, "rope qkv")
     T = qkv.shape[0]
     assert qkv.shape[1] == (n_heads + 2 * n_kv_heads) * head_dim
@@ -300,22 +318,34 @@ def linear_swiglu(a: torch.Tensor, w_gate_up: Weight, act_out: torch.Tensor, gro
     return swiglu(gu, act_out, group)
 
 
-def norm_linear_swiglu(x, norm_weight, eps, w_gate_up: Weight, act_out, group: int, rows=None) -> bool:
-    """act_out = SwiGLU(RMSNorm(x) w^T) as ONE kernel where the fast library has it (a few bfloat16
-    rows); False when it does not apply, and the caller runs the parts one after the other."""
+class Pending:
+    """A product whose K slices have yet to be added: into `out` (accumulate) or as `out` itself.
+    The kernel that reads the result next can add them on its way (rmsnorm and rope_kv_write take
+    `pending`); anything else calls finish() first. It must be consumed before the next small
+    product runs: the slices lie in scratch memory those products share."""
+    __slots__ = ("slices", "out", "accumulate")
+
+    def __init__(self, slices, out, accumulate):
+        self.slices, self.out, self.accumulate = slices, out, accumulate
+
+    def finish(self):
+        from . import fast
+
+        fast.finish_slices(self.slices, self.out, fast.EPI_ADD_F32 if self.accumulate else fast.EPI_F32)
+        return self.out
+
+
+def linear_deferred(a: torch.Tensor, w: Weight, out: torch.Tensor, accumulate: bool = False) -> Optional[Pending]:
+    """out (+)= a @ w.T, with the last step (adding the K slices of a small product) left to the
+    consumer where that applies: then a Pending comes back and `out` is not yet written. None: out is done."""
     from . import fast
 
-    return (x.is_cuda and fast._FUSE_ENV in ("1", "ffn")
-            and fast.norm_linear_swiglu(x, rows, norm_weight, eps, w_gate_up, act_out, group))
-
-
-def norm_qkv_rope(x, norm_weight, eps, w_qkv: Weight, positions, slot_map, table, q_out, k_cache, v_cache, n_heads,
-                  n_kv_heads, head_dim, rotary_dim, page_size) -> bool:
-    """RMSNorm, q/k/v product, rotation and cache write as ONE kernel where the fast library has it."""
-    from . import fast
-
-    return x.is_cuda and fast._FUSE_ENV in ("1", "qkv") and fast.norm_qkv_rope(x, norm_weight, eps, w_qkv, positions, slot_map, table, q_out, k_cache,
-                                            v_cache, n_heads, n_kv_heads, head_dim, rotary_dim, page_size)
+    if out.dtype == torch.float32 and a.is_cuda:
+        sl = fast.linear_slices(a, w)
+        if sl is not None:
+            return Pending(sl, out, accumulate)
+    linear(a, w, out, accumulate)
+    return None
 
 
 def attention(q, k_cache, v_cache, batch, group: int, out, n_heads, n_kv_heads, head_dim, page_size, window, scale):

@@ -13,6 +13,7 @@ from typing import Dict, List, Optional, Tuple
 import torch
 
 from ..cache import CacheGroupSpec
+from ..kernels import ops
 from ..parts.registry import BuildContext, build_part
 from ..parts.spec import ModelSpec, PartSpec
 
@@ -93,8 +94,22 @@ class DecoderModel:
     def forward(self, batch, storage) -> torch.Tensor:
         """Run the batch's tokens from the cache; logits float32 [len(batch.want_rows), vocab]."""
         x = self.embedding.forward(batch.tokens)
+        pending = None      # what a layer has left to be added into x (kernels.ops.Pending): the next norm adds it
         for i, st in enumerate(self.spec.order):
-            self.layers[st.layer].forward(x, batch, storage.layer_cache(self.cache_plan[i]), storage.layer_state(i))
+            layer = self.layers[st.layer]
+            cache, state = storage.layer_cache(self.cache_plan[i]), storage.layer_state(i)
+            if pending is not None and not layer.takes_pending:
+                pending.finish()
+                pending = None
+            left = layer.forward(x, batch, cache, state, pending) if pending is not None else layer.forward(x, batch, cache, state)
+            pending = left if isinstance(left, ops.Pending) else None
         if batch.n_want == 0:
+            if pending is not None:
+                pending.finish()
             return torch.empty(0, self.spec.vocab_size, dtype=torch.float32, device=x.device)
+        if pending is not None and not self.final_norm.takes_pending:
+            pending.finish()
+            pending = None
+        if pending is not None:
+            return self.head.forward(self.final_norm.forward(x, rows=batch.want_rows, pending=pending))
         return self.head.forward(self.final_norm.forward(x, rows=batch.want_rows))

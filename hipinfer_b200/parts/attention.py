@@ -55,31 +55,21 @@ class AttentionMixer(Mixer):
     def cache_need(self):
         return CacheNeed("window" if self.window else "full", self.n_kv_heads, self.head_dim, self.window)
 
-    def forward_prenorm(self, norm, x, batch, cache, state):
-        """The same, given the norm part instead of normalised rows: for a few rows the norm, the
-        q/k/v product, the rotation and the cache write run as one kernel."""
-        from .norm import RMSNorm
-        from .rotary import RotaryEmbedding
-
-        T = x.shape[0]
-        if type(norm) is RMSNorm and type(self.position) is RotaryEmbedding and T <= 16:
-            q = torch.empty(T, self.n_heads * self.head_dim, dtype=self.ctx.dtype, device=x.device)
-            slot_map = batch.slot_maps[cache.group] if cache.write else None
-            if ops.norm_qkv_rope(x, norm.weight, norm.eps, self.wqkv, batch.positions, slot_map, self.position.table, q,
-                                 cache.k, cache.v, self.n_heads, self.n_kv_heads, self.head_dim,
-                                 self.position.rotary_dim, self.ctx.page_size):
-                return self._attend_and_project(q, x, batch, cache)
-        self.forward(norm.forward(x), x, batch, cache, state)
-
     def forward(self, xn, x, batch, cache, state):
         T = xn.shape[0]
         Hq, Hkv, D = self.n_heads, self.n_kv_heads, self.head_dim
         qkv = torch.empty(T, (Hq + 2 * Hkv) * D, dtype=torch.float32, device=xn.device)
-        ops.linear(xn, self.wqkv, qkv)
+        pending = ops.linear_deferred(xn, self.wqkv, qkv)      # a few rows: the rotation adds the product's slices
         q = torch.empty(T, Hq * D, dtype=self.ctx.dtype, device=xn.device)
         slot_map = batch.slot_maps[cache.group] if cache.write else None
-        self.position.rotate_and_store(qkv, batch.positions, slot_map, q, cache.k, cache.v, Hq, Hkv)
-        self._attend_and_project(q, x, batch, cache)
+        if pending is not None and not self.position.takes_pending:
+            pending.finish()
+            pending = None
+        if pending is None:
+            self.position.rotate_and_store(qkv, batch.positions, slot_map, q, cache.k, cache.v, Hq, Hkv)
+        else:
+            self.position.rotate_and_store(qkv, batch.positions, slot_map, q, cache.k, cache.v, Hq, Hkv, pending=pending)
+        return self._attend_and_project(q, x, batch, cache)
 
     def _attend_and_project(self, q, x, batch, cache):
         T = q.shape[0]
@@ -87,7 +77,7 @@ class AttentionMixer(Mixer):
         att = torch.empty(T, Hq * D, dtype=self.ctx.dtype, device=q.device)
         ops.attention(q, cache.k, cache.v, batch, cache.group, att, Hq, Hkv, D, self.ctx.page_size, self.window,
                       self.scale)
-        ops.linear(att, self.wo, x, accumulate=True)
+        return ops.linear_deferred(att, self.wo, x, accumulate=True)   # the next norm may add it
 
 
 register_part("mixer", "attention", AttentionMixer)

@@ -2,6 +2,7 @@
 the order of the reference's attn_rows and mlp_rows (src/api.cu:1673, 1712)."""
 from __future__ import annotations
 
+from ..kernels import ops
 from .registry import Part, build_part, register_part
 
 
@@ -27,17 +28,24 @@ class PreNormBlock(Part):
     def weight_bytes(self):
         return sum(p.weight_bytes() for p in self.parts)
 
-    def forward(self, x, batch, cache, state):
-        # a part may take the norm itself (forward_prenorm) to fuse it into its first kernel;
-        # a part without that method gets the normalised rows
-        if hasattr(self.mixer, "forward_prenorm"):
-            self.mixer.forward_prenorm(self.mixer_norm, x, batch, cache, state)
-        else:
-            self.mixer.forward(self.mixer_norm.forward(x), x, batch, cache, state)
-        if hasattr(self.feed_forward, "forward_prenorm"):
-            self.feed_forward.forward_prenorm(self.feed_forward_norm, x, batch)
-        else:
-            self.feed_forward.forward(self.feed_forward_norm.forward(x), x, batch)
+    takes_pending = True
+
+    @staticmethod
+    def _normed(norm, x, pending):
+        if pending is None:
+            return norm.forward(x)
+        if norm.takes_pending:
+            return norm.forward(x, pending=pending)
+        pending.finish()
+        return norm.forward(x)
+
+    def forward(self, x, batch, cache, state, pending=None):
+        """pending: a sum the layer before has yet to add into x. Returns what this layer leaves
+        to be added (None when x is complete)."""
+        left = self.mixer.forward(self._normed(self.mixer_norm, x, pending), x, batch, cache, state)
+        pending = left if isinstance(left, ops.Pending) else None
+        left = self.feed_forward.forward(self._normed(self.feed_forward_norm, x, pending), x, batch)
+        return left if isinstance(left, ops.Pending) else None
 
 
 register_part("block", "pre_norm", PreNormBlock)

@@ -45,20 +45,10 @@ class SwiGLU(Part):
     def weight_bytes(self):
         return self.wgu.nbytes + self.wdown.nbytes
 
-    def forward_prenorm(self, norm, x, batch):
-        """The same, given the norm part: for a few rows norm, gate/up product and activation are one kernel."""
-        from .norm import RMSNorm
-
-        if type(norm) is RMSNorm and x.shape[0] <= 16:
-            act = torch.empty(x.shape[0], self.inter, dtype=self.ctx.dtype, device=x.device)
-            if ops.norm_linear_swiglu(x, norm.weight, norm.eps, self.wgu, act, GROUP):
-                return ops.linear(act, self.wdown, x, accumulate=True)
-        self.forward(norm.forward(x), x, batch)
-
     def forward(self, xn, x, batch):
         act = torch.empty(xn.shape[0], self.inter, dtype=self.ctx.dtype, device=xn.device)
         ops.linear_swiglu(xn, self.wgu, act, GROUP)
-        ops.linear(act, self.wdown, x, accumulate=True)
+        return ops.linear_deferred(act, self.wdown, x, accumulate=True)   # the next norm may add it
 
 
 register_part("feed_forward", "swiglu", SwiGLU)

@@ -28,11 +28,14 @@ class RMSNorm(Part):
     def weight_bytes(self):
         return self.weight.numel() * self.weight.element_size()
 
-    def forward(self, x, rows=None, out=None):
+    takes_pending = True
+
+    def forward(self, x, rows=None, out=None, pending=None):
+        """pending: a sum that has yet to be added into x (it is added before the norm)."""
         M = x.shape[0] if rows is None else rows.numel()
         if out is None:
             out = torch.empty(M, self.size, dtype=self.ctx.dtype, device=x.device)
-        return ops.rmsnorm(x, self.weight, self.eps, out, rows)
+        return ops.rmsnorm(x, self.weight, self.eps, out, rows, pending)
 
 
 register_part("norm", "rmsnorm", RMSNorm)

@@ -53,6 +53,12 @@ class CacheNeed:
 
 
 class Part:
+    # A mixer's or feed-forward's forward() adds its result into the residual rows x it is given.
+    # It may instead return a kernels.ops.Pending: a sum not yet added into x, which the next
+    # reader of x adds on its way. A norm (or block) whose forward() has a `pending` argument
+    # sets takes_pending; for any other part the sum is finished before the part runs.
+    takes_pending = False
+
     def __init__(self, params: Dict[str, Any], ctx: BuildContext, prefix: str = ""):
         self.params, self.ctx, self.prefix = params, ctx, prefix
 

@@ -61,10 +61,13 @@ class RotaryEmbedding(Part):
             else:
                 self.table = torch.zeros(ctx.max_model_len, 0, 2, dtype=torch.float32, device=ctx.device)
 
-    def rotate_and_store(self, qkv, positions, slot_map, q_out, k_cache, v_cache, n_heads, n_kv_heads):
-        """q of qkv rotated into q_out; k rotated and v raw into the pages at slot_map (None: no write)."""
+    takes_pending = True
+
+    def rotate_and_store(self, qkv, positions, slot_map, q_out, k_cache, v_cache, n_heads, n_kv_heads, pending=None):
+        """q of qkv rotated into q_out; k rotated and v raw into the pages at slot_map (None: no write).
+        pending: qkv has yet to be summed from its product's slices (kernels.ops.Pending)."""
         return ops.rope_kv_write(qkv, positions, slot_map, self.table, q_out, k_cache, v_cache, n_heads, n_kv_heads,
-                                 self.head_dim, self.rotary_dim, self.ctx.page_size)
+                                 self.head_dim, self.rotary_dim, self.ctx.page_size, pending)
 
 
 register_part("position", "rope", RotaryEmbedding)

@@ -277,67 +277,73 @@ def test_flash_prefill_far_key_and_cutting(impl):
 
 
 # ------------------------------------------------------------------------------------------
-# decode products with norm, rotation and activation fused in
+# small products left as K slices, and the kernels that consume them
 # ------------------------------------------------------------------------------------------
-@pytest.mark.parametrize("M,I,K,wdt", [(1, 512, 256, torch.bfloat16), (8, 8192, 2048, torch.bfloat16), (13, 352, 520, torch.float32),
-                                       (16, 1024, 704, torch.bfloat16)])
-def test_fused_norm_gate_up_swiglu(M, I, K, wdt):
+@pytest.mark.parametrize("M,H,K", [(1, 2048, 2048), (8, 2048, 8192), (13, 520, 352), (40, 3072, 1024), (64, 4096, 256)])
+def test_slices_added_by_the_norm(M, H, K):
+    """x += a w^T and RMSNorm(x) with the slices added by the norm kernel: bit-identical to the
+    product finishing itself and the plain norm after it; also on gathered rows, where x stays."""
     from hipinfer_b200.kernels import ops
 
-    x = rnd(M + 2, K, seed=41, scale=2.0, dtype=torch.float32)
-    nw = (1 + rnd(K, seed=42, dtype=torch.float32) * 0.1).to(wdt)
-    g, u = rnd(I, K, seed=43, scale=0.05), rnd(I, K, seed=44, scale=0.05)
-    gu = ops.Weight(torch.stack([g.reshape(I // 16, 16, K), u.reshape(I // 16, 16, K)], 1).reshape(2 * I, K).contiguous())
-    out = torch.full((M + 1, I), 7.0, dtype=torch.bfloat16, device=DEV)
-    assert fast().norm_linear_swiglu(x, None, nw, 1e-5, gu, out[:M], 16)
+    a, w = rnd(M, K, seed=41), ops.Weight(rnd(H, K, seed=42, scale=0.05))
+    x0 = rnd(M, H, seed=43, scale=2.0, dtype=torch.float32)
+    nw = (1 + rnd(H, seed=44, dtype=torch.float32) * 0.1).to(torch.bfloat16)
+    x_ref = x0.clone()
+    ops.linear(a, w, x_ref, accumulate=True)
+    y_ref = ops.rmsnorm(x_ref, nw, 1e-5, torch.empty(M, H, dtype=torch.bfloat16, device=DEV))
+    want = x0.float().cpu() + a.float().cpu() @ w.t.float().cpu().T
+    assert float((x_ref.cpu() - want).abs().max()) < 1e-3 * float(want.abs().max())
+    x = x0.clone()
+    pend = ops.linear_deferred(a, w, x, accumulate=True)
+    assert pend is not None and torch.equal(x, x0)          # nothing added yet
+    y = ops.rmsnorm(x, nw, 1e-5, torch.full((M, H), 3.0, dtype=torch.bfloat16, device=DEV), pending=pend)
     sync_check()
-    xn = plain.rmsnorm(x[:M].cpu(), nw.float().cpu(), 1e-5).to(torch.bfloat16).float()
-    gg, uu = xn @ g.float().cpu().T, xn @ u.float().cpu().T
-    ref = gg / (1 + torch.exp(-gg)) * uu
-    assert float((out[:M].float().cpu() - ref).abs().max()) < 1.5e-2 * max(1.0, float(ref.abs().max()))
-    assert bool((out[M] == 7.0).all())
-    rows = torch.tensor([M + 1, 0], dtype=torch.int32, device=DEV)      # gathered rows
-    out2 = torch.empty(2, I, dtype=torch.bfloat16, device=DEV)
-    assert fast().norm_linear_swiglu(x, rows, nw, 1e-5, gu, out2, 16)
-    assert torch.equal(out2[1], out[0])
+    assert torch.equal(x, x_ref) and torch.equal(y, y_ref)
+    rows = torch.tensor([M - 1, 0, M - 1], dtype=torch.int32, device=DEV)
+    x = x0.clone()
+    pend = ops.linear_deferred(a, w, x, accumulate=True)
+    y = ops.rmsnorm(x, nw, 1e-5, torch.empty(3, H, dtype=torch.bfloat16, device=DEV), rows=rows, pending=pend)
+    assert torch.equal(y, y_ref[[M - 1, 0, M - 1]]) and torch.equal(x, x0)
+    # finished by hand, and the guard against a product in between
+    x = x0.clone()
+    ops.linear_deferred(a, w, x, accumulate=True).finish()
+    assert torch.equal(x, x_ref)
+    pend = ops.linear_deferred(a, w, x, accumulate=True)
+    ops.linear(a, w, torch.empty(M, H, device=DEV))
+    with pytest.raises(RuntimeError, match="overwritten"):
+        pend.finish()
 
 
 @pytest.mark.parametrize("M,Hq,Hkv,D,K", [(1, 32, 8, 64, 2048), (8, 32, 8, 64, 2048), (16, 8, 2, 64, 256), (5, 4, 2, 128, 512),
-                                          (3, 2, 1, 64, 72)])
-def test_fused_norm_qkv_rope_and_cache_write(M, Hq, Hkv, D, K):
-    """Against the same steps run one after the other (norm, product, rotation + cache write)."""
+                                          (37, 3, 1, 72, 72)])
+def test_slices_added_by_the_rotation(M, Hq, Hkv, D, K):
+    """q/k/v product, rotation and cache write with the slices added by the rotation kernel:
+    bit-identical to the three steps one after the other."""
     from hipinfer_b200.kernels import ops
     from hipinfer_b200.parts.rotary import rope_inv_freq
 
     ps, n_pages = 16, 6
     N = (Hq + 2 * Hkv) * D
-    x = rnd(M, K, seed=51, scale=2.0, dtype=torch.float32)
-    nw = (1 + rnd(K, seed=52, dtype=torch.float32) * 0.1).to(torch.bfloat16)
+    xn = rnd(M, K, seed=51)
     w = ops.Weight(rnd(N, K, seed=53, scale=0.05))
     table = ops.rope_table(rope_inv_freq(D, 500000.0).to(DEV), 128)
     g = torch.Generator().manual_seed(54)
     pos = torch.randint(0, 128, (M,), generator=g).to(torch.int32).to(DEV)
     slots = torch.randperm(ps * n_pages, generator=g)[:M].to(torch.int32).to(DEV)
-    # separate steps
-    xn = torch.empty(M, K, dtype=torch.bfloat16, device=DEV)
-    ops.rmsnorm(x, nw, 1e-5, xn)
     qkv = torch.empty(M, N, dtype=torch.float32, device=DEV)
-    fast().gemm_stream(xn, w.t, qkv, fast().EPI_F32)
+    ops.linear(xn, w, qkv)
     q_ref = torch.empty(M, Hq * D, dtype=torch.bfloat16, device=DEV)
     kc_ref = torch.full((n_pages, Hkv, ps, D), 9.0, dtype=torch.bfloat16, device=DEV)
     vc_ref = kc_ref.clone()
     ops.rope_kv_write(qkv, pos, slots, table, q_ref, kc_ref, vc_ref, Hq, Hkv, D, D, ps)
-    # one kernel
     q = torch.empty_like(q_ref)
     kc, vc = torch.full_like(kc_ref, 9.0), torch.full_like(vc_ref, 9.0)
-    assert fast().norm_qkv_rope(x, nw, 1e-5, w, pos, slots, table, q, kc, vc, Hq, Hkv, D, D, ps)
+    pend = ops.linear_deferred(xn, w, qkv)
+    assert pend is not None
+    ops.rope_kv_write(qkv, pos, slots, table, q, kc, vc, Hq, Hkv, D, D, ps, pending=pend)
     sync_check()
-    for got, ref, name in ((q, q_ref, "q"), (kc, kc_ref, "k cache"), (vc, vc_ref, "v cache")):
-        scale = float(ref.float().abs().max())
-        assert float((got.float() - ref.float()).abs().max()) <= 1.6e-2 * scale, name   # a bf16 ulp where the norm's sum order differs
-    assert bool(((kc == 9.0) == (kc_ref == 9.0)).all()) and bool(((vc == 9.0) == (vc_ref == 9.0)).all())
-    # without a slot map nothing is stored
-    kc2 = torch.full_like(kc_ref, 9.0)
-    assert fast().norm_qkv_rope(x, nw, 1e-5, w, pos, None, table, q, kc2, kc2, Hq, Hkv, D, D, ps)
+    assert torch.equal(q, q_ref) and torch.equal(kc, kc_ref) and torch.equal(vc, vc_ref)
+    kc2 = torch.full_like(kc_ref, 9.0)                      # without a slot map nothing is stored
+    ops.rope_kv_write(qkv, pos, None, table, q, kc2, kc2, Hq, Hkv, D, D, ps, pending=ops.linear_deferred(xn, w, qkv))
     torch.cuda.synchronize()
-    assert bool((kc2 == 9.0).all())
+    assert bool((kc2 == 9.0).all()) and torch.equal(q, q_ref)
