@@ -251,16 +251,37 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
   __syncthreads();
   if (!is_last) return;
   __threadfence();
+  const int nc = s_hi - s_lo + 1;
   for (int i = tid; i < G * D; i += AD_THREADS) {
     const int gg = i / D, d = i - gg * D;
     const size_t head = (size_t)t * Hq + (size_t)h * G + gg;
-    float m = -INFINITY;
-    for (int c = s_lo; c <= s_hi; c++) m = fmaxf(m, __ldcg(part_ml + (head * S + c) * 2));
-    float a = 0.f, l = 0.f;
-    for (int c = s_lo; c <= s_hi; c++) {
-      const float f = expf(__ldcg(part_ml + (head * S + c) * 2) - m);
-      l += __ldcg(part_ml + (head * S + c) * 2 + 1) * f;
-      a += __ldcg(part_acc + (head * S + c) * D + d) * f;
+    const float2* ml = (const float2*)part_ml + head * S + s_lo;
+    const float* pa = part_acc + (head * S + s_lo) * D + d;
+    float m = -INFINITY, a = 0.f, l = 0.f;
+    if (nc <= 16) {   // every load asked for before the first is used: one round trip to L2
+      float2 v[16];
+      float acc[16];
+#pragma unroll
+      for (int c = 0; c < 16; c++)
+        if (c < nc) { v[c] = __ldcg(ml + c); acc[c] = __ldcg(pa + (size_t)c * D); }
+#pragma unroll
+      for (int c = 0; c < 16; c++)
+        if (c < nc) m = fmaxf(m, v[c].x);
+#pragma unroll
+      for (int c = 0; c < 16; c++)
+        if (c < nc) {
+          const float f = expf(v[c].x - m);
+          l += v[c].y * f;
+          a += acc[c] * f;
+        }
+    } else {
+      for (int c = 0; c < nc; c++) m = fmaxf(m, __ldcg(ml + c).x);
+      for (int c = 0; c < nc; c++) {
+        const float2 v = __ldcg(ml + c);
+        const float f = expf(v.x - m);
+        l += v.y * f;
+        a += __ldcg(pa + (size_t)c * D) * f;
+      }
     }
     out[head * D + d] = __float2bfloat16_rn(a / l);
   }

@@ -9,28 +9,31 @@
 // reason, src/kernels.cuh:164-330).
 #include "common.cuh"
 
+// The sum over the slices of four consecutive columns, added in slice order. All loads are
+// asked for before the first is used (up to 16 slices; the kernels here are short chains of
+// round trips to L2, and every round trip saved is most of a microsecond).
+constexpr int SL_MAX = 16;
 __device__ __forceinline__ float4 slices_sum4(const float* __restrict__ p, int ksplit, long slice_stride) {
+  float4 a[SL_MAX];
+#pragma unroll
+  for (int j = 0; j < SL_MAX; j++)
+    if (j < ksplit) a[j] = __ldcg((const float4*)(p + j * slice_stride));
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  int sl = 0;
-  for (; sl + 4 <= ksplit; sl += 4) {
-    float4 a[4];
 #pragma unroll
-    for (int j = 0; j < 4; j++) a[j] = __ldcg((const float4*)(p + (sl + j) * slice_stride));
-#pragma unroll
-    for (int j = 0; j < 4; j++) { acc.x += a[j].x; acc.y += a[j].y; acc.z += a[j].z; acc.w += a[j].w; }
-  }
-  for (; sl < ksplit; sl++) {
-    const float4 a = __ldcg((const float4*)(p + sl * slice_stride));
-    acc.x += a.x; acc.y += a.y; acc.z += a.z; acc.w += a.w;
+  for (int j = 0; j < SL_MAX; j++)
+    if (j < ksplit) { acc.x += a[j].x; acc.y += a[j].y; acc.z += a[j].z; acc.w += a[j].w; }
+  for (int sl = SL_MAX; sl < ksplit; sl++) {
+    const float4 v = __ldcg((const float4*)(p + sl * slice_stride));
+    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
   }
   return acc;
 }
 
-// One block per row; the row stays in registers between the sum of squares and the scaling
-// (H a multiple of 4, at most 256 * 4 * NV). With `rows` (a gather of some rows, as before the
+// One block of 512 threads per row; the row stays in registers between the sum of squares and
+// the scaling (H a multiple of 4, at most 512 * 4 * NV). With `rows` (a gather of some rows, as before the
 // output head) x itself is left as it is: two entries may name the same row.
 template <int NV>
-__global__ void __launch_bounds__(256) add_rmsnorm_slices_kernel(float* __restrict__ x, long ldx, const float* __restrict__ ws,
+__global__ void __launch_bounds__(512) add_rmsnorm_slices_kernel(float* __restrict__ x, long ldx, const float* __restrict__ ws,
                                                                  int ksplit, long slice_stride, long row_stride,
                                                                  const __nv_bfloat16* __restrict__ w,
                                                                  __nv_bfloat16* __restrict__ y, const int* __restrict__ rows,
@@ -41,7 +44,7 @@ __global__ void __launch_bounds__(256) add_rmsnorm_slices_kernel(float* __restri
   float4 ww[NV];
 #pragma unroll
   for (int i = 0; i < NV; i++) {   // the norm's weight does not depend on the kernel ahead
-    const int c = threadIdx.x + i * 256;
+    const int c = threadIdx.x + i * 512;
     ww[i] = c < nvec ? hb_load4(w + 4 * c) : make_float4(0.f, 0.f, 0.f, 0.f);
   }
   hb_pdl_wait();
@@ -52,10 +55,10 @@ __global__ void __launch_bounds__(256) add_rmsnorm_slices_kernel(float* __restri
   float ss = 0.f;
 #pragma unroll
   for (int i = 0; i < NV; i++) {
-    const int c = threadIdx.x + i * 256;
+    const int c = threadIdx.x + i * 512;
     v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
     if (c < nvec) {
-      const float4 a = slices_sum4(pr + 4 * c, ksplit, slice_stride), o = hb_load4(xr + 4 * c);
+      const float4 o = hb_load4(xr + 4 * c), a = slices_sum4(pr + 4 * c, ksplit, slice_stride);
       v[i] = make_float4(o.x + a.x, o.y + a.y, o.z + a.z, o.w + a.w);
       if (!rows) hb_store4(xr + 4 * c, v[i]);
     }
@@ -66,7 +69,7 @@ __global__ void __launch_bounds__(256) add_rmsnorm_slices_kernel(float* __restri
   __nv_bfloat16* yr = y + (size_t)blockIdx.x * H;
 #pragma unroll
   for (int i = 0; i < NV; i++) {
-    const int c = threadIdx.x + i * 256;
+    const int c = threadIdx.x + i * 512;
     if (c < nvec)
       hb_store4(yr + 4 * c, make_float4(ww[i].x * (v[i].x * inv), ww[i].y * (v[i].y * inv), ww[i].z * (v[i].z * inv),
                                         ww[i].w * (v[i].w * inv)));
@@ -83,8 +86,9 @@ HB_EXPORT int hb_add_rmsnorm_slices(float* x, long ldx, const float* ws, int ksp
   if (ksplit < 1) HB_FAIL("hb_add_rmsnorm_slices: %d slices", ksplit);
   const __nv_bfloat16* ww = (const __nv_bfloat16*)w;
   __nv_bfloat16* yy = (__nv_bfloat16*)y;
-  if (H <= 2048) hb_launch(add_rmsnorm_slices_kernel<2>, M, 256, 0, s, x, ldx, ws, ksplit, slice_stride, row_stride, ww, yy, rows, H, eps);
-  else hb_launch(add_rmsnorm_slices_kernel<8>, M, 256, 0, s, x, ldx, ws, ksplit, slice_stride, row_stride, ww, yy, rows, H, eps);
+  if (H <= 2048) hb_launch(add_rmsnorm_slices_kernel<1>, M, 512, 0, s, x, ldx, ws, ksplit, slice_stride, row_stride, ww, yy, rows, H, eps);
+  else if (H <= 4096) hb_launch(add_rmsnorm_slices_kernel<2>, M, 512, 0, s, x, ldx, ws, ksplit, slice_stride, row_stride, ww, yy, rows, H, eps);
+  else hb_launch(add_rmsnorm_slices_kernel<4>, M, 512, 0, s, x, ldx, ws, ksplit, slice_stride, row_stride, ww, yy, rows, H, eps);
   HB_CHECK_LAUNCH("hb_add_rmsnorm_slices");
   return 0;
 }

@@ -281,8 +281,9 @@ def test_flash_prefill_far_key_and_cutting(impl):
 # ------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("M,H,K", [(1, 2048, 2048), (8, 2048, 8192), (13, 520, 352), (40, 3072, 1024), (64, 4096, 256)])
 def test_slices_added_by_the_norm(M, H, K):
-    """x += a w^T and RMSNorm(x) with the slices added by the norm kernel: bit-identical to the
-    product finishing itself and the plain norm after it; also on gathered rows, where x stays."""
+    """x += a w^T and RMSNorm(x) with the slices added by the norm kernel: x bit-identical to the
+    product finishing itself, the norm equal to the plain norm after it up to the rounding of its
+    sum of squares (another order) and of the result to bfloat16; also on gathered rows, where x stays."""
     from hipinfer_b200.kernels import ops
 
     a, w = rnd(M, K, seed=41), ops.Weight(rnd(H, K, seed=42, scale=0.05))
@@ -298,12 +299,14 @@ def test_slices_added_by_the_norm(M, H, K):
     assert pend is not None and torch.equal(x, x0)          # nothing added yet
     y = ops.rmsnorm(x, nw, 1e-5, torch.full((M, H), 3.0, dtype=torch.bfloat16, device=DEV), pending=pend)
     sync_check()
-    assert torch.equal(x, x_ref) and torch.equal(y, y_ref)
+    assert torch.equal(x, x_ref)
+    ulp = lambda got, ref: float(((got.float() - ref.float()).abs() / ref.float().abs().clamp_min(1e-3)).max())
+    assert ulp(y, y_ref) <= 2.0 ** -7 and float((y != y_ref).float().mean()) < 0.01
     rows = torch.tensor([M - 1, 0, M - 1], dtype=torch.int32, device=DEV)
     x = x0.clone()
     pend = ops.linear_deferred(a, w, x, accumulate=True)
-    y = ops.rmsnorm(x, nw, 1e-5, torch.empty(3, H, dtype=torch.bfloat16, device=DEV), rows=rows, pending=pend)
-    assert torch.equal(y, y_ref[[M - 1, 0, M - 1]]) and torch.equal(x, x0)
+    y2 = ops.rmsnorm(x, nw, 1e-5, torch.empty(3, H, dtype=torch.bfloat16, device=DEV), rows=rows, pending=pend)
+    assert torch.equal(y2, y[[M - 1, 0, M - 1]]) and torch.equal(x, x0)
     # finished by hand, and the guard against a product in between
     x = x0.clone()
     ops.linear_deferred(a, w, x, accumulate=True).finish()
