@@ -8,6 +8,15 @@
 // of the core library.
 #include "tc_common.cuh"
 
+#ifndef HB_AD_LATE_TRIGGER
+#define HB_AD_LATE_TRIGGER 0   // 1: dependents start only when every block has its keys; measured 1 to 3 % slower at batch 1 and 8
+#endif
+#ifndef HB_AD_HEAD_FIRST
+#define HB_AD_HEAD_FIRST 0   // 1: blocks next to each other read pieces of the same pages; measured: no difference
+#endif
+#ifndef HB_AD_TMA
+#define HB_AD_TMA 1
+#endif
 #ifndef HB_AD_THREADS
 #define HB_AD_THREADS 128
 #endif
@@ -17,6 +26,13 @@ constexpr int AD_THREADS = HB_AD_THREADS, AD_WARPS = AD_THREADS / 32;
 // swizzle that makes ldmatrix of eight consecutive rows free of bank conflicts.
 template <int D> __device__ __forceinline__ uint32_t ad_swz(int row, int c) {
   return (uint32_t)(row * (D * 2) + ((c ^ (row & 7)) << 4));
+}
+
+// The same for a tile that TMA wrote: per 64 columns a [keys][128 bytes] block in the 128-byte
+// swizzle (16-byte chunk ^ (row & 7)); head_dim 128 is two such blocks, half_stride bytes apart.
+template <int D, bool TMA> __device__ __forceinline__ uint32_t ad_off(int row, int c, uint32_t half_stride) {
+  if constexpr (TMA) return (uint32_t)((c >> 3) * half_stride + row * 128 + (((c & 7) ^ (row & 7)) << 4));
+  else return ad_swz<D>(row, c);
 }
 
 // Rows [r_lo, r_hi) of the tile (row r = key k0 + r) by cp.async, page by page: the page
@@ -81,23 +97,39 @@ HB_EXPORT int hb_ad_stamps(unsigned long long* out) {
 // under programmatic dependent launch the cache streams in while the projections still run.
 // A row that spans several chunks is finished by the block that ends last (a counter per
 // (row, kv head), left at zero again): it adds the chunks' partials in ascending chunk order.
-template <int D, int G>
+//
+// TMA: the tile comes by cp.async.bulk.tensor, one box per page and 64 columns, asked for by lane 0
+// of the warp that will use it and awaited on that warp's own mbarrier (bounded). The copy engine
+// keeps far more bytes in flight than 16-byte loads from 128 threads can: this is the kernel for
+// whole pages (no window, page size 8 to 64); the other one takes the rest.
+template <int D, int G, bool TMA>
 __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
+    const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, int* __restrict__ status,
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc,
     const int* __restrict__ bt, int bt_stride, const int* __restrict__ row_req, const int* __restrict__ pos,
     __nv_bfloat16* __restrict__ out, float* __restrict__ part_acc, float* __restrict__ part_ml, int Hq, int Hkv,
     int page_size, int window, float scale_log2, int chunk, int S, const int* __restrict__ q_len, int row_limit,
     const int* __restrict__ ctx_len, int* __restrict__ counters) {
   constexpr int CH = D / 8, KS = D / 16, NT_O = D / 8, WK = 64;  // WK: keys per warp pass
-  extern __shared__ __align__(128) uint8_t smem_raw[];
+  extern __shared__ __align__(128) uint8_t smem_dyn[];
+  uint8_t* smem_raw = TMA ? (uint8_t*)(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023) : smem_dyn;   // the swizzle wants 1 KB
   const uint32_t sK = hb_smem_u32(smem_raw), sV = sK + chunk * D * 2, sQ = sV + chunk * D * 2;
+  const uint32_t hs = (uint32_t)chunk * 128;                            // bytes between the 64-column halves of a TMA tile
   float* red_o = (float*)(smem_raw + 2 * chunk * D * 2 + 16 * D * 2);  // [warps][G][D]
   float* red_ml = red_o + AD_WARPS * G * D;                             // [warps][G][2]
   __shared__ int is_last;
+  __shared__ __align__(8) uint64_t bars[AD_WARPS];
+  __shared__ int abort_flag;
+#if !HB_AD_LATE_TRIGGER
   hb_pdl_launch();
+#endif
   AD_STAMP(0);
   AD_STAMP(5);
+#if HB_AD_HEAD_FIRST
+  const int t = blockIdx.z, h = blockIdx.x, s = blockIdx.y;   // blocks next to each other read pieces of the same pages
+#else
   const int t = blockIdx.z, h = blockIdx.y, s = blockIdx.x;
+#endif
   const int rq = row_req[t];
   const int p = pos[t];
   const int lo = window > 0 ? max(0, p - window + 1) : 0;
@@ -110,6 +142,50 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
   const int n_old = ctx_len ? max(0, min(k1, ctx_len[rq]) - k0) : 0;   // rows of the tile from earlier steps
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, tq = lane & 3;
   const int* table = bt + (size_t)rq * bt_stride;
+  bool loaded = true;
+  if constexpr (TMA) {
+    // whole pages: row r of the tile is key s * chunk + r; warp w owns rows 64 w .. 64 w + 63
+    if (tid == 0) {
+      for (int w = 0; w < AD_WARPS; w++) hb_mbar_init(&bars[w], 2);
+      abort_flag = 0;
+      hb_fence_barrier_init();
+    }
+    __syncthreads();
+    const int r_w = warp * WK, page_bytes = page_size * D * 2 * 2;   // a page's keys and values of one kv head
+    const int pages_w = r_w < nk ? min(WK / page_size, (nk - r_w + page_size - 1) / page_size) : 0;
+    const int old_w = min(pages_w, max(0, n_old - r_w) / page_size);  // pages wholly from earlier steps
+    const int page0 = (k0 + r_w) / page_size;
+    if (pages_w > 0) {
+      // rows of this warp beyond its last page are never written: the values there must be finite (they meet P = 0)
+      for (int i = (r_w + pages_w * page_size) * CH + lane; i < (r_w + WK) * CH; i += 32)
+        asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(sV + ad_off<D, true>(i / CH, i % CH, hs)), "r"(0u) : "memory");
+      if (lane == 0) {
+        hb_mbar_expect_tx(&bars[warp], (uint32_t)(old_w * page_bytes));
+        for (int j = 0; j < old_w; j++) {
+          const int row = (__ldg(table + page0 + j) * Hkv + h) * page_size, dst = (r_w + j * page_size) * 128;
+#pragma unroll
+          for (int hf = 0; hf < D / 64; hf++) {
+            hb_tma_load_2d(smem_raw + hf * hs + dst, &map_k, &bars[warp], hf * 64, row);
+            hb_tma_load_2d(smem_raw + chunk * D * 2 + hf * hs + dst, &map_v, &bars[warp], hf * 64, row);
+          }
+        }
+      }
+    }
+    AD_STAMP(1);
+    hb_pdl_wait();
+    AD_STAMP(2);
+    if (pages_w > 0 && lane == 0) {   // the pages that hold this step's keys
+      hb_mbar_expect_tx(&bars[warp], (uint32_t)((pages_w - old_w) * page_bytes));
+      for (int j = old_w; j < pages_w; j++) {
+        const int row = (__ldg(table + page0 + j) * Hkv + h) * page_size, dst = (r_w + j * page_size) * 128;
+#pragma unroll
+        for (int hf = 0; hf < D / 64; hf++) {
+          hb_tma_load_2d(smem_raw + hf * hs + dst, &map_k, &bars[warp], hf * 64, row);
+          hb_tma_load_2d(smem_raw + chunk * D * 2 + hf * hs + dst, &map_v, &bars[warp], hf * 64, row);
+        }
+      }
+    }
+  } else {
   const int rows_pad = (nk + WK - 1) / WK * WK;  // rows the warps will touch; the tail is zeroed
   for (int i = nk * CH + tid; i < rows_pad * CH; i += AD_THREADS) {
     const uint32_t off = ad_swz<D>(i / CH, i % CH);
@@ -123,6 +199,7 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
   AD_STAMP(2);
   ad_load_rows<D>(kc, vc, table, Hkv, h, page_size, k0, n_old, nk, sK, sV, tid);   // this step's keys
   hb_cp_async_commit();
+  }
   // Q tile [16][D]: rows 0..G-1 are the heads of this kv head, the rest zero
   for (int i = tid; i < 16 * CH; i += AD_THREADS) {
     const int r = i / CH, c = i - r * CH;
@@ -130,8 +207,17 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
     if (r < G) v = *(const uint4*)(q + ((size_t)t * Hq + (size_t)h * G + r) * D + c * 8);
     asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(sQ + ad_swz<D>(r, c)), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
   }
-  hb_cp_async_wait<0>();
+  if constexpr (!TMA) hb_cp_async_wait<0>();
   __syncthreads();
+  if constexpr (TMA) {
+    if (warp * WK < nk) loaded = hb_mbar_wait(&bars[warp], 0, &abort_flag);
+    if (!loaded && lane == 0) atomicExch(status, 1);   // the result is not valid; the host raises
+  }
+#if HB_AD_LATE_TRIGGER
+  // the kernels behind this one start (and ask for their weights) only when every block here
+  // has its keys and values: until then the memory system serves the attention alone
+  hb_pdl_launch();
+#endif
   AD_STAMP(3);
 
   float m_run = -INFINITY, l_run = 0.f;  // of row g (a head when g < G), over this warp's keys
@@ -145,7 +231,6 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
     for (int kk = 0; kk < KS; kk++) hb_ldmatrix_x4(qf[kk], sQ + ad_swz<D>((mi & 1) * 8 + r, kk * 2 + (mi >> 1)));
   }
   for (int kb = warp * WK; kb < nk; kb += AD_WARPS * WK) {
-    const uint32_t tK = sK + kb * D * 2, tV = sV + kb * D * 2;  // 64 rows are a whole number of 8-row swizzle groups
     float sc[8][4];
 #pragma unroll
     for (int i = 0; i < 8; i++) sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.f;
@@ -156,7 +241,7 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
 #pragma unroll
         for (int np = 0; np < 4; np++) {
           uint32_t b[4];
-          hb_ldmatrix_x4(b, tK + ad_swz<D>(np * 16 + (mi >> 1) * 8 + r, kk * 2 + (mi & 1)));
+          hb_ldmatrix_x4(b, sK + ad_off<D, TMA>(kb + np * 16 + (mi >> 1) * 8 + r, kk * 2 + (mi & 1), hs));
           hb_mma_16816(sc[2 * np], qf[kk], b);
           hb_mma_16816(sc[2 * np + 1], qf[kk], b + 2);
         }
@@ -194,7 +279,7 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
 #pragma unroll
         for (int cp = 0; cp < NT_O / 2; cp++) {
           uint32_t b[4];
-          hb_ldmatrix_x4_trans(b, tV + ad_swz<D>(j2 * 16 + (mi & 1) * 8 + r, cp * 2 + (mi >> 1)));
+          hb_ldmatrix_x4_trans(b, sV + ad_off<D, TMA>(kb + j2 * 16 + (mi & 1) * 8 + r, cp * 2 + (mi >> 1), hs));
           hb_mma_16816(o[2 * cp], pf[j2], b);
           hb_mma_16816(o[2 * cp + 1], pf[j2], b + 2);
         }
@@ -287,22 +372,24 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
   }
 }
 
-template <int D>
-static int launch_decode(int G, dim3 grid, size_t smem, cudaStream_t st, const __nv_bfloat16* q, const __nv_bfloat16* kc,
-                         const __nv_bfloat16* vc, const int* bt, int bt_stride, const int* row_req, const int* pos,
-                         __nv_bfloat16* out, float* pa, float* pm, int Hq, int Hkv, int page_size, int window, float scale,
-                         int chunk, int S, const int* q_len, int row_limit, const int* ctx_len, int* counters) {
+template <int D, bool TMA>
+static int launch_decode(int G, dim3 grid, size_t smem, cudaStream_t st, const CUtensorMap& mk, const CUtensorMap& mv,
+                         int* status, const __nv_bfloat16* q, const __nv_bfloat16* kc, const __nv_bfloat16* vc,
+                         const int* bt, int bt_stride, const int* row_req, const int* pos, __nv_bfloat16* out, float* pa,
+                         float* pm, int Hq, int Hkv, int page_size, int window, float scale, int chunk, int S,
+                         const int* q_len, int row_limit, const int* ctx_len, int* counters) {
 #define HB_AD_CASE(GG)                                                                                              \
   case GG:                                                                                                          \
     {                                                                                                               \
       static bool configured = false;                                                                               \
       if (!configured) {                                                                                            \
-        cudaFuncSetAttribute(attn_decode_kernel<D, GG>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);   \
+        cudaFuncSetAttribute(attn_decode_kernel<D, GG, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
         configured = true;                                                                                          \
       }                                                                                                             \
     }                                                                                                               \
-    hb_launch(attn_decode_kernel<D, GG>, grid, AD_THREADS, smem, st, q, kc, vc, bt, bt_stride, row_req, pos, out, pa, pm, \
-              Hq, Hkv, page_size, window, scale, chunk, S, q_len, row_limit, ctx_len, counters);                     \
+    hb_launch(attn_decode_kernel<D, GG, TMA>, grid, AD_THREADS, smem, st, mk, mv, status, q, kc, vc, bt, bt_stride,  \
+              row_req, pos, out, pa, pm, Hq, Hkv, page_size, window, scale, chunk, S, q_len, row_limit, ctx_len,    \
+              counters);                                                                                            \
     return 0;
   switch (G) {
     HB_AD_CASE(1) HB_AD_CASE(2) HB_AD_CASE(3) HB_AD_CASE(4) HB_AD_CASE(5) HB_AD_CASE(6) HB_AD_CASE(7) HB_AD_CASE(8)
@@ -321,27 +408,48 @@ HB_EXPORT int hb_attn_decode_supported(int Hq, int Hkv, int D) {
 // between calls (needed when S > 1). With q_len given, rows of requests whose portion has
 // row_limit rows or more are skipped (the flash kernel computes those). ctx_len (per request,
 // or null): the tokens that were in the cache before this step; their keys may be read before
-// the kernel ahead in the stream has ended.
-HB_EXPORT int hb_attn_decode(const void* q, const void* kc, const void* vc, const int* bt, int bt_stride,
+// the kernel ahead in the stream has ended. n_pages: the pages the cache holds (its first
+// extent); status: the word a bounded wait that ran out sets to 1. With both, no window, a chunk
+// of 256 and pages of 8 to 64 tokens the keys and values come by TMA.
+HB_EXPORT int hb_attn_decode(const void* q, const void* kc, const void* vc, long n_pages, const int* bt, int bt_stride,
                              const int* row_req, const int* pos, void* out, float* workspace, int* counters, int T,
                              int Hq, int Hkv, int D, int page_size, int window, float scale, int chunk, int max_pos,
-                             const int* q_len, int row_limit, const int* ctx_len, cudaStream_t st) {
+                             const int* q_len, int row_limit, const int* ctx_len, int* status, cudaStream_t st) {
   if (T <= 0) return 0;
   if (!hb_attn_decode_supported(Hq, Hkv, D)) HB_FAIL("hb_attn_decode: %d/%d heads of %d are not supported", Hq, Hkv, D);
   if (chunk <= 0 || chunk % 32) HB_FAIL("hb_attn_decode: chunk %d must be a positive multiple of 32", chunk);
-  if (T > 65535 || Hkv > 65535) HB_FAIL("hb_attn_decode: %d rows / %d kv heads are beyond the grid limit", T, Hkv);
+  if (T > 65535 || Hkv > 65535 || max_pos / chunk + 1 > 65535) HB_FAIL("hb_attn_decode: %d rows / %d kv heads / %d chunks are beyond the grid limit", T, Hkv, max_pos / chunk + 1);
   const int G = Hq / Hkv, S = max_pos / chunk + 1;
   if (S > 1 && (!workspace || !counters)) HB_FAIL("hb_attn_decode: rows that span %d chunks need a workspace and counters", S);
   if (chunk % 64) HB_FAIL("hb_attn_decode: chunk %d must be a multiple of 64", chunk);
-  const size_t smem = 2 * (size_t)chunk * D * 2 + 16 * (size_t)D * 2 + AD_WARPS * (size_t)G * (D + 2) * sizeof(float);
+  const long cache_rows = n_pages * Hkv * page_size;
+  const bool tma = HB_AD_TMA && status && n_pages > 0 && window == 0 && chunk == AD_WARPS * 64 && page_size % 8 == 0 &&
+                   page_size <= 64 && 64 % page_size == 0 && cache_rows < (1L << 31) && !(((uintptr_t)kc | (uintptr_t)vc) & 15);
+  const size_t smem = 2 * (size_t)chunk * D * 2 + 16 * (size_t)D * 2 + AD_WARPS * (size_t)G * (D + 2) * sizeof(float) +
+                      (tma ? 1024 : 0);
   if (smem > 200 * 1024) HB_FAIL("hb_attn_decode: %zu bytes of shared memory (chunk %d, head_dim %d)", smem, chunk, D);
   float* pa = workspace;
   float* pm = workspace ? workspace + (size_t)T * Hq * S * D : nullptr;
+#if HB_AD_HEAD_FIRST
+  dim3 grid(Hkv, S, T);
+#else
   dim3 grid(S, Hkv, T);
+#endif
   const __nv_bfloat16 *qq = (const __nv_bfloat16*)q, *kk = (const __nv_bfloat16*)kc, *vv = (const __nv_bfloat16*)vc;
+  CUtensorMap mk, mv;
+  memset(&mk, 0, sizeof(mk));
+  memset(&mv, 0, sizeof(mv));
+  if (tma) {   // the cache as [pages * kv heads * page_size rows][D], a box = one page of one kv head, 64 columns
+    if (hb_make_tensor_map_bf16(&mk, kc, (uint64_t)cache_rows, (uint64_t)D, (uint64_t)D, (uint32_t)page_size)) return -1;
+    if (hb_make_tensor_map_bf16(&mv, vc, (uint64_t)cache_rows, (uint64_t)D, (uint64_t)D, (uint32_t)page_size)) return -1;
+  }
+  const float sl2 = scale * 1.4426950408889634f;
   int r = 1;
-  if (D == 64) r = launch_decode<64>(G, grid, smem, st, qq, kk, vv, bt, bt_stride, row_req, pos, (__nv_bfloat16*)out, pa, pm, Hq, Hkv, page_size, window, scale * 1.4426950408889634f, chunk, S, q_len, row_limit, ctx_len, counters);
-  else if (D == 128) r = launch_decode<128>(G, grid, smem, st, qq, kk, vv, bt, bt_stride, row_req, pos, (__nv_bfloat16*)out, pa, pm, Hq, Hkv, page_size, window, scale * 1.4426950408889634f, chunk, S, q_len, row_limit, ctx_len, counters);
+#define HB_AD_ARGS G, grid, smem, st, mk, mv, status, qq, kk, vv, bt, bt_stride, row_req, pos, (__nv_bfloat16*)out, pa, pm, Hq, Hkv, \
+                   page_size, window, sl2, chunk, S, q_len, row_limit, ctx_len, counters
+  if (D == 64) r = tma ? launch_decode<64, true>(HB_AD_ARGS) : launch_decode<64, false>(HB_AD_ARGS);
+  else if (D == 128) r = tma ? launch_decode<128, true>(HB_AD_ARGS) : launch_decode<128, false>(HB_AD_ARGS);
+#undef HB_AD_ARGS
   if (r) HB_FAIL("hb_attn_decode: no kernel for group %d", G);
   HB_CHECK_LAUNCH("hb_attn_decode");
   return 0;

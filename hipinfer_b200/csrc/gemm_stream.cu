@@ -67,7 +67,8 @@ template <int NT, bool DEEP>
 __global__ void __launch_bounds__(192) gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w,
                                                           const __grid_constant__ CUtensorMap map_x, void* C, long ldc,
                                                           int M, int N, int K, int kslice, float* ws, int* counters,
-                                                          int epi, int* status, int defer) {
+                                                          int epi, int* status, int defer,
+                                                          const __nv_bfloat16* __restrict__ W, long ldw) {
   using S = StreamCfg<NT, DEEP>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -111,9 +112,6 @@ __global__ void __launch_bounds__(192) gemm_stream_kernel(const __grid_constant_
         hb_mbar_expect_tx(&full[kb], S::STAGE);
         hb_tma_load_2d(smem + kb * S::STAGE, &map_w, &full[kb], k_begin + kb * ST_BK, n0);
       }
-      // and the next weight tiles of this CTA are asked into L2 meanwhile
-      const int ahead = num_kb < pre + HB_STREAM_L2_AHEAD ? num_kb : pre + HB_STREAM_L2_AHEAD;
-      for (int kb = pre; kb < ahead; kb++) hb_tma_prefetch_l2_2d(&map_w, k_begin + kb * ST_BK, n0);
       hb_pdl_wait();
       HB_STAMP(2);
       for (int kb = 0; kb < pre; kb++)
@@ -146,6 +144,18 @@ __global__ void __launch_bounds__(192) gemm_stream_kernel(const __grid_constant_
     }
   } else {
     // epilogue warps: lane = output column n0 + 32 * warp + lane, v[m] = token m
+    if (HB_STREAM_L2_AHEAD > 0) {
+      // idle until the product is done: they ask the weight tiles that will not fit into the
+      // stages into L2 (one 128-byte line of one weight row per thread and tile)
+      const int pre = num_kb < S::STAGES ? num_kb : S::STAGES;
+      const int ahead = num_kb < pre + HB_STREAM_L2_AHEAD ? num_kb : pre + HB_STREAM_L2_AHEAD;
+      const int row = n0 + threadIdx.x;
+      if (row < N)
+        for (int kb = pre; kb < ahead; kb++) {
+          const int k = k_begin + kb * ST_BK;
+          if (k < K) asm volatile("prefetch.global.L2 [%0];" ::"l"(W + (size_t)row * ldw + k));
+        }
+    }
     const bool ok = hb_mbar_wait(done, 0, abort_flag);
     if (threadIdx.x == 0) HB_STAMP(5);
     hb_tc_fence_after();
@@ -297,7 +307,7 @@ HB_EXPORT int hb_gemm_stream_plan(int N, int K, int* kslice, int* ksplit, long* 
 }
 
 template <int NT, bool DEEP>
-static int launch_stream(const CUtensorMap& mw, const CUtensorMap& mx, void* C, long ldc, int M, int N, int K, int kslice,
+static int launch_stream(const CUtensorMap& mw, const CUtensorMap& mx, const __nv_bfloat16* W, long ldw, void* C, long ldc, int M, int N, int K, int kslice,
                          int ksplit, int n_blocks, float* ws, int* counters, int epi, int* status, cudaStream_t s) {
   // from 8 token rows on (measured) the slices are added by a kernel of its own; ST_SLICES leaves them to the consumer
   const int defer = epi == ST_SLICES || (ksplit > 1 && M >= 8);
@@ -310,7 +320,7 @@ static int launch_stream(const CUtensorMap& mw, const CUtensorMap& mx, void* C, 
     configured = true;
   }
   cudaError_t e = hb_launch(kern, dim3(n_blocks, ksplit), 192, S::TOTAL, s, mw, mx, C, ldc, M, N, K, kslice, ws, counters,
-                            epi, status, defer);
+                            epi, status, defer, W, ldw);
   if (e != cudaSuccess) HB_FAIL("hb_gemm_stream: %s", cudaGetErrorString(e));
   if (defer && epi != ST_SLICES) {
     const int NP = n_blocks * ST_ROWS;
@@ -346,7 +356,7 @@ HB_EXPORT int hb_gemm_stream(const void* A, long lda, const void* W, long ldw, v
   if (hb_make_tensor_map_bf16(&mw, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, ST_ROWS)) return -1;
   if (hb_make_tensor_map_bf16(&mx, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, (uint32_t)NT)) return -1;
   int r;
-#define HB_ST_ARGS mw, mx, C, ldc, M, N, K, kslice, ksplit, n_blocks, ws, counters, epi, status, s
+#define HB_ST_ARGS mw, mx, (const __nv_bfloat16*)W, ldw, C, ldc, M, N, K, kslice, ksplit, n_blocks, ws, counters, epi, status, s
   if (ksplit == 1) {
     if (NT == 16) r = launch_stream<16, true>(HB_ST_ARGS);
     else if (NT == 32) r = launch_stream<32, true>(HB_ST_ARGS);

@@ -26,7 +26,7 @@ _SIGS = {
     "hb_gemm_stream_finish": [_p, _p, _l, _i, _i, _i, _i, _p],
     "hb_add_rmsnorm_slices": [_p, _l, _p, _i, _l, _l, _p, _p, _p, _i, _i, _f, _p],
     "hb_rope_kv_slices": [_p, _i, _l, _l, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p],
-    "hb_attn_decode": [_p, _p, _p, _p, _i, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _i, _p, _i, _p, _p],
+    "hb_attn_decode": [_p, _p, _p, _l, _p, _i, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _i, _p, _i, _p, _p, _p],
     "hb_flash_prefill": [_p, _p, _p, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p],
     "hb_flash_prefill_supported": [_i, _i, _i],
     "hb_flash_prefill_tc": [_p, _p, _p, _l, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p, _p],
@@ -291,12 +291,12 @@ def attention_decode(q, k_cache, v_cache, block_table, row_request, positions, o
     T = q.shape[0]
     ws = ops.attention_workspace(T, n_heads, head_dim, max_pos, chunk, q.device)
     cnt = None if ws is None else _decode_counters(q.device, T * n_kv_heads)
-    _call("hb_attn_decode", q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_table.data_ptr(),
+    _call("hb_attn_decode", q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), k_cache.shape[0], block_table.data_ptr(),
           block_table.stride(0), row_request.data_ptr(), positions.data_ptr(), out.data_ptr(),
           None if ws is None else ws.data_ptr(), None if cnt is None else cnt.data_ptr(), T, n_heads, n_kv_heads,
           head_dim, page_size, int(window), float(scale), chunk, int(max_pos),
           None if q_len is None else q_len.data_ptr(), int(row_limit), None if ctx_len is None else ctx_len.data_ptr(),
-          _stream())
+          status_word().data_ptr(), _stream())
     return out
 
 
