@@ -18,12 +18,18 @@
 enum { EPI_F32 = 0, EPI_BF16 = 1, EPI_ADD_F32 = 2, EPI_SWIGLU_BF16 = 3 };
 
 constexpr int BM = 128, BK = 64;
+#ifndef HB_GEMM_TMA_STORE
+#define HB_GEMM_TMA_STORE 1
+#endif
 
 template <int BN, int STAGES>
 struct GemmSmem {
   static constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
   static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;  // barriers + slack to align the base to 1024
+  // with the epilogue through TMA stores: two 32 x 32 fp32 boxes per epilogue warp, 1 KB aligned, after the barriers
+  static constexpr int STAGING_OFFSET = (BAR_OFFSET + 256 + 1023) / 1024 * 1024;
+  static constexpr int TOTAL_TS = STAGING_OFFSET + 4 * 2 * 4096 + 1024;
 };
 
 template <int EPI>
@@ -75,9 +81,15 @@ __device__ __forceinline__ void epilogue_store(const float* v, void* C, long ldc
   }
 }
 
-template <int BN, int STAGES, int EPI>
+// TS: results leave through shared memory and TMA: a warp writes 32 rows x 128 bytes in
+// the 128-byte swizzle (no bank conflicts) and one lane sends the box as a tensor store, or,
+// for the add into the residual stream, as a tensor REDUCE (the add happens at the memory side:
+// the SM never reads C). Rows are whole 128-byte lines, and the next box is read from tensor
+// memory while the last one is on its way.
+template <int BN, int STAGES, int EPI, bool TS>
 __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
-                                                         const __grid_constant__ CUtensorMap map_w, void* C, long ldc,
+                                                         const __grid_constant__ CUtensorMap map_w,
+                                                         const __grid_constant__ CUtensorMap map_c, void* C, long ldc,
                                                          int M, int N, int K, int* status) {
   using S = GemmSmem<BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
@@ -103,7 +115,11 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
     hb_tmem_alloc(tmem_slot, 2 * BN);
     hb_tmem_relinquish();
   }
-  if (warp == 4 && lane == 0) { hb_tma_prefetch_desc(&map_a); hb_tma_prefetch_desc(&map_w); }
+  if (warp == 4 && lane == 0) {
+    hb_tma_prefetch_desc(&map_a);
+    hb_tma_prefetch_desc(&map_w);
+    if (TS) hb_tma_prefetch_desc(&map_c);
+  }
   hb_tc_fence_before();
   __syncthreads();
   hb_tc_fence_after();
@@ -160,12 +176,59 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
       for (int c = 0; c < BN / 32; c++) {
         float v[32];
         hb_tmem_ld32(t0 + c * 32, v);
-        if (n0 + c * 32 < N) epilogue_store<EPI>(v, C, ldc, row, n0 + c * 32, M, N);
+        if (n0 + c * 32 >= N) continue;
+        if constexpr (TS) {
+          // PER chunks of 32 accumulator columns fill one box of 128-byte rows: 1 (fp32), 2 (bf16), 4 (SwiGLU: 16 outputs each)
+          constexpr int PER = EPI == EPI_SWIGLU_BF16 ? 4 : EPI == EPI_BF16 ? 2 : 1;
+          uint8_t* box = smem + S::STAGING_OFFSET + warp * 8192 + ((c / PER) & 1) * 4096;
+          if (c % PER == 0) {
+            if (lane == 0) hb_tma_store_wait_read<1>();   // the store that last read this box is done with it
+            __syncwarp();
+          }
+          const uint32_t b = hb_smem_u32(box) + lane * 128;
+          if constexpr (EPI == EPI_SWIGLU_BF16) {
+            uint32_t r[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+              const float g0 = v[2 * j], g1 = v[2 * j + 1];
+              r[j] = hb_pack_bf16(g0 / (1.f + __expf(-g0)) * v[16 + 2 * j], g1 / (1.f + __expf(-g1)) * v[17 + 2 * j]);
+            }
+#pragma unroll
+            for (int j = 0; j < 2; j++)
+              asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(b + ((((c % PER) * 2 + j) ^ (lane & 7)) << 4)),
+                           "r"(r[4 * j]), "r"(r[4 * j + 1]), "r"(r[4 * j + 2]), "r"(r[4 * j + 3]) : "memory");
+          } else if constexpr (EPI == EPI_BF16) {
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+              asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(b + ((((c % PER) * 4 + j) ^ (lane & 7)) << 4)),
+                           "r"(hb_pack_bf16(v[8 * j], v[8 * j + 1])), "r"(hb_pack_bf16(v[8 * j + 2], v[8 * j + 3])),
+                           "r"(hb_pack_bf16(v[8 * j + 4], v[8 * j + 5])), "r"(hb_pack_bf16(v[8 * j + 6], v[8 * j + 7])) : "memory");
+          } else {
+#pragma unroll
+            for (int j = 0; j < 8; j++)
+              asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(b + ((j ^ (lane & 7)) << 4)), "f"(v[4 * j]),
+                           "f"(v[4 * j + 1]), "f"(v[4 * j + 2]), "f"(v[4 * j + 3]) : "memory");
+          }
+          if ((c + 1) % PER == 0 || n0 + (c + 1) * 32 >= N) {   // the box is full, or the tensor ends here
+            hb_fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+              // first column of the box in the output: accumulator column / 2 for SwiGLU
+              const int x = EPI == EPI_SWIGLU_BF16 ? (n0 >> 1) + (c / PER) * 64 : n0 + (c / PER) * (PER * 32);
+              if (EPI == EPI_ADD_F32) hb_tma_reduce_add_2d(&map_c, box, x, m0 + warp * 32);
+              else hb_tma_store_2d(&map_c, box, x, m0 + warp * 32);
+              hb_tma_store_commit();
+            }
+          }
+        } else {
+          epilogue_store<EPI>(v, C, ldc, row, n0 + c * 32, M, N);
+        }
       }
       hb_tc_fence_before();
       __syncwarp();
       if (lane == 0) hb_mbar_arrive(&tmem_empty[buf]);
     }
+    if (TS && lane == 0) hb_tma_store_wait_all();   // before the shared memory is given up and the kernel ends
   }
 
   hb_tc_fence_before();
@@ -218,6 +281,21 @@ int hb_make_tensor_map_bf16(CUtensorMap* out, const void* base, uint64_t rows, u
   return 0;
 }
 
+// A 2-D fp32 tensor map [rows, cols] with a box of 32 x 32 (128-byte rows) and the 128-byte swizzle: for stores.
+static int hb_make_tensor_map_f32_box32(CUtensorMap* out, void* base, uint64_t rows, uint64_t cols, uint64_t row_stride_elems) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) HB_FAIL("cuTensorMapEncodeTiled is not available from this driver");
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {row_stride_elems * 4};
+  const cuuint32_t box[2] = {32, 32};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) HB_FAIL("cuTensorMapEncodeTiled (fp32 output) failed with code %d (rows %llu, cols %llu)", (int)r,
+                                 (unsigned long long)rows, (unsigned long long)cols);
+  return 0;
+}
+
 static int sm_count() {
   static int n = 0;
   if (!n) {
@@ -228,21 +306,43 @@ static int sm_count() {
   return n;
 }
 
-template <int BN, int STAGES, int EPI>
-static int launch_gemm_tc(const CUtensorMap& ma, const CUtensorMap& mw, void* C, long ldc, int M, int N, int K,
-                          int* status, cudaStream_t s) {
+template <int BN, int STAGES, int EPI, bool TS>
+static int launch_gemm_tc_ts(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap& mc, void* C, long ldc, int M,
+                             int N, int K, int* status, cudaStream_t s) {
   using S = GemmSmem<BN, STAGES>;
-  auto kern = gemm_tc_kernel<BN, STAGES, EPI>;
+  constexpr int smem = TS ? S::TOTAL_TS : S::TOTAL;
+  auto kern = gemm_tc_kernel<BN, STAGES, EPI, TS>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) HB_FAIL("hb_gemm_tc: %s", cudaGetErrorString(e));
     configured = true;
   }
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  kern<<<grid, 192, S::TOTAL, s>>>(ma, mw, C, ldc, M, N, K, status);
+  kern<<<grid, 192, smem, s>>>(ma, mw, mc, C, ldc, M, N, K, status);
   return 0;
+}
+
+// fp32 results go out through TMA stores where C allows it (16-byte aligned base and rows)
+template <int BN, int STAGES, int EPI>
+static int launch_gemm_tc(const CUtensorMap& ma, const CUtensorMap& mw, void* C, long ldc, int M, int N, int K,
+                          int* status, cudaStream_t s) {
+  CUtensorMap mc;
+  memset(&mc, 0, sizeof(mc));
+  if constexpr (EPI == EPI_F32 || EPI == EPI_ADD_F32) {
+    if (HB_GEMM_TMA_STORE && !((uintptr_t)C & 15) && (ldc & 3) == 0) {
+      if (hb_make_tensor_map_f32_box32(&mc, C, (uint64_t)M, (uint64_t)N, (uint64_t)ldc)) return -1;
+      return launch_gemm_tc_ts<BN, STAGES, EPI, true>(ma, mw, mc, C, ldc, M, N, K, status, s);
+    }
+  } else {
+    if (HB_GEMM_TMA_STORE && !((uintptr_t)C & 15) && (ldc & 7) == 0) {   // bf16 [M, N] or [M, N / 2]: boxes of 32 rows x 64 columns
+      const uint64_t cols = EPI == EPI_SWIGLU_BF16 ? (uint64_t)N / 2 : (uint64_t)N;
+      if (hb_make_tensor_map_bf16(&mc, C, (uint64_t)M, cols, (uint64_t)ldc, 32)) return -1;
+      return launch_gemm_tc_ts<BN, STAGES, EPI, true>(ma, mw, mc, C, ldc, M, N, K, status, s);
+    }
+  }
+  return launch_gemm_tc_ts<BN, STAGES, EPI, false>(ma, mw, mc, C, ldc, M, N, K, status, s);
 }
 
 template <int BN, int STAGES>

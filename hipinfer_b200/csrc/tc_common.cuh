@@ -58,6 +58,23 @@ __device__ __forceinline__ void hb_tma_load_2d(void* dst, const CUtensorMap* m, 
       ::"r"(hb_smem_u32(dst)), "l"((uint64_t)m), "r"(hb_smem_u32(bar)), "r"(c0), "r"(c1)
       : "memory");
 }
+// A box of shared memory (laid out as the map's swizzle says) written to the tensor, or added into
+// it (the add is made at the memory side; fp32 maps). The part of the box beyond the tensor's
+// extent is not written. Asynchronous: commit, then wait before the shared memory is reused.
+__device__ __forceinline__ void hb_tma_store_2d(const CUtensorMap* m, const void* src, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"((uint64_t)m), "r"(hb_smem_u32(src)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void hb_tma_reduce_add_2d(const CUtensorMap* m, const void* src, int c0, int c1) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"((uint64_t)m), "r"(hb_smem_u32(src)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void hb_tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Until at most N of this thread's groups still READ their shared memory / until all have completed.
+template <int N> __device__ __forceinline__ void hb_tma_store_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void hb_tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 // The same tile brought into L2 only (nothing arrives in shared memory, nothing to wait for).
 __device__ __forceinline__ void hb_tma_prefetch_l2_2d(const CUtensorMap* m, int c0, int c1) {
   asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"((uint64_t)m), "r"(c0), "r"(c1)
