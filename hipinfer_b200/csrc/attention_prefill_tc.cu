@@ -75,8 +75,14 @@ __global__ void __launch_bounds__(192, 1) flash_prefill_tc_kernel(
 
   // the last query tiles of a portion have the most keys to walk: they are started first
   const int req = blockIdx.z, hq = blockIdx.y, qt = gridDim.x - 1 - blockIdx.x;
+  // the step's own metadata (lengths, tables) was copied before the step's first kernel began; everything else
+  // that an earlier kernel wrote is read after hb_pdl_wait() below
+  hb_pdl_launch();
   const int n_rows = q_len[req];
-  if (n_rows < min_rows || qt * FT_BM >= n_rows) return;
+  if (n_rows < min_rows || qt * FT_BM >= n_rows) {
+    if ((blockIdx.x | blockIdx.y | blockIdx.z) == 0) hb_pdl_wait();   // the grid never ends before the one ahead of it
+    return;
+  }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int h = hq / (Hq / Hkv);
   const int row0 = q_start[req] + qt * FT_BM, rows_here = min(FT_BM, n_rows - qt * FT_BM);
@@ -110,6 +116,7 @@ __global__ void __launch_bounds__(192, 1) flash_prefill_tc_kernel(
   __syncthreads();
   hb_tc_fence_after();
   const uint32_t tmem_s = bar->tmem_slot, tmem_o = tmem_s + 2 * FT_BN;  // S: 2 x 128 columns, O: 2 x 64
+  hb_pdl_wait();   // barriers, shared and tensor memory were set up while the kernel ahead was still running
 
   if (warp == 4) {  // ---------------- TMA: lane l brings page l of the tile (the page ids come in one load)
     if (lane == 0) {
@@ -311,8 +318,9 @@ HB_EXPORT int hb_flash_prefill_tc(const void* q, const void* kc, const void* vc,
     configured = true;
   }
   dim3 grid((max_q_len + FT_BM - 1) / FT_BM, Hq, R);
-  flash_prefill_tc_kernel<<<grid, 192, smem, st>>>(mq, mk, mv, bt, bt_stride, q_start, q_len, ctx_len, (__nv_bfloat16*)out, Hq,
-                                                   Hkv, page_size, window, scale * 1.4426950408889634f, min_rows, status);
+  cudaError_t e = hb_launch(flash_prefill_tc_kernel, grid, 192, smem, st, mq, mk, mv, bt, bt_stride, q_start, q_len, ctx_len,
+                            (__nv_bfloat16*)out, Hq, Hkv, page_size, window, scale * 1.4426950408889634f, min_rows, status);
+  if (e != cudaSuccess) HB_FAIL("hb_flash_prefill_tc: %s", cudaGetErrorString(e));
   HB_CHECK_LAUNCH("hb_flash_prefill_tc");
   return 0;
 }

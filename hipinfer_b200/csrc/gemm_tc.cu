@@ -101,6 +101,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
   uint32_t* tmem_slot = (uint32_t*)(tmem_empty + 2);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
+  hb_pdl_launch();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN, num_tiles = m_tiles * n_tiles;
   const int num_kb = (K + BK - 1) / BK;
@@ -124,6 +125,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
   __syncthreads();
   hb_tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  hb_pdl_wait();   // barriers and tensor memory were set up while the kernel ahead was still running
 
   if (warp == 4) {
     if (lane == 0) {  // ---------------- TMA producer
@@ -320,7 +322,8 @@ static int launch_gemm_tc_ts(const CUtensorMap& ma, const CUtensorMap& mw, const
   }
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  kern<<<grid, 192, smem, s>>>(ma, mw, mc, C, ldc, M, N, K, status);
+  cudaError_t e = hb_launch(kern, grid, 192, smem, s, ma, mw, mc, C, ldc, M, N, K, status);
+  if (e != cudaSuccess) HB_FAIL("hb_gemm_tc: %s", cudaGetErrorString(e));
   return 0;
 }
 
