@@ -214,10 +214,14 @@ def prefill_flops(layers: int) -> float:
 
 
 def breakdown(layers: int, batch: int) -> int:
-    """Per-kernel device time of decode steps at `batch` (a table on stdout, not the JSON line):
-    ten graph-replayed steps under torch's CUPTI profiler, launches made ordinary
-    (HIPINFER_B200_PDL=0 is set here) so that kernels do not overlap and their times add up."""
-    os.environ["HIPINFER_B200_PDL"] = "0"
+    """The time line of one graph-replayed decode step at `batch` from torch's CUPTI profiler (a
+    table on stdout, not the JSON line). Kernels overlap (programmatic dependent launch: they start
+    early and wait), so besides start and duration the table gives, for the kernels of one layer in
+    the middle of the step, the time from the end of the kernel before to the kernel's own end: its
+    share of the chain. Below it the kernels by name with their summed durations."""
+    import json as _json
+    import tempfile
+
     import torch
     from torch.profiler import ProfilerActivity, profile
 
@@ -238,16 +242,39 @@ def breakdown(layers: int, batch: int) -> int:
     for _ in range(5):
         one()
     torch.cuda.synchronize()
-    n = 10
+    n = 4
     with profile(activities=[ProfilerActivity.CUDA]) as prof:
         for _ in range(n):
             one()
         torch.cuda.synchronize()
-    rows = [(e.key, e.device_time_total / n, e.count / n) for e in prof.key_averages() if e.device_time_total > 0]
-    total = sum(r[1] for r in rows)
-    print(f"decode step at batch {batch}, context {PROMPT_LEN}+: {total:.1f} us of kernel time per step (launches do not overlap)")
-    for name, us, cnt in sorted(rows, key=lambda r: -r[1]):
-        print(f"{us:9.1f} us  {100 * us / total:5.1f} %  {cnt:6.1f} launches  {us / cnt:7.2f} us each  {name[:70]}")
+    with tempfile.TemporaryDirectory() as tmp:
+        path = os.path.join(tmp, "trace.json")
+        prof.export_chrome_trace(path)
+        with open(path) as f:
+            events = [e for e in _json.load(f)["traceEvents"] if e.get("cat") == "kernel"]
+    events.sort(key=lambda e: e["ts"])
+    per = len(events) // n
+    step = events[2 * per: 3 * per]                      # the third of the four steps
+    t0 = step[0]["ts"]
+    span = step[-1]["ts"] + step[-1]["dur"] - t0
+    print(f"decode step at batch {batch}, context {PROMPT_LEN}+: {per} kernels, {span:.1f} us from the first kernel's start "
+          f"to the last one's end")
+    per_layer = max(1, (per - 5) // max(1, layers))      # besides the layers: embedding, last norm, head, two of sampling
+    lo = min(len(step) - 1, 1 + per_layer * (layers // 2))
+    print(f"kernels {lo}..{lo + per_layer - 1} (one layer): start, duration, end minus the end of the kernel before")
+    prev_end = max(e["ts"] + e["dur"] for e in step[:lo]) if lo else t0
+    for e in step[lo: lo + per_layer]:
+        end = e["ts"] + e["dur"]
+        print(f"{e['ts'] - t0:9.2f} us  dur {e['dur']:7.2f}  chain {end - prev_end:6.2f}  {e['name'][:56]:56s} grid {e['args'].get('grid')}")
+        prev_end = max(prev_end, end)
+    agg = {}
+    for e in step:
+        a = agg.setdefault(e["name"][:70], [0, 0.0])
+        a[0] += 1
+        a[1] += e["dur"]
+    print("by kernel (durations overlap and do not add up to the step):")
+    for name, (cnt, us) in sorted(agg.items(), key=lambda kv: -kv[1][1]):
+        print(f"{us:9.1f} us  {cnt:4d} launches  {us / cnt:7.2f} us each  {name}")
     eng.close()
     return 0
 
