@@ -12,9 +12,13 @@
 //                        exponentiates in the exp2 domain in fp32, writes P as bf16 into shared
 //                        memory in the swizzled K-major layout the tensor core reads, and keeps
 //                        the output row in registers: o = o * 2^(m_old - m_new) + O_tile.
-// S and the output tile are double-buffered in tensor memory and K, V in shared memory: the
-// scores of tile i + 1 are computed while the softmax of tile i runs, and the output tile of
-// tile i is added one tile late, so a softmax thread never waits for the tensor core. Because tiles are cut at absolute
+// The output tile is double-buffered in tensor memory and K, V in shared memory; the output tile
+// of tile i is added one tile late, so a softmax thread rarely waits for the tensor core. A CTA
+// takes 256 columns of tensor memory (S 128, O 2 x 64), 113 KB of shared memory and at most 168
+// registers a thread (a row of S is read in two halves of 64, the first one twice: once for the
+// maximum, once for the exponentials), so that TWO CTAs share an SM: while the softmax of one
+// keeps the special-function unit busy, the other stores P, adds its output tile or waits for the
+// tensor core. Because tiles are cut at absolute
 // positions and a row's running max and sum are its own, a row's result does not depend on how
 // the prompt was cut or on what else is in the batch. Replaces flash_prefill_mma_kernel of the
 // reference (src/kernels.cuh:1335-1482). Every wait is bounded.
@@ -50,7 +54,7 @@ HB_EXPORT int hb_ft_stamps(unsigned long long* out) {
 #endif
 
 struct FtBars {
-  uint64_t q_full, k_full[2], k_free[2], v_full[2], v_free[2], s_full[2], s_free[2], o_full[2], o_free[2], p_full, p_free;
+  uint64_t q_full, k_full[2], k_free[2], v_full[2], v_free[2], s_full, s_free, o_full[2], o_free[2], p_full, p_free;
   uint32_t tmem_slot;
   int abort_flag;
 };
@@ -59,13 +63,14 @@ struct FtBars {
 #define FT_B(i) ((i) & 1)
 #define FT_PH(i) (((i) >> 1) & 1)
 
-__global__ void __launch_bounds__(192, 1) flash_prefill_tc_kernel(
+__global__ void __launch_bounds__(192, 2) flash_prefill_tc_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, const int* __restrict__ bt, int bt_stride, const int* __restrict__ q_start,
     const int* __restrict__ q_len, const int* __restrict__ ctx_len, __nv_bfloat16* __restrict__ out, int Hq, int Hkv,
     int page_size, int window, float scale_log2, int min_rows, int* status) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  // the 128-byte swizzle wants the tiles on 1 KB boundaries; with no room for slack (two CTAs an SM) the
+  // dynamic shared memory itself has to start on one, which is checked below
+  extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* sQ = smem;                  // [128][64]
   uint8_t* sK = sQ + FT_TILE;          // two stages of [128 keys][64]
   uint8_t* sV = sK + 2 * FT_TILE;      // two stages of [128 keys][64]
@@ -83,6 +88,10 @@ __global__ void __launch_bounds__(192, 1) flash_prefill_tc_kernel(
     if ((blockIdx.x | blockIdx.y | blockIdx.z) == 0) hb_pdl_wait();   // the grid never ends before the one ahead of it
     return;
   }
+  if (hb_smem_u32(smem) & 1023) {   // never seen; the tiles would not be where the tensor core expects them
+    if (threadIdx.x == 0) atomicExch(status, 1);
+    return;
+  }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int h = hq / (Hq / Hkv);
   const int row0 = q_start[req] + qt * FT_BM, rows_here = min(FT_BM, n_rows - qt * FT_BM);
@@ -96,10 +105,10 @@ __global__ void __launch_bounds__(192, 1) flash_prefill_tc_kernel(
     for (int b = 0; b < 2; b++) {
       hb_mbar_init(&bar->k_full[b], 1); hb_mbar_init(&bar->k_free[b], 1);
       hb_mbar_init(&bar->v_full[b], 1); hb_mbar_init(&bar->v_free[b], 1);
-      hb_mbar_init(&bar->s_full[b], 1); hb_mbar_init(&bar->s_free[b], 128);
       hb_mbar_init(&bar->o_full[b], 1); hb_mbar_init(&bar->o_free[b], 128);
     }
     hb_mbar_init(&bar->p_full, 128); hb_mbar_init(&bar->p_free, 1);
+    hb_mbar_init(&bar->s_full, 1); hb_mbar_init(&bar->s_free, 128);
     bar->abort_flag = 0;
     hb_fence_barrier_init();
   }
@@ -107,7 +116,7 @@ __global__ void __launch_bounds__(192, 1) flash_prefill_tc_kernel(
   // must be finite (P is exactly 0 there, and 0 * NaN would poison the row)
   for (int i = threadIdx.x; i < 4 * FT_TILE / 16; i += 192) ((uint4*)sK)[i] = make_uint4(0, 0, 0, 0);
   if (warp == 5) {
-    hb_tmem_alloc(&bar->tmem_slot, 512);
+    hb_tmem_alloc(&bar->tmem_slot, 256);
     hb_tmem_relinquish();
   }
   if (warp == 4 && lane == 0) { hb_tma_prefetch_desc(&map_q); hb_tma_prefetch_desc(&map_k); hb_tma_prefetch_desc(&map_v); }
@@ -115,7 +124,7 @@ __global__ void __launch_bounds__(192, 1) flash_prefill_tc_kernel(
   hb_tc_fence_before();
   __syncthreads();
   hb_tc_fence_after();
-  const uint32_t tmem_s = bar->tmem_slot, tmem_o = tmem_s + 2 * FT_BN;  // S: 2 x 128 columns, O: 2 x 64
+  const uint32_t tmem_s = bar->tmem_slot, tmem_o = tmem_s + FT_BN;  // S: 128 columns, O: 2 x 64
   hb_pdl_wait();   // barriers, shared and tensor memory were set up while the kernel ahead was still running
 
   if (warp == 4) {  // ---------------- TMA: lane l brings page l of the tile (the page ids come in one load)
@@ -152,12 +161,12 @@ __global__ void __launch_bounds__(192, 1) flash_prefill_tc_kernel(
       for (int i = 0; i <= n_tiles && ok; i++) {
         if (i < n_tiles) {
           const int b = FT_B(i);
-          if (!hb_mbar_wait(&bar->k_full[b], FT_PH(i), abort_flag) || !hb_mbar_wait(&bar->s_free[b], FT_PH(i) ^ 1, abort_flag)) break;
+          if (!hb_mbar_wait(&bar->k_full[b], FT_PH(i), abort_flag) || !hb_mbar_wait(&bar->s_free, (i & 1) ^ 1, abort_flag)) break;
           hb_tc_fence_after();
           const uint64_t dq = hb_umma_desc_k128(hb_smem_u32(sQ)), dk = hb_umma_desc_k128(hb_smem_u32(sK + b * FT_TILE));
 #pragma unroll
-          for (int k = 0; k < FT_D / 16; k++) hb_umma_bf16(tmem_s + b * FT_BN, dq + 2 * k, dk + 2 * k, idesc_s, k != 0);
-          hb_umma_commit(&bar->s_full[b]);
+          for (int k = 0; k < FT_D / 16; k++) hb_umma_bf16(tmem_s, dq + 2 * k, dk + 2 * k, idesc_s, k != 0);
+          hb_umma_commit(&bar->s_full);
           hb_umma_commit(&bar->k_free[b]);
         }
         if (i > 0) {
@@ -190,60 +199,78 @@ __global__ void __launch_bounds__(192, 1) flash_prefill_tc_kernel(
     for (int i = 0; i <= n_tiles && ok; i++) {
       float corr = 1.f;
       if (i < n_tiles) {
-        const int b = FT_B(i), k_base = (kt_lo + i) * FT_BN;
+        const int k_base = (kt_lo + i) * FT_BN;
         const bool need_mask = k_base + FT_BN - 1 > p_first || (window > 0 && k_base < p_last - window + 1);
         if (threadIdx.x == 0) FT_STAMP(1 + 6 * i);
-        if (!hb_mbar_wait(&bar->s_full[b], FT_PH(i), abort_flag)) break;
+        if (!hb_mbar_wait(&bar->s_full, i & 1, abort_flag)) break;
         if (threadIdx.x == 0) FT_STAMP(2 + 6 * i);
         hb_tc_fence_after();
-        uint32_t sr[128];  // the whole row of S: both halves requested, one wait
-        hb_tmem_ld64_nowait(tmem_s + b * FT_BN + lane_base, sr);
-        hb_tmem_ld64_nowait(tmem_s + b * FT_BN + lane_base + 64, sr + 64);
-        hb_tmem_ld_wait();
-        hb_tmem_ld_fence64(sr);
-        hb_tmem_ld_fence64(sr + 64);
-        hb_tc_fence_before();
-        hb_mbar_arrive(&bar->s_free[b]);  // S is in registers: the scores of tile i + 2 may overwrite it
-        if (threadIdx.x == 0) FT_STAMP(3 + 6 * i);
-        // a softmax warp is alone on its scheduler: four independent chains for the maximum and
-        // for the sum instead of one, and the mask only on the tiles that need one
+        // the row of S in two halves of 64 keys; a softmax warp is alone on its scheduler: four
+        // independent chains for the maximum and for the sum, and the mask only where one is needed
+        uint32_t sr[64];
+        const int hi_j = qp - k_base, lo_j = window > 0 ? qp - window - k_base : -1;  // key j of the tile is visible iff lo_j < j <= hi_j
         float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-        if (need_mask) {
-          const int hi_j = qp - k_base, lo_j = window > 0 ? qp - window - k_base : -1;  // visible iff lo_j < j <= hi_j
 #pragma unroll
-          for (int j = 0; j < 128; j++) {
-            const float v = (j <= hi_j && j > lo_j) ? __uint_as_float(sr[j]) : -INFINITY;
-            sr[j] = __float_as_uint(v);
-            mx4[j & 3] = fmaxf(mx4[j & 3], v);
+        for (int hh = 0; hh < 2; hh++) {
+          hb_tmem_ld64_nowait(tmem_s + lane_base + hh * 64, sr);
+          hb_tmem_ld_wait();
+          hb_tmem_ld_fence64(sr);
+          if (need_mask) {
+#pragma unroll
+            for (int j = 0; j < 64; j++) {
+              const float v = (j + hh * 64 <= hi_j && j + hh * 64 > lo_j) ? __uint_as_float(sr[j]) : -INFINITY;
+              sr[j] = __float_as_uint(v);
+              mx4[j & 3] = fmaxf(mx4[j & 3], v);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 64; j++) mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(sr[j]));
           }
-        } else {
-#pragma unroll
-          for (int j = 0; j < 128; j++) mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(sr[j]));
         }
+        if (threadIdx.x == 0) FT_STAMP(3 + 6 * i);
         const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
         const float m_new = fmaxf(m_run, mx * scale_log2);
         const float sub = m_new == -INFINITY ? 0.f : m_new;
         corr = hb_exp2(m_run - sub);
         m_run = m_new;
         float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+        // the exponentials: keys 64-127 are still in the registers (masked), keys 0-63 are read again
 #pragma unroll
-        for (int j = 0; j < 128; j += 2) {  // masked scores are -inf: 2^-inf = 0
-          const float p0 = hb_exp2(fmaf(__uint_as_float(sr[j]), scale_log2, -sub));
-          const float p1 = hb_exp2(fmaf(__uint_as_float(sr[j + 1]), scale_log2, -sub));
-          sum4[(j >> 1) & 3] += p0 + p1;
-          sr[j >> 1] = hb_pack_bf16(p0, p1);
+        for (int hh = 1; hh >= 0; hh--) {
+          if (hh == 0) {
+            hb_tmem_ld64_nowait(tmem_s + lane_base, sr);
+            hb_tmem_ld_wait();
+            hb_tmem_ld_fence64(sr);
+            hb_tc_fence_before();
+            hb_mbar_arrive(&bar->s_free);  // the last read of S: the scores of the next tile may overwrite it
+            if (need_mask) {
+#pragma unroll
+              for (int j = 0; j < 64; j++)
+                if (!(j <= hi_j && j > lo_j)) sr[j] = __float_as_uint(-INFINITY);
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 64; j += 2) {  // masked scores are -inf: 2^-inf = 0
+            const float p0 = hb_exp2(fmaf(__uint_as_float(sr[j]), scale_log2, -sub));
+            const float p1 = hb_exp2(fmaf(__uint_as_float(sr[j + 1]), scale_log2, -sub));
+            sum4[(j >> 1) & 3] += p0 + p1;
+            sr[j >> 1] = hb_pack_bf16(p0, p1);
+          }
+          if (hh == 1) {
+            if (threadIdx.x == 0) FT_STAMP(4 + 6 * i);
+            if (!hb_mbar_wait(&bar->p_free, (i & 1) ^ 1, abort_flag)) { ok = false; break; }
+          }
+          // 64 keys = eight 16-byte chunks of this row in K block hh of P
+#pragma unroll
+          for (int cc = 0; cc < 8; cc++) {
+            const uint32_t dst = hb_smem_u32(sP + hh * FT_TILE) + r * 128 + ((cc ^ (r & 7)) << 4);
+            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(sr[4 * cc]), "r"(sr[4 * cc + 1]),
+                         "r"(sr[4 * cc + 2]), "r"(sr[4 * cc + 3]) : "memory");
+          }
         }
+        if (!ok) break;
         const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
         l_run = l_run * corr + sum;
-        if (threadIdx.x == 0) FT_STAMP(4 + 6 * i);
-        if (!hb_mbar_wait(&bar->p_free, (i & 1) ^ 1, abort_flag)) break;
-        // 128 keys = sixteen 16-byte chunks of this row: eight in each K block of P
-#pragma unroll
-        for (int cc = 0; cc < 16; cc++) {
-          const uint32_t dst = hb_smem_u32(sP + (cc >> 3) * FT_TILE) + r * 128 + (((cc & 7) ^ (r & 7)) << 4);
-          asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(sr[4 * cc]), "r"(sr[4 * cc + 1]),
-                       "r"(sr[4 * cc + 2]), "r"(sr[4 * cc + 3]) : "memory");
-        }
         hb_fence_proxy_async();
         hb_mbar_arrive(&bar->p_full);
         if (threadIdx.x == 0) FT_STAMP(5 + 6 * i);
@@ -285,7 +312,7 @@ __global__ void __launch_bounds__(192, 1) flash_prefill_tc_kernel(
   }
   if (warp == 5) {
     __syncwarp();
-    hb_tmem_dealloc(tmem_s, 512);
+    hb_tmem_dealloc(tmem_s, 256);
   }
 }
 
@@ -310,7 +337,7 @@ HB_EXPORT int hb_flash_prefill_tc(const void* q, const void* kc, const void* vc,
   const uint64_t rows = (uint64_t)num_pages * Hkv * page_size;
   if (hb_make_tensor_map_bf16(&mk, kc, rows, (uint64_t)D, (uint64_t)D, (uint32_t)page_size)) return -1;
   if (hb_make_tensor_map_bf16(&mv, vc, rows, (uint64_t)D, (uint64_t)D, (uint32_t)page_size)) return -1;
-  const size_t smem = 7 * (size_t)FT_TILE + sizeof(FtBars) + 1024;
+  const size_t smem = 7 * (size_t)FT_TILE + sizeof(FtBars);   // 113 KB: two CTAs an SM
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(flash_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
