@@ -8,6 +8,8 @@
 // of the core library.
 #include "tc_common.cuh"
 
+HB_TL_DEFINE(attn)
+
 #ifndef HB_AD_LATE_TRIGGER
 #define HB_AD_LATE_TRIGGER 0   // 1: dependents start only when every block has its keys; measured 1 to 3 % slower at batch 1 and 8
 #endif
@@ -124,6 +126,7 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
   hb_pdl_launch();
 #endif
   AD_STAMP(0);
+  HB_TL_MARK(0, 0);
   AD_STAMP(5);
 #if HB_AD_HEAD_FIRST
   const int t = blockIdx.z, h = blockIdx.x, s = blockIdx.y;   // blocks next to each other read pieces of the same pages
@@ -174,6 +177,7 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
     AD_STAMP(1);
     hb_pdl_wait();
     AD_STAMP(2);
+    HB_TL_MARK(0, 1);
     if (pages_w > 0 && lane == 0) {   // the pages that hold this step's keys
       hb_mbar_expect_tx(&bars[warp], (uint32_t)((pages_w - old_w) * page_bytes));
       for (int j = old_w; j < pages_w; j++) {
@@ -219,6 +223,7 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
   hb_pdl_launch();
 #endif
   AD_STAMP(3);
+  HB_TL_MARK(0, 2);
 
   float m_run = -INFINITY, l_run = 0.f;  // of row g (a head when g < G), over this warp's keys
   float o[NT_O][4];
@@ -323,6 +328,7 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
     }
   }
   AD_STAMP(4);
+  HB_TL_MARK(1, 3);   // slot 1: the end of the chunk work; slot 0: the end of the merge
   if (whole) return;
   // the block of this (row, kv head) that ends last adds the chunks, lowest first
   __threadfence();
@@ -335,31 +341,51 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
   }
   __syncthreads();
   if (!is_last) return;
-  __threadfence();
+  // the others' partials were made visible (their fence) before their count; they are read from L2 below
   const int nc = s_hi - s_lo + 1;
-  for (int i = tid; i < G * D; i += AD_THREADS) {
-    const int gg = i / D, d = i - gg * D;
-    const size_t head = (size_t)t * Hq + (size_t)h * G + gg;
-    const float2* ml = (const float2*)part_ml + head * S + s_lo;
-    const float* pa = part_acc + (head * S + s_lo) * D + d;
-    float m = -INFINITY, a = 0.f, l = 0.f;
-    if (nc <= 16) {   // every load asked for before the first is used: one round trip to L2
-      float2 v[16];
-      float acc[16];
+  constexpr int PER = 2;   // (head, column) pairs of a thread whose loads are in flight together
+  if (nc <= 16) {   // every load of a group of pairs asked for before the first is used: one round trip to L2 a group
+   for (int i0 = tid; i0 < G * D; i0 += PER * AD_THREADS) {
+    float2 v[PER][16];
+    float acc[PER][16];
 #pragma unroll
-      for (int c = 0; c < 16; c++)
-        if (c < nc) { v[c] = __ldcg(ml + c); acc[c] = __ldcg(pa + (size_t)c * D); }
+    for (int k = 0; k < PER; k++) {
+      const int i = i0 + k * AD_THREADS, gg = i / D, d = i - gg * D;
+      if (i < G * D) {
+        const size_t head = (size_t)t * Hq + (size_t)h * G + gg;
+        const float2* ml = (const float2*)part_ml + head * S + s_lo;
+        const float* pa = part_acc + (head * S + s_lo) * D + d;
 #pragma unroll
-      for (int c = 0; c < 16; c++)
-        if (c < nc) m = fmaxf(m, v[c].x);
+        for (int c = 0; c < 16; c++)
+          if (c < nc) { v[k][c] = __ldcg(ml + c); acc[k][c] = __ldcg(pa + (size_t)c * D); }
+      }
+    }
 #pragma unroll
-      for (int c = 0; c < 16; c++)
-        if (c < nc) {
-          const float f = expf(v[c].x - m);
-          l += v[c].y * f;
-          a += acc[c] * f;
-        }
-    } else {
+    for (int k = 0; k < PER; k++) {
+      const int i = i0 + k * AD_THREADS, gg = i / D, d = i - gg * D;
+      if (i < G * D) {
+        float m = -INFINITY, a = 0.f, l = 0.f;
+#pragma unroll
+        for (int c = 0; c < 16; c++)
+          if (c < nc) m = fmaxf(m, v[k][c].x);
+#pragma unroll
+        for (int c = 0; c < 16; c++)
+          if (c < nc) {
+            const float f = expf(v[k][c].x - m);
+            l += v[k][c].y * f;
+            a += acc[k][c] * f;
+          }
+        out[((size_t)t * Hq + (size_t)h * G + gg) * D + d] = __float2bfloat16_rn(a / l);
+      }
+    }
+   }
+  } else {
+    for (int i = tid; i < G * D; i += AD_THREADS) {
+      const int gg = i / D, d = i - gg * D;
+      const size_t head = (size_t)t * Hq + (size_t)h * G + gg;
+      const float2* ml = (const float2*)part_ml + head * S + s_lo;
+      const float* pa = part_acc + (head * S + s_lo) * D + d;
+      float m = -INFINITY, a = 0.f, l = 0.f;
       for (int c = 0; c < nc; c++) m = fmaxf(m, __ldcg(ml + c).x);
       for (int c = 0; c < nc; c++) {
         const float2 v = __ldcg(ml + c);
@@ -367,9 +393,10 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
         l += v.y * f;
         a += __ldcg(pa + (size_t)c * D) * f;
       }
+      out[head * D + d] = __float2bfloat16_rn(a / l);
     }
-    out[head * D + d] = __float2bfloat16_rn(a / l);
   }
+  HB_TL_MARK(0, 3);
 }
 
 template <int D, bool TMA>

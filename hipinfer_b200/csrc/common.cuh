@@ -91,6 +91,32 @@ __device__ __forceinline__ void hb_store4(__nv_bfloat16* p, float4 v) {
   } while (0)
 
 // ---------------------------------------------------------------------------------------
+// A timing build (-DHB_TL): kernels leave globaltimer stamps of their last launch, per translation
+// unit, in slot `id`: phase 0 entry, 1 the dependency wait over, 2 inputs loaded (block 0), 3 the
+// end of the block that ended last. Compiled out otherwise.
+// ---------------------------------------------------------------------------------------
+#ifdef HB_TL
+#define HB_TL_DEFINE(tu)                                                                                  \
+  static __device__ unsigned long long hb_tl_buf[32 * 4];                                                 \
+  HB_EXPORT int hb_tl_dump_##tu(unsigned long long* out) {                                                \
+    return cudaMemcpyFromSymbol(out, hb_tl_buf, sizeof(hb_tl_buf)) == cudaSuccess ? 0 : -1;               \
+  }
+#define HB_TL_MARK(id, ph) hb_tl_mark(hb_tl_buf, id, ph, 0)
+#define HB_TL_MARK_T(id, ph, thread) hb_tl_mark(hb_tl_buf, id, ph, thread)
+__device__ __forceinline__ void hb_tl_mark(unsigned long long* buf, int id, int ph, int thread) {
+  if (threadIdx.x != thread) return;
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  if (ph == 3) atomicMax(&buf[id * 4 + 3], t);
+  else if ((blockIdx.x | blockIdx.y | blockIdx.z) == 0) buf[id * 4 + ph] = t;
+}
+#else
+#define HB_TL_DEFINE(tu)
+#define HB_TL_MARK(id, ph)
+#define HB_TL_MARK_T(id, ph, thread)
+#endif
+
+// ---------------------------------------------------------------------------------------
 // Programmatic dependent launch: a kernel launched with hb_launch() may start while the kernel
 // before it in the stream is still running. It calls hb_pdl_launch() at once (so that ITS
 // successor can be staged as early) and hb_pdl_wait() before its first access to anything an

@@ -18,6 +18,8 @@
 // All waits are bounded.
 #include "tc_common.cuh"
 
+HB_TL_DEFINE(stream)
+
 enum { ST_F32 = 0, ST_BF16 = 1, ST_ADD_F32 = 2, ST_SWIGLU_BF16 = 3, ST_SLICES = 4 };
 constexpr int ST_ROWS = 128, ST_BK = 64, ST_W_BYTES = ST_ROWS * ST_BK * 2;
 #ifndef HB_STREAM_L2_AHEAD
@@ -81,6 +83,9 @@ __global__ void __launch_bounds__(192) gemm_stream_kernel(const __grid_constant_
 
   hb_pdl_launch();
   if (threadIdx.x == 0) HB_STAMP(0);
+  // timing slots: 0 q/k/v, 1 o, 2 gate/up, 3 down, 4 anything else (by the grid)
+  const int tl = gridDim.y == 8 ? (gridDim.x == 24 ? 0 : 1) : gridDim.y == 3 ? 2 : gridDim.y == 16 ? 3 : 4;
+  HB_TL_MARK(tl, 0);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nb = blockIdx.x, sp = blockIdx.y, ksplit = gridDim.y, NP = gridDim.x * ST_ROWS;
   const int n0 = nb * ST_ROWS, k_begin = sp * kslice, k_end = min(K, k_begin + kslice);
@@ -114,6 +119,7 @@ __global__ void __launch_bounds__(192) gemm_stream_kernel(const __grid_constant_
       }
       hb_pdl_wait();
       HB_STAMP(2);
+      HB_TL_MARK_T(tl, 1, 128);
       for (int kb = 0; kb < pre; kb++)
         hb_tma_load_2d(smem + kb * S::STAGE + ST_W_BYTES, &map_x, &full[kb], k_begin + kb * ST_BK, 0);
       for (int kb = pre; kb < num_kb; kb++) {
@@ -160,6 +166,7 @@ __global__ void __launch_bounds__(192) gemm_stream_kernel(const __grid_constant_
     if (threadIdx.x == 0) HB_STAMP(5);
     hb_tc_fence_after();
     hb_pdl_wait();  // before the first access to memory that earlier kernels wrote or still read
+    HB_TL_MARK(tl, 2);   // (thread 0 is an epilogue thread: the product is done)
     float v[NT];
 #pragma unroll
     for (int c = 0; c < NT / 16; c++) hb_tmem_ld16(tmem_base + ((uint32_t)(warp * 32) << 16) + c * 16, v + 16 * c);
@@ -181,7 +188,8 @@ __global__ void __launch_bounds__(192) gemm_stream_kernel(const __grid_constant_
   }
 
   if (threadIdx.x == 0) HB_STAMP(6);
-  __threadfence();
+  HB_TL_MARK(tl, 3);
+  if (ksplit > 1 && !defer) __threadfence();   // only the block that adds the slices in here has to see the others' partials
   __syncthreads();
   if (threadIdx.x == 0) HB_STAMP(7);
   if (warp == 5) {
@@ -244,7 +252,9 @@ __global__ void __launch_bounds__(192) gemm_stream_kernel(const __grid_constant_
 __global__ void __launch_bounds__(256) stream_reduce_kernel(const float* __restrict__ ws, void* C, long ldc, int M, int N,
                                                             int NP, int NT, int ksplit, int epi) {
   hb_pdl_launch();
+  HB_TL_MARK(5, 0);
   hb_pdl_wait();
+  HB_TL_MARK(5, 1);
   const int per_row = NP >> 2;
   const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (long)M * per_row) return;
@@ -280,6 +290,7 @@ __global__ void __launch_bounds__(256) stream_reduce_kernel(const float* __restr
   stream_store(epi, C, ldc, m, n + 1, N, acc.y, up.y, gate);
   stream_store(epi, C, ldc, m, n + 2, N, acc.z, up.z, gate);
   stream_store(epi, C, ldc, m, n + 3, N, acc.w, up.w, gate);
+  HB_TL_MARK(5, 3);
 }
 
 // The split of K for an [N, K] weight: a function of the weight's shape alone.

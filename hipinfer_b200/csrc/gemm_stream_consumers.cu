@@ -9,6 +9,8 @@
 // reason, src/kernels.cuh:164-330).
 #include "common.cuh"
 
+HB_TL_DEFINE(consumers)
+
 // The sum over the slices of four consecutive columns, added in slice order. All loads are
 // asked for before the first is used (up to 16 slices; the kernels here are short chains of
 // round trips to L2, and every round trip saved is most of a microsecond).
@@ -40,6 +42,8 @@ __global__ void __launch_bounds__(512) add_rmsnorm_slices_kernel(float* __restri
                                                                  int H, float eps) {
   __shared__ float sh[32];
   hb_pdl_launch();
+  const int tl = rows ? 2 : ksplit <= 8 ? 0 : 1;
+  HB_TL_MARK(tl, 0);
   const int nvec = H >> 2;
   float4 ww[NV];
 #pragma unroll
@@ -48,6 +52,7 @@ __global__ void __launch_bounds__(512) add_rmsnorm_slices_kernel(float* __restri
     ww[i] = c < nvec ? hb_load4(w + 4 * c) : make_float4(0.f, 0.f, 0.f, 0.f);
   }
   hb_pdl_wait();
+  HB_TL_MARK(tl, 1);
   const size_t r = rows ? (size_t)rows[blockIdx.x] : (size_t)blockIdx.x;
   float* xr = x + r * ldx;
   const float* pr = ws + r * row_stride;
@@ -65,6 +70,7 @@ __global__ void __launch_bounds__(512) add_rmsnorm_slices_kernel(float* __restri
     ss = fmaf(v[i].x, v[i].x, ss); ss = fmaf(v[i].y, v[i].y, ss);
     ss = fmaf(v[i].z, v[i].z, ss); ss = fmaf(v[i].w, v[i].w, ss);
   }
+  HB_TL_MARK(tl, 2);
   const float inv = rsqrtf(hb_block_sum(ss, sh) / (float)H + eps);
   __nv_bfloat16* yr = y + (size_t)blockIdx.x * H;
 #pragma unroll
@@ -74,6 +80,7 @@ __global__ void __launch_bounds__(512) add_rmsnorm_slices_kernel(float* __restri
       hb_store4(yr + 4 * c, make_float4(ww[i].x * (v[i].x * inv), ww[i].y * (v[i].y * inv), ww[i].z * (v[i].z * inv),
                                         ww[i].w * (v[i].w * inv)));
   }
+  HB_TL_MARK(tl, 3);
 }
 
 // x [M, H] fp32 (row stride ldx) += the slices; y [M or n_rows, H] bf16 = RMSNorm of the sum times w.
@@ -109,7 +116,9 @@ __global__ void __launch_bounds__(256) rope_kv_slices_kernel(const float* __rest
   const int t = blockIdx.x, half = D >> 1, hv = half >> 2;  // hv: groups of 4 pairs per head
   const float2* cs = table + (size_t)pos[t] * half;         // positions and slots are the step's own input
   const int slot = slot_map ? slot_map[t] : -1;
+  HB_TL_MARK(3, 0);
   hb_pdl_wait();
+  HB_TL_MARK(3, 1);
   const float* base = ws + (size_t)t * row_stride;
   const size_t page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot % page_size : 0;
   const int n_rot = (slot >= 0 ? Hq + Hkv : Hq) * hv, dv = D >> 2;
@@ -135,6 +144,7 @@ __global__ void __launch_bounds__(256) rope_kv_slices_kernel(const float* __rest
                 slices_sum4(base + (size_t)(Hq + Hkv) * D + h * D + d, ksplit, slice_stride));
     }
   }
+  HB_TL_MARK(3, 3);
 }
 
 // Rotary over the whole head only (D a multiple of 8); q_out and the cache are bf16.
