@@ -49,15 +49,17 @@ def peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons while the timed region runs (reading only)."""
+    """nvidia-smi clocks and throttle reasons while the timed region runs (reading only). The
+    process is started ahead of the region (it takes a while to print its first line); only the
+    lines that arrive between `with` entry and exit count."""
 
     Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self):
-        self.rows, self.proc = [], None
+        self.rows, self.proc, self.t0, self.t1 = [], None, None, None
 
-    def __enter__(self):
+    def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
                                           "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
@@ -68,9 +70,16 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append((time.monotonic(), [c.strip() for c in line.split(",")]))
+
+    def __enter__(self):
+        if self.proc is None:
+            self.start()
+        self.t0 = time.monotonic()
+        return self
 
     def __exit__(self, *a):
+        self.t1 = time.monotonic()
         if self.proc:
             self.proc.terminate()
             try:
@@ -79,10 +88,11 @@ class ClockSampler:
                 self.proc.kill()
 
     def summary(self):
-        sm = [int(r[0]) for r in self.rows if len(r) >= 6 and r[0].isdigit()]
-        mx = [int(r[1]) for r in self.rows if len(r) >= 6 and r[1].isdigit()]
+        rows = [r for t, r in self.rows if self.t0 is not None and self.t0 <= t <= self.t1 + 0.02 and len(r) >= 6]
+        sm = [int(r[0]) for r in rows if r[0].isdigit()]
+        mx = [int(r[1]) for r in rows if r[1].isdigit()]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(len(r) >= 6 and r[2 + i].lower().startswith("active") for r in self.rows)]
+        reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower().startswith("active") for r in rows)]
         return dict(sm_mhz=int(statistics.median(sm)) if sm else None, sm_max_mhz=max(mx) if mx else None,
                     reasons=reasons, samples=len(sm))
 
@@ -322,7 +332,7 @@ def main() -> int:
     point_batches = [] if a.no_points else [b for b in (1, 64) if b != a.batch]
     max_batch = max([a.batch] + point_batches)
     eng = build_engine(a.layers, max_batch, a.steps + a.warmup + 8)
-    clocks = ClockSampler()
+    clocks = ClockSampler().start()
     ms, mean_ctx, launches = decode_device(eng, a.batch, a.steps, a.warmup, clocks)
     value = a.batch / ms * 1e3
     step_bytes = eng.weight_bytes + a.batch * mean_ctx * eng.kv_bytes_per_token

@@ -113,7 +113,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
     hb_fence_barrier_init();
   }
   if (warp == 5) {
-    hb_tmem_alloc(tmem_slot, 2 * BN);
+    hb_tmem_alloc(tmem_slot, BN == 192 ? 512 : 2 * BN);   // a power of two
     hb_tmem_relinquish();
   }
   if (warp == 4 && lane == 0) {
@@ -241,7 +241,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
   }
   if (warp == 5) {
     __syncwarp();
-    hb_tmem_dealloc(tmem_base, 2 * BN);
+    hb_tmem_dealloc(tmem_base, BN == 192 ? 512 : 2 * BN);
   }
 }
 
@@ -371,17 +371,26 @@ HB_EXPORT int hb_gemm_tc(const void* A, long lda, const void* W, long ldw, void*
   if (epi == EPI_SWIGLU_BF16 && (N & 31)) HB_FAIL("hb_gemm_tc: SwiGLU needs N = %d to be a multiple of 32", N);
   if (!status) HB_FAIL("hb_gemm_tc: no status word");
   if (tile_n == 0) {
-    // 128 x 256 tiles feed the tensor cores best; the narrower tile only when the wide one
-    // would leave most SMs without work
-    const long tiles256 = (long)((M + BM - 1) / BM) * ((N + 255) / 256);
-    tile_n = (N >= 256 && 4 * tiles256 >= 3L * sm_count()) ? 256 : 128;
+    // 128 x 256 tiles feed the tensor cores best (a narrower tile reads more operand bytes per flop: measured
+    // 1.1 times the time per column at 192, 1.35 times at 128); a narrower one is taken when it fills the
+    // SMs' rounds better. An output's value is the same for every tile width.
+    const long mt = (M + BM - 1) / BM, sms = sm_count();
+    auto cost = [&](int bn, double per_col) { return (double)((mt * ((N + bn - 1) / bn) + sms - 1) / sms) * bn * per_col; };
+    tile_n = 256;
+    double best = cost(256, 1.0);
+    if ((epi == EPI_F32 || epi == EPI_ADD_F32) && cost(192, 1.1) < best) { tile_n = 192; best = cost(192, 1.1); }
+    if (cost(128, 1.35) < best) tile_n = 128;
   }
-  if (tile_n != 128 && tile_n != 256) HB_FAIL("hb_gemm_tc: tile_n must be 128 or 256");
+  if (tile_n != 128 && tile_n != 256 && !(tile_n == 192 && (epi == EPI_F32 || epi == EPI_ADD_F32)))
+    HB_FAIL("hb_gemm_tc: tile_n must be 128 or 256 (or 192 with an fp32 result)");
   CUtensorMap ma, mw;
   if (hb_make_tensor_map_bf16(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM)) return -1;
   if (hb_make_tensor_map_bf16(&mw, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, (uint32_t)tile_n)) return -1;
-  int r = tile_n == 256 ? dispatch_epi<256, 4>(epi, ma, mw, C, ldc, M, N, K, status, s)
-                        : dispatch_epi<128, 6>(epi, ma, mw, C, ldc, M, N, K, status, s);
+  int r;
+  if (tile_n == 256) r = dispatch_epi<256, 4>(epi, ma, mw, C, ldc, M, N, K, status, s);
+  else if (tile_n == 128) r = dispatch_epi<128, 6>(epi, ma, mw, C, ldc, M, N, K, status, s);
+  else r = epi == EPI_F32 ? launch_gemm_tc<192, 4, EPI_F32>(ma, mw, C, ldc, M, N, K, status, s)
+                          : launch_gemm_tc<192, 4, EPI_ADD_F32>(ma, mw, C, ldc, M, N, K, status, s);
   if (r) return r;
   HB_CHECK_LAUNCH("hb_gemm_tc");
   return 0;
