@@ -201,6 +201,24 @@ def test_attention_decode(Hq, Hkv, D, ps, window):
         torch.testing.assert_close(got[t:t + 1], ref, rtol=1e-2, atol=1e-2, msg=lambda m: f"row {t} {rows[t]}: {m}")
 
 
+def test_attention_decode_long_context_many_chunks():
+    """4,500 keys: 18 chunks of 256, more than the merge keeps in registers at once (its other path)."""
+    Hq, Hkv, D, ps = 4, 1, 64, 16
+    kc, vc, bt, ks, vs = _paged_setup([4500, 300], Hkv, D, ps, torch.bfloat16, 25)
+    rows = [(0, 4499), (1, 299), (0, 4096), (0, 4095)]
+    q = rnd(len(rows), Hq * D, seed=26)
+    qf = q.float().cpu().reshape(len(rows), Hq, D)
+    out = torch.empty(len(rows), Hq * D, dtype=torch.bfloat16, device=DEV)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    fast().attention_decode(q, kc, vc, bt, i32([r for r, _ in rows]), i32([p for _, p in rows]), out, Hq, Hkv, D, ps, 0,
+                            1 / math.sqrt(D), 4499, ctx_len=i32([4095, 299]))
+    sync_check()
+    got = out.float().cpu().reshape(len(rows), Hq, D)
+    for t, (r, p) in enumerate(rows):
+        ref = plain.attention_scores_softmax_values(qf[t:t + 1], ks[r][:p + 1], vs[r][:p + 1], [p], list(range(p + 1)))
+        torch.testing.assert_close(got[t:t + 1], ref, rtol=1e-2, atol=1e-2, msg=lambda m: f"row {t} {rows[t]}: {m}")
+
+
 def test_attention_decode_far_key_stands_out():
     Hq, Hkv, D, ps = 4, 1, 64, 16
     kc, vc, bt, ks, vs = _paged_setup([900], Hkv, D, ps, torch.bfloat16, 23)
