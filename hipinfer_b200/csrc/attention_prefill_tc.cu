@@ -1,4 +1,4 @@
-// Causal flash attention of prompt portions on the 5th-generation tensor cores (head_dim 64).
+// Causal flash attention of prompt portions on the 5th-generation tensor cores (head_dim 64 or 128).
 //
 // One CTA = 128 consecutive query rows of one request and one query head; it walks the
 // request's keys in tiles of 128 ABSOLUTE positions. Six warps:
@@ -24,8 +24,8 @@
 // reference (src/kernels.cuh:1335-1482). Every wait is bounded.
 #include "tc_common.cuh"
 
-constexpr int FT_BM = 128, FT_BN = 128, FT_D = 64;
-constexpr int FT_TILE = 128 * 64 * 2;  // one [128][64] bf16 tile: 16 KB
+constexpr int FT_BM = 128, FT_BN = 128;
+constexpr int FT_TILE = 128 * 64 * 2;  // one [128][64] bf16 tile: 16 KB; a [128][head_dim] operand is head_dim / 64 of them, 64 columns each
 
 // MN-major operand with the 128-byte swizzle: 64 contiguous elements of the MN dimension per row,
 // eight K rows per 1,024-byte group (stride SBO); further MN atoms would lie LBO apart (one here).
@@ -63,7 +63,10 @@ struct FtBars {
 #define FT_B(i) ((i) & 1)
 #define FT_PH(i) (((i) >> 1) & 1)
 
-__global__ void __launch_bounds__(192, 2) flash_prefill_tc_kernel(
+// head_dim 128: operands of two 64-column tiles each, the output tile 128 columns wide (512 TMEM
+// columns, 192 KB of shared memory: one CTA per SM).
+template <int FT_D>
+__global__ void __launch_bounds__(192, FT_D == 64 ? 2 : 1) flash_prefill_tc_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, const int* __restrict__ bt, int bt_stride, const int* __restrict__ q_start,
     const int* __restrict__ q_len, const int* __restrict__ ctx_len, __nv_bfloat16* __restrict__ out, int Hq, int Hkv,
@@ -71,10 +74,11 @@ __global__ void __launch_bounds__(192, 2) flash_prefill_tc_kernel(
   // the 128-byte swizzle wants the tiles on 1 KB boundaries; with no room for slack (two CTAs an SM) the
   // dynamic shared memory itself has to start on one, which is checked below
   extern __shared__ __align__(1024) uint8_t smem[];
-  uint8_t* sQ = smem;                  // [128][64]
-  uint8_t* sK = sQ + FT_TILE;          // two stages of [128 keys][64]
-  uint8_t* sV = sK + 2 * FT_TILE;      // two stages of [128 keys][64]
-  uint8_t* sP = sV + 2 * FT_TILE;      // two K blocks of [128 rows][64 keys]
+  constexpr int NH = FT_D / 64, OPND = NH * FT_TILE;   // 64-column tiles and bytes of a [128][head_dim] operand
+  uint8_t* sQ = smem;                  // [128][head_dim]
+  uint8_t* sK = sQ + OPND;             // two stages of [128 keys][head_dim]
+  uint8_t* sV = sK + 2 * OPND;         // two stages of [128 keys][head_dim]
+  uint8_t* sP = sV + 2 * OPND;         // two K blocks of [128 rows][64 keys]
   FtBars* bar = (FtBars*)(sP + 2 * FT_TILE);
   volatile int* abort_flag = &bar->abort_flag;
 
@@ -114,9 +118,9 @@ __global__ void __launch_bounds__(192, 2) flash_prefill_tc_kernel(
   }
   // masked keys of a last, ragged tile are never loaded: what the tensor core reads in their place
   // must be finite (P is exactly 0 there, and 0 * NaN would poison the row)
-  for (int i = threadIdx.x; i < 4 * FT_TILE / 16; i += 192) ((uint4*)sK)[i] = make_uint4(0, 0, 0, 0);
+  for (int i = threadIdx.x; i < 4 * OPND / 16; i += 192) ((uint4*)sK)[i] = make_uint4(0, 0, 0, 0);
   if (warp == 5) {
-    hb_tmem_alloc(&bar->tmem_slot, 256);
+    hb_tmem_alloc(&bar->tmem_slot, FT_D == 64 ? 256 : 512);
     hb_tmem_relinquish();
   }
   if (warp == 4 && lane == 0) { hb_tma_prefetch_desc(&map_q); hb_tma_prefetch_desc(&map_k); hb_tma_prefetch_desc(&map_v); }
@@ -124,13 +128,14 @@ __global__ void __launch_bounds__(192, 2) flash_prefill_tc_kernel(
   hb_tc_fence_before();
   __syncthreads();
   hb_tc_fence_after();
-  const uint32_t tmem_s = bar->tmem_slot, tmem_o = tmem_s + FT_BN;  // S: 128 columns, O: 2 x 64
+  const uint32_t tmem_s = bar->tmem_slot, tmem_o = tmem_s + FT_BN;  // S: 128 columns, O: 2 x head_dim
   hb_pdl_wait();   // barriers, shared and tensor memory were set up while the kernel ahead was still running
 
   if (warp == 4) {  // ---------------- TMA: lane l brings page l of the tile (the page ids come in one load)
     if (lane == 0) {
-      hb_mbar_expect_tx(&bar->q_full, FT_TILE);
-      hb_tma_load_2d(sQ, &map_q, &bar->q_full, hq * FT_D, row0);
+      hb_mbar_expect_tx(&bar->q_full, OPND);
+#pragma unroll
+      for (int hf = 0; hf < NH; hf++) hb_tma_load_2d(sQ + hf * FT_TILE, &map_q, &bar->q_full, hq * FT_D + hf * 64, row0);
     }
     for (int i = 0; i < n_tiles; i++) {
       const int k_base = (kt_lo + i) * FT_BN, b = FT_B(i);
@@ -139,20 +144,26 @@ __global__ void __launch_bounds__(192, 2) flash_prefill_tc_kernel(
       const uint32_t bytes = (uint32_t)np * page_size * FT_D * 2;
       const int pg = first_page + lane;
       const int row = lane < np ? (table[pg] * Hkv + h) * page_size : 0;
-      const int off = b * FT_TILE + (pg * page_size - k_base) * FT_D * 2;
+      const int off = b * OPND + (pg * page_size - k_base) * 128;   // rows of 128 bytes in each 64-column tile
       int ok = 1;
       if (lane == 0) {
         ok = hb_mbar_wait(&bar->k_free[b], FT_PH(i) ^ 1, abort_flag);
         if (ok) hb_mbar_expect_tx(&bar->k_full[b], bytes);
       }
       if (!__shfl_sync(0xffffffffu, ok, 0)) break;
-      if (lane < np) hb_tma_load_2d(sK + off, &map_k, &bar->k_full[b], 0, row);
+      if (lane < np) {
+#pragma unroll
+        for (int hf = 0; hf < NH; hf++) hb_tma_load_2d(sK + off + hf * FT_TILE, &map_k, &bar->k_full[b], hf * 64, row);
+      }
       if (lane == 0) {
         ok = hb_mbar_wait(&bar->v_free[b], FT_PH(i) ^ 1, abort_flag);
         if (ok) hb_mbar_expect_tx(&bar->v_full[b], bytes);
       }
       if (!__shfl_sync(0xffffffffu, ok, 0)) break;
-      if (lane < np) hb_tma_load_2d(sV + off, &map_v, &bar->v_full[b], 0, row);
+      if (lane < np) {
+#pragma unroll
+        for (int hf = 0; hf < NH; hf++) hb_tma_load_2d(sV + off + hf * FT_TILE, &map_v, &bar->v_full[b], hf * 64, row);
+      }
     }
   } else if (warp == 5) {
     if (lane == 0) {  // ---------------- tensor cores: S_i is issued before O_{i-1}, so it overlaps the softmax of tile i - 1
@@ -163,9 +174,12 @@ __global__ void __launch_bounds__(192, 2) flash_prefill_tc_kernel(
           const int b = FT_B(i);
           if (!hb_mbar_wait(&bar->k_full[b], FT_PH(i), abort_flag) || !hb_mbar_wait(&bar->s_free, (i & 1) ^ 1, abort_flag)) break;
           hb_tc_fence_after();
-          const uint64_t dq = hb_umma_desc_k128(hb_smem_u32(sQ)), dk = hb_umma_desc_k128(hb_smem_u32(sK + b * FT_TILE));
 #pragma unroll
-          for (int k = 0; k < FT_D / 16; k++) hb_umma_bf16(tmem_s, dq + 2 * k, dk + 2 * k, idesc_s, k != 0);
+          for (int k = 0; k < FT_D / 16; k++) {   // 16 columns a step: four steps in each 64-column tile
+            const uint64_t dq = hb_umma_desc_k128(hb_smem_u32(sQ + (k >> 2) * FT_TILE)) + 2 * (k & 3);
+            const uint64_t dk = hb_umma_desc_k128(hb_smem_u32(sK + b * OPND + (k >> 2) * FT_TILE)) + 2 * (k & 3);
+            hb_umma_bf16(tmem_s, dq, dk, idesc_s, k != 0);
+          }
           hb_umma_commit(&bar->s_full);
           hb_umma_commit(&bar->k_free[b]);
         }
@@ -178,7 +192,7 @@ __global__ void __launch_bounds__(192, 2) flash_prefill_tc_kernel(
 #pragma unroll
           for (int k = 0; k < FT_BN / 16; k++) {
             const uint64_t dp = hb_umma_desc_k128(hb_smem_u32(sP + (k >> 2) * FT_TILE)) + 2 * (k & 3);
-            const uint64_t dv = ft_desc_mn128(hb_smem_u32(sV + b * FT_TILE + k * 16 * FT_D * 2));
+            const uint64_t dv = ft_desc_mn128(hb_smem_u32(sV + b * OPND + k * 16 * 128));   // 16 keys on; the second 64 columns lie FT_TILE further (the descriptor's leading offset)
             hb_umma_bf16(tmem_o + b * FT_D, dp, dv, idesc_o, k != 0);
           }
           hb_umma_commit(&bar->o_full[b]);
@@ -280,14 +294,19 @@ __global__ void __launch_bounds__(192, 2) flash_prefill_tc_kernel(
         if (!hb_mbar_wait(&bar->o_full[b], FT_PH(j), abort_flag)) break;
         if (threadIdx.x == 0) FT_STAMP(6 + 6 * i);
         hb_tc_fence_after();
-        uint32_t orr[64];
-        hb_tmem_ld64_nowait(tmem_o + b * FT_D + lane_base, orr);
-        hb_tmem_ld_wait();
-        hb_tmem_ld_fence64(orr);
-        hb_tc_fence_before();
-        hb_mbar_arrive(&bar->o_free[b]);
 #pragma unroll
-        for (int d = 0; d < FT_D; d++) o[d] = fmaf(o[d], corr_prev, __uint_as_float(orr[d]));
+        for (int hf = 0; hf < NH; hf++) {
+          uint32_t orr[64];
+          hb_tmem_ld64_nowait(tmem_o + b * FT_D + hf * 64 + lane_base, orr);
+          hb_tmem_ld_wait();
+          hb_tmem_ld_fence64(orr);
+          if (hf == NH - 1) {
+            hb_tc_fence_before();
+            hb_mbar_arrive(&bar->o_free[b]);
+          }
+#pragma unroll
+          for (int d = 0; d < 64; d++) o[hf * 64 + d] = fmaf(o[hf * 64 + d], corr_prev, __uint_as_float(orr[d]));
+        }
       }
       corr_prev = corr;
       if (i == n_tiles && r < rows_here) {
@@ -312,15 +331,15 @@ __global__ void __launch_bounds__(192, 2) flash_prefill_tc_kernel(
   }
   if (warp == 5) {
     __syncwarp();
-    hb_tmem_dealloc(tmem_s, 256);
+    hb_tmem_dealloc(tmem_s, FT_D == 64 ? 256 : 512);
   }
 }
 
 HB_EXPORT int hb_flash_prefill_tc_supported(int Hq, int Hkv, int D, int page_size) {
-  return Hkv > 0 && Hq % Hkv == 0 && D == FT_D && page_size >= 8 && page_size <= FT_BN && (page_size & (page_size - 1)) == 0;
+  return Hkv > 0 && Hq % Hkv == 0 && (D == 64 || D == 128) && page_size >= 8 && page_size <= FT_BN && (page_size & (page_size - 1)) == 0;
 }
 
-// q, out [T, Hq, 64] bf16; caches [num_pages, Hkv, page_size, 64] bf16; per request q_start, q_len,
+// q, out [T, Hq, D] bf16; caches [num_pages, Hkv, page_size, D] bf16 (D 64 or 128); per request q_start, q_len,
 // ctx_len and a block table row, as hb_flash_prefill. Requests with fewer than min_rows rows are
 // skipped. `status` is set to 1 if a bounded wait ran out.
 HB_EXPORT int hb_flash_prefill_tc(const void* q, const void* kc, const void* vc, long num_pages, const int* bt, int bt_stride,
@@ -337,16 +356,30 @@ HB_EXPORT int hb_flash_prefill_tc(const void* q, const void* kc, const void* vc,
   const uint64_t rows = (uint64_t)num_pages * Hkv * page_size;
   if (hb_make_tensor_map_bf16(&mk, kc, rows, (uint64_t)D, (uint64_t)D, (uint32_t)page_size)) return -1;
   if (hb_make_tensor_map_bf16(&mv, vc, rows, (uint64_t)D, (uint64_t)D, (uint32_t)page_size)) return -1;
-  const size_t smem = 7 * (size_t)FT_TILE + sizeof(FtBars);   // 113 KB: two CTAs an SM
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(flash_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) HB_FAIL("hb_flash_prefill_tc: %s", cudaGetErrorString(e));
-    configured = true;
-  }
   dim3 grid((max_q_len + FT_BM - 1) / FT_BM, Hq, R);
-  cudaError_t e = hb_launch(flash_prefill_tc_kernel, grid, 192, smem, st, mq, mk, mv, bt, bt_stride, q_start, q_len, ctx_len,
-                            (__nv_bfloat16*)out, Hq, Hkv, page_size, window, scale * 1.4426950408889634f, min_rows, status);
+  const float sl2 = scale * 1.4426950408889634f;
+  cudaError_t e;
+  if (D == 64) {
+    const size_t smem = 7 * (size_t)FT_TILE + sizeof(FtBars);   // 113 KB: two CTAs an SM
+    static bool configured = false;
+    if (!configured) {
+      e = cudaFuncSetAttribute(flash_prefill_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) HB_FAIL("hb_flash_prefill_tc: %s", cudaGetErrorString(e));
+      configured = true;
+    }
+    e = hb_launch(flash_prefill_tc_kernel<64>, grid, 192, smem, st, mq, mk, mv, bt, bt_stride, q_start, q_len, ctx_len,
+                  (__nv_bfloat16*)out, Hq, Hkv, page_size, window, sl2, min_rows, status);
+  } else {
+    const size_t smem = 12 * (size_t)FT_TILE + sizeof(FtBars);  // Q, 2 K, 2 V of 32 KB each and P: 192 KB
+    static bool configured = false;
+    if (!configured) {
+      e = cudaFuncSetAttribute(flash_prefill_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) HB_FAIL("hb_flash_prefill_tc: %s", cudaGetErrorString(e));
+      configured = true;
+    }
+    e = hb_launch(flash_prefill_tc_kernel<128>, grid, 192, smem, st, mq, mk, mv, bt, bt_stride, q_start, q_len, ctx_len,
+                  (__nv_bfloat16*)out, Hq, Hkv, page_size, window, sl2, min_rows, status);
+  }
   if (e != cudaSuccess) HB_FAIL("hb_flash_prefill_tc: %s", cudaGetErrorString(e));
   HB_CHECK_LAUNCH("hb_flash_prefill_tc");
   return 0;
