@@ -25,6 +25,8 @@ import heapq
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
 
+import numpy as np
+
 
 class OutOfPages(RuntimeError):
     """A group's pool cannot cover the tokens asked for. Nothing was allocated."""
@@ -206,7 +208,13 @@ class CacheManager:
             for _ in range(n):
                 table.append(self.pools[g].alloc())
             ps = self.page_size
-            slot_maps.append([table[p // ps] * ps + p % ps for p in range(rc.length, rc.length + n_tokens)])
+            if n_tokens <= 8:
+                slot_maps.append([table[p // ps] * ps + p % ps for p in range(rc.length, rc.length + n_tokens)])
+            else:       # a prompt portion: the same in one numpy expression
+                p = np.arange(rc.length, rc.length + n_tokens)
+                first = rc.length // ps
+                pages = np.asarray(table[first:(rc.length + n_tokens - 1) // ps + 1], dtype=np.int64)
+                slot_maps.append((pages[p // ps - first] * ps + p % ps).tolist())
         rc.length += n_tokens
         return slot_maps
 

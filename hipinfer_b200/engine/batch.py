@@ -12,6 +12,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import List, Optional, Sequence
 
+import numpy as np
 import torch
 
 
@@ -84,9 +85,10 @@ def build_step_batch(entries: Sequence[StepEntry], ctx_lens: Sequence[int], stat
         off += n
         return o
 
-    toks = [int(t) for e in entries for t in e.tokens]
-    pos = [ctx_lens[r] + i for r in range(R) for i in range(q_len[r])]
-    rowreq = [r for r in range(R) for _ in range(q_len[r])]
+    # (numpy, not comprehensions: a prompt portion has thousands of rows)
+    toks = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries]) if R else np.zeros(0, np.int64)
+    pos = np.concatenate([np.arange(ctx_lens[r], ctx_lens[r] + q_len[r]) for r in range(R)]) if R else np.zeros(0, np.int64)
+    rowreq = np.repeat(np.arange(R), q_len)
     o_tok, o_pos, o_rr = put(toks, T), put(pos, T), put(rowreq, T)
     o_map = put(list(token_map) if token_map is not None else -1, T)
     o_qs, o_ql, o_cl, o_ss = put(q_start, R), put(q_len, R), put(list(ctx_lens), R), put(list(state_slots), R)
@@ -100,7 +102,8 @@ def build_step_batch(entries: Sequence[StepEntry], ctx_lens: Sequence[int], stat
             buf[o + r * w:o + r * w + len(row)] = row
         off += R * w
         o_bt.append(o)
-    o_sm = [put([s for r in range(R) for s in slot_maps[r][g]], T) for g in range(n_groups)]
+    o_sm = [put(np.concatenate([np.asarray(slot_maps[r][g], dtype=np.int64) for r in range(R)]) if R else [], T)
+            for g in range(n_groups)]
     if static is not None:
         assert static.numel() >= n_int
         static[:n_int].copy_(host[:n_int], non_blocking=True)
@@ -118,4 +121,4 @@ def build_step_batch(entries: Sequence[StepEntry], ctx_lens: Sequence[int], stat
         block_tables=[view(o_bt[g], R * widths[g]).view(R, widths[g]) for g in range(n_groups)],
         slot_maps=[view(o_sm[g], T) for g in range(n_groups)],
         h_q_start=q_start, h_q_len=q_len, h_ctx_len=list(ctx_lens), h_state_slot=list(state_slots),
-        max_pos=(max(pos) if pos else 0) if max_pos is None else max_pos, max_q_len=max(q_len) if q_len else 0)
+        max_pos=(int(pos.max()) if T else 0) if max_pos is None else max_pos, max_q_len=max(q_len) if q_len else 0)

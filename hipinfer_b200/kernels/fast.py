@@ -80,7 +80,7 @@ def check_status() -> None:
 
 
 def _stream():
-    return torch.cuda.current_stream().cuda_stream
+    return library.current_stream()
 
 
 def _tc_ok(a, w) -> bool:

@@ -164,3 +164,15 @@ def load(name: str) -> ctypes.CDLL:
 
 def build_all(verbose: bool = True) -> List[str]:
     return [build(n, verbose) for n in LIBRARIES]
+
+
+def current_stream() -> int:
+    """torch's current CUDA stream on the current device, as a raw cudaStream_t. A step launches more than a
+    hundred kernels: torch.cuda.current_stream() builds a Stream object each time (several microseconds), the
+    raw accessor does not."""
+    import torch
+
+    raw = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+    if raw is not None:
+        return raw(torch._C._cuda_getDevice())
+    return torch.cuda.current_stream().cuda_stream

@@ -64,7 +64,7 @@ def _call(lib_name: str, name: str, *args):
 
 
 def _stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    return library.current_stream()
 
 
 def _dt(t: torch.Tensor) -> int:
