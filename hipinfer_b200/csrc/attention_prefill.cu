@@ -50,7 +50,9 @@ __global__ void __launch_bounds__(FP_THREADS, HB_FP_MINB) flash_prefill_kernel(
   constexpr int CH = D / 8, KS = D / 16, NT_O = D / 8, TILE = FP_BKV * D * 2;
   extern __shared__ __align__(128) uint8_t smem[];
   // the last query tiles of a portion have the most keys to walk: they are started first
-  const int req = blockIdx.z, hq = blockIdx.y, qt = gridDim.x - 1 - blockIdx.x;
+  // blocks start in the order of blockIdx.x, then y: all heads' heaviest query tile first, then the next one
+  // (longest work first: with the query tile fastest, the last head's heaviest tile would start last and run alone)
+  const int req = blockIdx.z, hq = blockIdx.x, qt = gridDim.y - 1 - blockIdx.y;
   const int n_rows = q_len[req];
   if (n_rows < min_rows || qt * FP_BQ >= n_rows) return;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
@@ -200,9 +202,9 @@ HB_EXPORT int hb_flash_prefill(const void* q, const void* kc, const void* vc, co
                                cudaStream_t st) {
   if (R <= 0 || max_q_len <= 0) return 0;
   if (!hb_flash_prefill_supported(Hq, Hkv, D)) HB_FAIL("hb_flash_prefill: %d/%d heads of %d are not supported", Hq, Hkv, D);
-  if (R > 65535 || Hq > 65535) HB_FAIL("hb_flash_prefill: %d requests / %d heads are beyond the grid limit", R, Hq);
+  if (R > 65535 || max_q_len > 65535 * FP_BQ) HB_FAIL("hb_flash_prefill: %d requests / portions of %d rows are beyond the grid limit", R, max_q_len);
   const float scale_log2 = scale * 1.4426950408889634f;
-  dim3 grid((max_q_len + FP_BQ - 1) / FP_BQ, Hq, R);
+  dim3 grid(Hq, (max_q_len + FP_BQ - 1) / FP_BQ, R);
   const size_t smem = (size_t)(FP_BQ + 4 * FP_BKV) * D * 2;
   const __nv_bfloat16 *qq = (const __nv_bfloat16*)q, *kk = (const __nv_bfloat16*)kc, *vv = (const __nv_bfloat16*)vc;
   if (D == 64) {

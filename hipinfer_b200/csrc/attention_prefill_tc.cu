@@ -83,7 +83,9 @@ __global__ void __launch_bounds__(192, FT_D == 64 ? 2 : 1) flash_prefill_tc_kern
   volatile int* abort_flag = &bar->abort_flag;
 
   // the last query tiles of a portion have the most keys to walk: they are started first
-  const int req = blockIdx.z, hq = blockIdx.y, qt = gridDim.x - 1 - blockIdx.x;
+  // blocks start in the order of blockIdx.x, then y: all heads' heaviest query tile first, then the next one
+  // (longest work first: with the query tile fastest, the last head's heaviest tile would start last and run alone)
+  const int req = blockIdx.z, hq = blockIdx.x, qt = gridDim.y - 1 - blockIdx.y;
   // the step's own metadata (lengths, tables) was copied before the step's first kernel began; everything else
   // that an earlier kernel wrote is read after hb_pdl_wait() below
   hb_pdl_launch();
@@ -349,14 +351,14 @@ HB_EXPORT int hb_flash_prefill_tc(const void* q, const void* kc, const void* vc,
   if (R <= 0 || max_q_len <= 0 || T <= 0) return 0;
   if (!hb_flash_prefill_tc_supported(Hq, Hkv, D, page_size))
     HB_FAIL("hb_flash_prefill_tc: %d/%d heads of %d with pages of %d are not supported", Hq, Hkv, D, page_size);
-  if (R > 65535 || Hq > 65535) HB_FAIL("hb_flash_prefill_tc: %d requests / %d heads are beyond the grid limit", R, Hq);
+  if (R > 65535 || max_q_len > 65535 * FT_BM) HB_FAIL("hb_flash_prefill_tc: %d requests / portions of %d rows are beyond the grid limit", R, max_q_len);
   if (!status) HB_FAIL("hb_flash_prefill_tc: no status word");
   CUtensorMap mq, mk, mv;
   if (hb_make_tensor_map_bf16(&mq, q, (uint64_t)T, (uint64_t)Hq * D, (uint64_t)Hq * D, FT_BM)) return -1;
   const uint64_t rows = (uint64_t)num_pages * Hkv * page_size;
   if (hb_make_tensor_map_bf16(&mk, kc, rows, (uint64_t)D, (uint64_t)D, (uint32_t)page_size)) return -1;
   if (hb_make_tensor_map_bf16(&mv, vc, rows, (uint64_t)D, (uint64_t)D, (uint32_t)page_size)) return -1;
-  dim3 grid((max_q_len + FT_BM - 1) / FT_BM, Hq, R);
+  dim3 grid(Hq, (max_q_len + FT_BM - 1) / FT_BM, R);
   const float sl2 = scale * 1.4426950408889634f;
   cudaError_t e;
   if (D == 64) {
