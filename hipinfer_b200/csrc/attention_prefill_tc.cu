@@ -89,6 +89,7 @@ __global__ void __launch_bounds__(192, FT_D == 64 ? 2 : 1) flash_prefill_tc_kern
   // the step's own metadata (lengths, tables) was copied before the step's first kernel began; everything else
   // that an earlier kernel wrote is read after hb_pdl_wait() below
   hb_pdl_launch();
+  if (threadIdx.x == 0) FT_STAMP(200);   // (timing build) entry; 201: set-up done; 202: the end
   const int n_rows = q_len[req];
   if (n_rows < min_rows || qt * FT_BM >= n_rows) {
     if ((blockIdx.x | blockIdx.y | blockIdx.z) == 0) hb_pdl_wait();   // the grid never ends before the one ahead of it
@@ -132,6 +133,7 @@ __global__ void __launch_bounds__(192, FT_D == 64 ? 2 : 1) flash_prefill_tc_kern
   hb_tc_fence_after();
   const uint32_t tmem_s = bar->tmem_slot, tmem_o = tmem_s + FT_BN;  // S: 128 columns, O: 2 x head_dim
   hb_pdl_wait();   // barriers, shared and tensor memory were set up while the kernel ahead was still running
+  if (threadIdx.x == 0) FT_STAMP(201);
 
   if (warp == 4) {  // ---------------- TMA: lane l brings page l of the tile (the page ids come in one load)
     if (lane == 0) {
@@ -327,6 +329,7 @@ __global__ void __launch_bounds__(192, FT_D == 64 ? 2 : 1) flash_prefill_tc_kern
 
   hb_tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) FT_STAMP(202);
   if (*abort_flag) {
     if (threadIdx.x == 0) atomicExch(status, 1);
     __nanosleep(100000);
