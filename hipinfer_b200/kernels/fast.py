@@ -160,6 +160,8 @@ def gemm_stream(a, w, out, epi):
     nt = 16 if M <= 16 else 32 if M <= 32 else 64
     ws, cnt = _skinny_scratch(a.device, per_token * nt, n_blocks)
     _scratch_gen[0] += 1
+    if stream_plan(N, K)[1] > 1 and M >= 8:
+        library.launches[0] += 1     # the slices are added by a kernel of its own (counted here, launched by the call below)
     _call("hb_gemm_stream", a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0), M, N, K,
           epi, ws.data_ptr(), ws.numel(), cnt.data_ptr(), cnt.numel(), status_word().data_ptr(), _stream())
     return out

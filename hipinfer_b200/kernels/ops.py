@@ -252,6 +252,8 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], seed: Opti
         assert position is not None and position.dtype == torch.int32 and position.numel() == R
     n = library.load("core").hb_sample_slices(V)
     ws = torch.empty(2 * R * n, dtype=torch.int32, device=logits.device) if n > 1 else None
+    if n > 1:
+        library.launches[0] += 1     # two kernels: the slices' candidates, then the pick among them
     _call("core", "hb_sample", logits.data_ptr(), logits.stride(0), R, V, _ptr(temperature), _ptr(seed),
           _ptr(position), out.data_ptr(), _ptr(ws), _stream())
     return out
