@@ -4,8 +4,8 @@
 // (key chunk, kv head, row); the G query heads of the kv head share one pass over its keys and
 // values. Keys are cut into chunks of ABSOLUTE positions, so the split of a row depends on its
 // position alone. Softmax and the value sums are fp32; partial (acc, max, sum) of rows that span
-// several chunks go to a workspace and are merged in ascending chunk order by attn_merge_kernel
-// of the core library.
+// several chunks go to a workspace and are merged in ascending chunk order by the block of the
+// row and kv head that finishes last.
 #include "tc_common.cuh"
 
 HB_TL_DEFINE(attn)
