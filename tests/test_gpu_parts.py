@@ -307,6 +307,164 @@ def test_toy_architecture_registered_from_the_test(dtype):
     runner.end("long")
 
 
+# ------------------------------------------------------------------------------------------
+# A second toy architecture: a position encoding and a feed-forward of its own kind.
+#   layer 0: attention with "toy_decay_position" (no rotation: q_t is scaled by e^(+l t), k_s by e^(-l s), so a
+#            score carries the factor e^(l (t - s))) + "toy_top1_experts" (a router picks one of E small experts)
+#   layer 1: attention with rope + SwiGLU
+# ------------------------------------------------------------------------------------------
+def _register_toy2():
+    from hipinfer_b200.config import ModelConfig, register_architecture, take
+    from hipinfer_b200.parts import LayerSpec, ModelSpec, Part, PartSpec, RunStep, register_part
+    from hipinfer_b200.weights import ParamSpec
+
+    class DecayPosition(Part):
+        """params: head_dim, rate. It has no `pending` argument: the mixer finishes its product first."""
+
+        def __init__(self, params, ctx, prefix=""):
+            super().__init__(params, ctx, prefix)
+            self.head_dim, self.rate = params["head_dim"], params["rate"]
+
+        def rotate_and_store(self, qkv, positions, slot_map, q_out, k_cache, v_cache, n_heads, n_kv_heads):
+            T, D, ps = qkv.shape[0], self.head_dim, self.ctx.page_size
+            p = positions.float()[:, None, None]
+            q = qkv[:, :n_heads * D].float().reshape(T, n_heads, D) * torch.exp(self.rate * p)
+            k = qkv[:, n_heads * D:(n_heads + n_kv_heads) * D].float().reshape(T, n_kv_heads, D) * torch.exp(-self.rate * p)
+            v = qkv[:, (n_heads + n_kv_heads) * D:].float().reshape(T, n_kv_heads, D)
+            q_out.copy_(q.reshape(T, n_heads * D).to(q_out.dtype))
+            if slot_map is not None:
+                page, off = (slot_map // ps).long(), (slot_map % ps).long()
+                k_cache[page, :, off] = k.to(k_cache.dtype)
+                v_cache[page, :, off] = v.to(v_cache.dtype)
+            return q_out
+
+    class Top1Experts(Part):
+        """params: hidden_size, inner_size, n_experts. y = p_e W2_e relu(W1_e xn), e = arg max of the router's softmax p."""
+
+        def __init__(self, params, ctx, prefix=""):
+            super().__init__(params, ctx, prefix)
+            self.H, self.I, self.E = params["hidden_size"], params["inner_size"], params["n_experts"]
+            self.names = [prefix + n for n in ("moe.router.weight", "moe.w1", "moe.w2")]
+
+        def param_specs(self):
+            return [ParamSpec(self.names[0], (self.E, self.H)), ParamSpec(self.names[1], (self.E * self.I, self.H)),
+                    ParamSpec(self.names[2], (self.E * self.H, self.I))]
+
+        def load(self, tensors):
+            self.router = tensors[self.names[0]].float()
+            self.w1 = tensors[self.names[1]].float().reshape(self.E, self.I, self.H)
+            self.w2 = tensors[self.names[2]].float().reshape(self.E, self.H, self.I)
+
+        def forward(self, xn, x, batch):
+            xf = xn.float()
+            p = torch.softmax(xf @ self.router.T, -1)
+            e = p.argmax(-1)
+            h = torch.relu(torch.einsum("tih,th->ti", self.w1[e], xf))
+            x += p.gather(1, e[:, None]) * torch.einsum("thi,ti->th", self.w2[e], h)
+
+    @dataclass(frozen=True)
+    class Toy2Config(ModelConfig):
+        vocab_size: int
+        hidden_size: int
+        n_heads: int
+        n_kv_heads: int
+        head_dim: int
+        intermediate_size: int
+        n_experts: int
+        rate: float
+        eps: float
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(d["architectures"][0], *(take(d, k, int) for k in ("vocab_size", "hidden_size", "n_heads", "n_kv_heads",
+                       "head_dim", "intermediate_size", "n_experts")), take(d, "rate", float), take(d, "eps", float))
+
+        def to_dict(self):
+            return dict(architectures=[self.architecture], **{k: getattr(self, k) for k in (
+                "vocab_size", "hidden_size", "n_heads", "n_kv_heads", "head_dim", "intermediate_size", "n_experts", "rate", "eps")})
+
+    def toy2_spec(c):
+        H = c.hidden_size
+        norm = lambda name: PartSpec("rmsnorm", dict(name=name, size=H, eps=c.eps))
+        att = lambda pos: PartSpec("attention", dict(hidden_size=H, n_heads=c.n_heads, n_kv_heads=c.n_kv_heads,
+                                                     head_dim=c.head_dim, window=0, position=pos))
+        mixers = [att(PartSpec("toy_decay_position", dict(head_dim=c.head_dim, rate=c.rate))),
+                  att(PartSpec("rope", dict(head_dim=c.head_dim, theta=10000.0, scaling=None)))]
+        ffns = [PartSpec("toy_top1_experts", dict(hidden_size=H, inner_size=c.intermediate_size, n_experts=c.n_experts)),
+                PartSpec("swiglu", dict(hidden_size=H, intermediate_size=c.intermediate_size))]
+        layers = tuple(LayerSpec(f"toy2.layers.{i}.", "pre_norm", mixers[i], norm("input_layernorm.weight"), ffns[i],
+                                 norm("post_attention_layernorm.weight")) for i in range(2))
+        return ModelSpec(c.architecture, H, c.vocab_size, 256,
+                         PartSpec("token", dict(name="toy2.embed.weight", vocab_size=c.vocab_size, hidden_size=H)), layers,
+                         (RunStep(0), RunStep(1)), norm("toy2.norm.weight"),
+                         PartSpec("linear", dict(tied_to="toy2.embed.weight", vocab_size=c.vocab_size, hidden_size=H)))
+
+    register_part("position", "toy_decay_position", DecayPosition)
+    register_part("feed_forward", "toy_top1_experts", Top1Experts)
+    register_architecture("Toy2ForCausalLM", Toy2Config, toy2_spec)
+
+
+TOY2 = dict(architectures=["Toy2ForCausalLM"], vocab_size=150, hidden_size=64, n_heads=4, n_kv_heads=2, head_dim=64,
+            intermediate_size=48, n_experts=3, rate=0.004, eps=1e-6)
+
+
+def toy2_plain(c, w, tokens):
+    T, H, Hq, Hkv, D, E, I = (len(tokens), c["hidden_size"], c["n_heads"], c["n_kv_heads"], c["head_dim"], c["n_experts"],
+                              c["intermediate_size"])
+    pos = list(range(T))
+    x = plain.embed(tokens, w["toy2.embed.weight"])
+    p0, p1 = "toy2.layers.0.", "toy2.layers.1."
+    # layer 0: attention with the decaying position factors
+    xn = plain.rmsnorm(x, w[p0 + "input_layernorm.weight"], c["eps"])
+    t = torch.arange(T, dtype=torch.float32)[:, None, None]
+    q = (xn @ w[p0 + "self_attn.q_proj.weight"].T).reshape(T, Hq, D) * torch.exp(c["rate"] * t)
+    k = (xn @ w[p0 + "self_attn.k_proj.weight"].T).reshape(T, Hkv, D) * torch.exp(-c["rate"] * t)
+    v = (xn @ w[p0 + "self_attn.v_proj.weight"].T).reshape(T, Hkv, D)
+    x = x + plain.attention_scores_softmax_values(q, k, v, pos, pos).reshape(T, Hq * D) @ w[p0 + "self_attn.o_proj.weight"].T
+    # layer 0: one expert per token
+    xn = plain.rmsnorm(x, w[p0 + "post_attention_layernorm.weight"], c["eps"])
+    p = torch.softmax(xn @ w[p0 + "moe.router.weight"].T, -1)
+    w1, w2 = w[p0 + "moe.w1"].reshape(E, I, H), w[p0 + "moe.w2"].reshape(E, H, I)
+    for i in range(T):
+        e = int(p[i].argmax())
+        x[i] = x[i] + p[i, e] * (w2[e] @ torch.relu(w1[e] @ xn[i]))
+    # layer 1: the architecture's own parts
+    inv = plain.rope_inv_freq(D, 10000.0)
+    x = x + plain.attention_block(plain.rmsnorm(x, w[p1 + "input_layernorm.weight"], c["eps"]),
+                                  *(w[p1 + f"self_attn.{n}_proj.weight"] for n in "qkvo"), pos, Hq, Hkv, D, inv)
+    x = x + plain.swiglu_mlp(plain.rmsnorm(x, w[p1 + "post_attention_layernorm.weight"], c["eps"]),
+                             *(w[p1 + f"mlp.{n}_proj.weight"] for n in ("gate", "up", "down")))
+    return plain.lm_head(x, w["toy2.norm.weight"], w["toy2.embed.weight"], c["eps"])
+
+
+def test_toy_position_encoding_and_routed_feed_forward():
+    """Another position encoding and a feed-forward with routing, defined here, in one model beside the
+    architecture's own parts (32-bit: a router's arg max is not stable under bfloat16 rounding)."""
+    from hipinfer_b200.config import config_from_dict, get_architecture
+    from hipinfer_b200.engine import ModelRunner
+    from hipinfer_b200.parts import spec_param_specs
+    from hipinfer_b200.weights import random_weights
+
+    _register_toy2()
+    cfg = config_from_dict(TOY2)
+    spec = get_architecture("Toy2ForCausalLM").build_spec(cfg)
+    tensors = random_weights(spec_param_specs(spec), seed=11, std=0.08, norm_std=0.1, dtype=torch.float32)
+    assert "toy2.layers.0.moe.router.weight" in tensors and "toy2.layers.0.mlp.gate_proj.weight" not in tensors
+    runner = ModelRunner(cfg, {k: v.to(DEV) for k, v in tensors.items()}, dtype="float32", num_pages=30, max_model_len=256,
+                         max_num_seqs=4, cuda_graphs=False)
+    w = {k: v.float() for k, v in tensors.items()}
+    requests = {f"u{i}": tiny.random_tokens(n, 150, 80 + i) for i, n in enumerate([120, 33, 70, 9])}
+    ref = {rid: toy2_plain(TOY2, w, toks) for rid, toks in requests.items()}
+    st = tiny.RunnerStepper(runner)
+    for name, plan in (("whole", tiny.plan_whole(requests)), ("portions", tiny.plan_portions(requests)),
+                       ("mixed", tiny.plan_mixed(requests, 3))):
+        got = tiny.run_plan(st, requests, plan)
+        for rid in requests:
+            tiny.assert_logits_close(got[rid], ref[rid], "float32", f"toy2 {name} {rid}")
+        runner.cache.check()
+        assert runner.cache.free_pages() == [30] and runner.cache.slots.free_count == 4
+
+
 def test_unknown_part_kind_is_named():
     from hipinfer_b200.parts import BuildContext, PartSpec, build_part
 
