@@ -133,7 +133,9 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
 #else
   const int t = blockIdx.z, h = blockIdx.y, s = blockIdx.x;
 #endif
-  const int rq = row_req[t];
+  // row_req null: a step of single decode rows, row t being request t (and its position the length its request had):
+  // one round trip to memory less before the keys can be asked for
+  const int rq = row_req ? row_req[t] : t;
   const int p = pos[t];
   const int lo = window > 0 ? max(0, p - window + 1) : 0;
   const int s_lo = lo / chunk, s_hi = p / chunk;
@@ -142,7 +144,7 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
     return;
   }
   const int k0 = max(s * chunk, lo), k1 = min((s + 1) * chunk, p + 1), nk = k1 - k0;
-  const int n_old = ctx_len ? max(0, min(k1, ctx_len[rq]) - k0) : 0;   // rows of the tile from earlier steps
+  const int n_old = ctx_len ? max(0, min(k1, row_req ? ctx_len[rq] : p) - k0) : 0;   // rows of the tile from earlier steps
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, tq = lane & 3;
   const int* table = bt + (size_t)rq * bt_stride;
   bool loaded = true;
@@ -435,7 +437,7 @@ HB_EXPORT int hb_attn_decode_supported(int Hq, int Hkv, int D) {
 // between calls (needed when S > 1). With q_len given, rows of requests whose portion has
 // row_limit rows or more are skipped (the flash kernel computes those). ctx_len (per request,
 // or null): the tokens that were in the cache before this step; their keys may be read before
-// the kernel ahead in the stream has ended. n_pages: the pages the cache holds (its first
+// the kernel ahead in the stream has ended. row_req null: row t is request t's only row. n_pages: the pages the cache holds (its first
 // extent); status: the word a bounded wait that ran out sets to 1. With both, no window, a chunk
 // of 256 and pages of 8 to 64 tokens the keys and values come by TMA.
 HB_EXPORT int hb_attn_decode(const void* q, const void* kc, const void* vc, long n_pages, const int* bt, int bt_stride,

@@ -285,7 +285,8 @@ def attention_decode(q, k_cache, v_cache, block_table, row_request, positions, o
                      page_size, window, scale, max_pos, chunk=DECODE_CHUNK, q_len=None, row_limit=0, ctx_len=None):
     """The bf16 row-attention kernel itself (see csrc/attention_fast.cu); rows whose keys span several
     chunks are finished inside it. With q_len (int32 per request) rows of requests with row_limit
-    rows or more are skipped. ctx_len (int32 per request): the tokens in the cache before this
+    rows or more are skipped. row_request None: row t is the only row of request t (a decode-only
+    step). ctx_len (int32 per request): the tokens in the cache before this
     step; with it the kernel asks for their keys before the kernel ahead of it has ended, so
     positions, tables and ctx_len must then be in place before that kernel starts."""
     from . import ops
@@ -294,7 +295,7 @@ def attention_decode(q, k_cache, v_cache, block_table, row_request, positions, o
     ws = ops.attention_workspace(T, n_heads, head_dim, max_pos, chunk, q.device)
     cnt = None if ws is None else _decode_counters(q.device, T * n_kv_heads)
     _call("hb_attn_decode", q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), k_cache.shape[0], block_table.data_ptr(),
-          block_table.stride(0), row_request.data_ptr(), positions.data_ptr(), out.data_ptr(),
+          block_table.stride(0), None if row_request is None else row_request.data_ptr(), positions.data_ptr(), out.data_ptr(),
           None if ws is None else ws.data_ptr(), None if cnt is None else cnt.data_ptr(), T, n_heads, n_kv_heads,
           head_dim, page_size, int(window), float(scale), chunk, int(max_pos),
           None if q_len is None else q_len.data_ptr(), int(row_limit), None if ctx_len is None else ctx_len.data_ptr(),
@@ -353,7 +354,9 @@ def attention(q, k_cache, v_cache, batch, group, out, n_heads, n_kv_heads, head_
                                                     batch.req_ctx_len, out, batch.max_q_len, n_heads, n_kv_heads,
                                                     head_dim, page_size, window, scale, FLASH_MIN_ROWS)
     if need_rows:
-        attention_decode(q, k_cache, v_cache, bt, batch.row_request, batch.positions, out, n_heads, n_kv_heads,
+        # a step of single decode rows: row t is request t, which the kernel need not look up
+        rows_are_requests = batch.max_q_len == 1 and batch.n_rows == batch.n_requests
+        attention_decode(q, k_cache, v_cache, bt, None if rows_are_requests else batch.row_request, batch.positions, out, n_heads, n_kv_heads,
                          head_dim, page_size, window, scale, batch.max_pos,
                          q_len=batch.req_q_len if use_flash else None, row_limit=FLASH_MIN_ROWS,
                          ctx_len=batch.req_ctx_len)

@@ -104,7 +104,7 @@ def main(argv=None) -> int:
         scale = 1.0 / math.sqrt(D)
         if a.kernel == "attn_decode":
             rr, pos, cl = i32(list(range(R))), i32([ctx - 1] * R), i32(ctx_len)
-            fn = lambda: fast.attention_decode(q, kc, vc, bt, rr, pos, o, Hq, Hkv, D, ps, 0, scale, ctx - 1, ctx_len=cl)
+            fn = lambda: fast.attention_decode(q, kc, vc, bt, None, pos, o, Hq, Hkv, D, ps, 0, scale, ctx - 1, ctx_len=cl)   # row t = request t, as in a decode step
             nbytes = 2 * R * ctx * Hkv * D * 2
             flops = 4.0 * R * ctx * Hq * D
         else:

@@ -224,6 +224,21 @@ def test_attention_decode_long_context_many_chunks():
         torch.testing.assert_close(got[t:t + 1], ref, rtol=1e-2, atol=1e-2, msg=lambda m: f"row {t} {rows[t]}: {m}")
 
 
+def test_attention_decode_rows_that_are_requests():
+    """A decode-only step: row t is request t, which the kernel then does not look up: the same bits."""
+    Hq, Hkv, D, ps = 8, 2, 64, 16
+    lens = [700, 37, 1, 300, 257]
+    kc, vc, bt, ks, vs = _paged_setup(lens, Hkv, D, ps, torch.bfloat16, 27)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    q = rnd(len(lens), Hq * D, seed=28)
+    pos, rr = i32([n - 1 for n in lens]), i32(list(range(len(lens))))
+    a, b = (torch.empty(len(lens), Hq * D, dtype=torch.bfloat16, device=DEV) for _ in range(2))
+    fast().attention_decode(q, kc, vc, bt, rr, pos, a, Hq, Hkv, D, ps, 0, 1 / math.sqrt(D), max(lens) - 1, ctx_len=pos)
+    fast().attention_decode(q, kc, vc, bt, None, pos, b, Hq, Hkv, D, ps, 0, 1 / math.sqrt(D), max(lens) - 1, ctx_len=pos)
+    sync_check()
+    assert torch.equal(a, b)
+
+
 def test_attention_decode_far_key_stands_out():
     Hq, Hkv, D, ps = 4, 1, 64, 16
     kc, vc, bt, ks, vs = _paged_setup([900], Hkv, D, ps, torch.bfloat16, 23)
