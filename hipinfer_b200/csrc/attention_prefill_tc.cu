@@ -10,14 +10,16 @@
 //   warps 0-3            softmax: a thread owns one query ROW: it reads its row of S from
 //                        tensor memory (no shuffles for max or sum), masks on absolute positions,
 //                        exponentiates in the exp2 domain in fp32, writes P as bf16 into shared
-//                        memory in the swizzled K-major layout the tensor core reads, and keeps
-//                        the output row in registers: o = o * 2^(m_old - m_new) + O_tile.
-// The output tile is double-buffered in tensor memory and K, V in shared memory; the output tile
-// of tile i is added one tile late, so a softmax thread rarely waits for the tensor core. A CTA
-// takes 256 columns of tensor memory (S 128, O 2 x 64), 113 KB of shared memory and at most 168
-// registers a thread (a row of S is read in two halves of 64, the first one twice: once for the
-// maximum, once for the exponentials), so that TWO CTAs share an SM: while the softmax of one
-// keeps the special-function unit busy, the other stores P, adds its output tile or waits for the
+//                        memory in the swizzled K-major layout the tensor core reads. The output
+//                        row stays in tensor memory over all the tiles (the products accumulate);
+//                        it is in units of 2^m, where m follows the row's maximum lazily: only a
+//                        maximum that exceeds m by more than 8 raises it, and only then is the row
+//                        read, rescaled and written back.
+// K and V are double-buffered in shared memory, S and P single. A CTA takes 256 columns of tensor
+// memory (S 128, O head_dim), 113 KB of shared memory at head_dim 64 and 114 registers a thread (a
+// row of S is read in two halves of 64, the first one twice: once for the maximum, once for the
+// exponentials), so that TWO CTAs share an SM: while the softmax of one keeps the
+// special-function unit busy, the other stores P or waits for the
 // tensor core. Because tiles are cut at absolute
 // positions and a row's running max and sum are its own, a row's result does not depend on how
 // the prompt was cut or on what else is in the batch. Replaces flash_prefill_mma_kernel of the
@@ -38,12 +40,21 @@ __host__ __device__ constexpr uint32_t ft_idesc_b_mn(int M, int N) { return hb_u
 
 #ifdef HB_FT_TIMING
 __device__ unsigned long long g_ft_stamps[256];
+__device__ unsigned long long g_ft_blocks[4 * 1024];   // every block's entry, set-up, end and SM
 __device__ __forceinline__ void ft_stamp(int i) {
-  if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && i < 256) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    g_ft_stamps[i] = t;
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && i < 256) g_ft_stamps[i] = t;
+  const int lin = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+  if (i >= 200 && lin < 1024) {
+    g_ft_blocks[4 * lin + (i - 200)] = t;
+    unsigned sm;
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(sm));
+    g_ft_blocks[4 * lin + 3] = sm;
   }
+}
+HB_EXPORT int hb_ft_blocks(unsigned long long* out) {
+  return cudaMemcpyFromSymbol(out, g_ft_blocks, sizeof(g_ft_blocks)) == cudaSuccess ? 0 : -1;
 }
 HB_EXPORT int hb_ft_stamps(unsigned long long* out) {
   return cudaMemcpyFromSymbol(out, g_ft_stamps, sizeof(g_ft_stamps)) == cudaSuccess ? 0 : -1;
@@ -54,7 +65,7 @@ HB_EXPORT int hb_ft_stamps(unsigned long long* out) {
 #endif
 
 struct FtBars {
-  uint64_t q_full, k_full[2], k_free[2], v_full[2], v_free[2], s_full, s_free, o_full[2], o_free[2], p_full, p_free;
+  uint64_t q_full, k_full[2], k_free[2], v_full[2], v_free[2], s_full, s_free, o_full, p_full, p_free;
   uint32_t tmem_slot;
   int abort_flag;
 };
@@ -63,10 +74,10 @@ struct FtBars {
 #define FT_B(i) ((i) & 1)
 #define FT_PH(i) (((i) >> 1) & 1)
 
-// head_dim 128: operands of two 64-column tiles each, the output tile 128 columns wide (512 TMEM
-// columns, 192 KB of shared memory: one CTA per SM).
+// head_dim 128: operands of two 64-column tiles each, the output tile 128 columns wide (192 KB of
+// shared memory: one CTA per SM).
 template <int FT_D>
-__global__ void __launch_bounds__(192, FT_D == 64 ? 2 : 1) flash_prefill_tc_kernel(
+__global__ void __launch_bounds__(FT_D == 64 ? 256 : 192, FT_D == 64 ? 2 : 1) flash_prefill_tc_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, const int* __restrict__ bt, int bt_stride, const int* __restrict__ q_start,
     const int* __restrict__ q_len, const int* __restrict__ ctx_len, __nv_bfloat16* __restrict__ out, int Hq, int Hkv,
@@ -112,8 +123,8 @@ __global__ void __launch_bounds__(192, FT_D == 64 ? 2 : 1) flash_prefill_tc_kern
     for (int b = 0; b < 2; b++) {
       hb_mbar_init(&bar->k_full[b], 1); hb_mbar_init(&bar->k_free[b], 1);
       hb_mbar_init(&bar->v_full[b], 1); hb_mbar_init(&bar->v_free[b], 1);
-      hb_mbar_init(&bar->o_full[b], 1); hb_mbar_init(&bar->o_free[b], 128);
     }
+    hb_mbar_init(&bar->o_full, 1);
     hb_mbar_init(&bar->p_full, 128); hb_mbar_init(&bar->p_free, 1);
     hb_mbar_init(&bar->s_full, 1); hb_mbar_init(&bar->s_free, 128);
     bar->abort_flag = 0;
@@ -123,7 +134,7 @@ __global__ void __launch_bounds__(192, FT_D == 64 ? 2 : 1) flash_prefill_tc_kern
   // must be finite (P is exactly 0 there, and 0 * NaN would poison the row)
   for (int i = threadIdx.x; i < 4 * OPND / 16; i += 192) ((uint4*)sK)[i] = make_uint4(0, 0, 0, 0);
   if (warp == 5) {
-    hb_tmem_alloc(&bar->tmem_slot, FT_D == 64 ? 256 : 512);
+    hb_tmem_alloc(&bar->tmem_slot, 256);
     hb_tmem_relinquish();
   }
   if (warp == 4 && lane == 0) { hb_tma_prefetch_desc(&map_q); hb_tma_prefetch_desc(&map_k); hb_tma_prefetch_desc(&map_v); }
@@ -131,7 +142,7 @@ __global__ void __launch_bounds__(192, FT_D == 64 ? 2 : 1) flash_prefill_tc_kern
   hb_tc_fence_before();
   __syncthreads();
   hb_tc_fence_after();
-  const uint32_t tmem_s = bar->tmem_slot, tmem_o = tmem_s + FT_BN;  // S: 128 columns, O: 2 x head_dim
+  const uint32_t tmem_s = bar->tmem_slot, tmem_o = tmem_s + FT_BN;  // S: 128 columns, O: head_dim columns
   hb_pdl_wait();   // barriers, shared and tensor memory were set up while the kernel ahead was still running
   if (threadIdx.x == 0) FT_STAMP(201);
 
@@ -189,17 +200,15 @@ __global__ void __launch_bounds__(192, FT_D == 64 ? 2 : 1) flash_prefill_tc_kern
         }
         if (i > 0) {
           const int j = i - 1, b = FT_B(j);
-          if (!hb_mbar_wait(&bar->p_full, j & 1, abort_flag) || !hb_mbar_wait(&bar->v_full[b], FT_PH(j), abort_flag) ||
-              !hb_mbar_wait(&bar->o_free[b], FT_PH(j) ^ 1, abort_flag))
-            break;
+          if (!hb_mbar_wait(&bar->p_full, j & 1, abort_flag) || !hb_mbar_wait(&bar->v_full[b], FT_PH(j), abort_flag)) break;
           hb_tc_fence_after();
 #pragma unroll
           for (int k = 0; k < FT_BN / 16; k++) {
             const uint64_t dp = hb_umma_desc_k128(hb_smem_u32(sP + (k >> 2) * FT_TILE)) + 2 * (k & 3);
             const uint64_t dv = ft_desc_mn128(hb_smem_u32(sV + b * OPND + k * 16 * 128));   // 16 keys on; the second 64 columns lie FT_TILE further (the descriptor's leading offset)
-            hb_umma_bf16(tmem_o + b * FT_D, dp, dv, idesc_o, k != 0);
+            hb_umma_bf16(tmem_o, dp, dv, idesc_o, j != 0 || k != 0);   // O stays in tensor memory over all the tiles
           }
-          hb_umma_commit(&bar->o_full[b]);
+          hb_umma_commit(&bar->o_full);
           hb_umma_commit(&bar->v_free[b]);
           hb_umma_commit(&bar->p_free);
         }
@@ -209,119 +218,132 @@ __global__ void __launch_bounds__(192, FT_D == 64 ? 2 : 1) flash_prefill_tc_kern
     const int r = warp * 32 + lane;
     const int qp = p_first + min(r, rows_here - 1);  // rows past the portion's end are computed, never stored
     const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-    float o[FT_D];
+    // The output row accumulates in tensor memory over all the tiles, in units of 2^m_run. m_run follows the
+    // row's maximum lazily: it is raised (and the row of O rescaled, which has to wait for the product of the
+    // tile before) only when a tile's maximum exceeds it by more than FT_SLACK, so P <= 2^FT_SLACK; the sum
+    // l_run is in the same units, and O / l_run is exact whichever maxima were used.
+    constexpr float FT_SLACK = 8.f;
+    float m_run = -INFINITY, l_run = 0.f;
+    bool ok = true;   // every wait's outcome is made uniform over the warp: the tensor-memory accesses below are warp-wide
+    for (int i = 0; i < n_tiles && ok; i++) {
+      const int k_base = (kt_lo + i) * FT_BN;
+      const bool need_mask = k_base + FT_BN - 1 > p_first || (window > 0 && k_base < p_last - window + 1);
+      if (threadIdx.x == 0) FT_STAMP(1 + 6 * i);
+      if (!__all_sync(0xffffffffu, hb_mbar_wait(&bar->s_full, i & 1, abort_flag))) { ok = false; break; }
+      if (threadIdx.x == 0) FT_STAMP(2 + 6 * i);
+      hb_tc_fence_after();
+      // the row of S in two halves of 64 keys, the first one read twice (once for the maximum, once for the
+      // exponentials): 128 registers a thread is all that lets a new CTA start beside one that is still
+      // running (see the launch bounds). A softmax warp is alone on its scheduler: four independent chains
+      // for the maximum and for the sum, and the mask only where one is needed
+      uint32_t sr[64];
+      const int hi_j = qp - k_base, lo_j = window > 0 ? qp - window - k_base : -1;  // key j of the tile is visible iff lo_j < j <= hi_j
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-    for (int d = 0; d < FT_D; d++) o[d] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f, corr_prev = 0.f;
-    bool ok = true;
-    for (int i = 0; i <= n_tiles && ok; i++) {
+      for (int hh = 0; hh < 2; hh++) {
+        hb_tmem_ld64_nowait(tmem_s + lane_base + hh * 64, sr);
+        hb_tmem_ld_wait();
+        hb_tmem_ld_fence64(sr);
+        if (need_mask) {
+#pragma unroll
+          for (int j = 0; j < 64; j++) {
+            const float v = (j + hh * 64 <= hi_j && j + hh * 64 > lo_j) ? __uint_as_float(sr[j]) : -INFINITY;
+            sr[j] = __float_as_uint(v);
+            mx4[j & 3] = fmaxf(mx4[j & 3], v);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 64; j++) mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(sr[j]));
+        }
+      }
+      if (threadIdx.x == 0) FT_STAMP(3 + 6 * i);
+      const float m_tile = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
+      const bool grow = m_tile > m_run + FT_SLACK;   // also the first tile with a visible key: m_run is -inf
       float corr = 1.f;
-      if (i < n_tiles) {
-        const int k_base = (kt_lo + i) * FT_BN;
-        const bool need_mask = k_base + FT_BN - 1 > p_first || (window > 0 && k_base < p_last - window + 1);
-        if (threadIdx.x == 0) FT_STAMP(1 + 6 * i);
-        if (!hb_mbar_wait(&bar->s_full, i & 1, abort_flag)) break;
-        if (threadIdx.x == 0) FT_STAMP(2 + 6 * i);
-        hb_tc_fence_after();
-        // the row of S in two halves of 64 keys; a softmax warp is alone on its scheduler: four
-        // independent chains for the maximum and for the sum, and the mask only where one is needed
-        uint32_t sr[64];
-        const int hi_j = qp - k_base, lo_j = window > 0 ? qp - window - k_base : -1;  // key j of the tile is visible iff lo_j < j <= hi_j
-        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      if (grow) {
+        corr = hb_exp2(m_run - m_tile);   // 0 while nothing has been summed
+        m_run = m_tile;
+      }
+      const float sub = m_run == -INFINITY ? 0.f : m_run;
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      // the exponentials: keys 64-127 are still in the registers (masked), keys 0-63 are read again
 #pragma unroll
-        for (int hh = 0; hh < 2; hh++) {
-          hb_tmem_ld64_nowait(tmem_s + lane_base + hh * 64, sr);
+      for (int hh = 1; hh >= 0; hh--) {
+        if (hh == 0) {
+          hb_tmem_ld64_nowait(tmem_s + lane_base, sr);
           hb_tmem_ld_wait();
           hb_tmem_ld_fence64(sr);
+          hb_tc_fence_before();
+          hb_mbar_arrive(&bar->s_free);  // the last read of S: the scores of the next tile may overwrite it
           if (need_mask) {
 #pragma unroll
-            for (int j = 0; j < 64; j++) {
-              const float v = (j + hh * 64 <= hi_j && j + hh * 64 > lo_j) ? __uint_as_float(sr[j]) : -INFINITY;
-              sr[j] = __float_as_uint(v);
-              mx4[j & 3] = fmaxf(mx4[j & 3], v);
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 64; j++) mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(sr[j]));
+            for (int j = 0; j < 64; j++)
+              if (!(j <= hi_j && j > lo_j)) sr[j] = __float_as_uint(-INFINITY);
           }
         }
-        if (threadIdx.x == 0) FT_STAMP(3 + 6 * i);
-        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-        const float m_new = fmaxf(m_run, mx * scale_log2);
-        const float sub = m_new == -INFINITY ? 0.f : m_new;
-        corr = hb_exp2(m_run - sub);
-        m_run = m_new;
-        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-        // the exponentials: keys 64-127 are still in the registers (masked), keys 0-63 are read again
 #pragma unroll
-        for (int hh = 1; hh >= 0; hh--) {
-          if (hh == 0) {
-            hb_tmem_ld64_nowait(tmem_s + lane_base, sr);
-            hb_tmem_ld_wait();
-            hb_tmem_ld_fence64(sr);
-            hb_tc_fence_before();
-            hb_mbar_arrive(&bar->s_free);  // the last read of S: the scores of the next tile may overwrite it
-            if (need_mask) {
-#pragma unroll
-              for (int j = 0; j < 64; j++)
-                if (!(j <= hi_j && j > lo_j)) sr[j] = __float_as_uint(-INFINITY);
-            }
-          }
-#pragma unroll
-          for (int j = 0; j < 64; j += 2) {  // masked scores are -inf: 2^-inf = 0
-            const float p0 = hb_exp2(fmaf(__uint_as_float(sr[j]), scale_log2, -sub));
-            const float p1 = hb_exp2(fmaf(__uint_as_float(sr[j + 1]), scale_log2, -sub));
-            sum4[(j >> 1) & 3] += p0 + p1;
-            sr[j >> 1] = hb_pack_bf16(p0, p1);
-          }
-          if (hh == 1) {
-            if (threadIdx.x == 0) FT_STAMP(4 + 6 * i);
-            if (!hb_mbar_wait(&bar->p_free, (i & 1) ^ 1, abort_flag)) { ok = false; break; }
-          }
-          // 64 keys = eight 16-byte chunks of this row in K block hh of P
-#pragma unroll
-          for (int cc = 0; cc < 8; cc++) {
-            const uint32_t dst = hb_smem_u32(sP + hh * FT_TILE) + r * 128 + ((cc ^ (r & 7)) << 4);
-            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(sr[4 * cc]), "r"(sr[4 * cc + 1]),
-                         "r"(sr[4 * cc + 2]), "r"(sr[4 * cc + 3]) : "memory");
-          }
+        for (int j = 0; j < 64; j += 2) {  // masked scores are -inf: 2^-inf = 0
+          const float p0 = hb_exp2(fmaf(__uint_as_float(sr[j]), scale_log2, -sub));
+          const float p1 = hb_exp2(fmaf(__uint_as_float(sr[j + 1]), scale_log2, -sub));
+          sum4[(j >> 1) & 3] += p0 + p1;
+          sr[j >> 1] = hb_pack_bf16(p0, p1);
         }
-        if (!ok) break;
-        const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-        l_run = l_run * corr + sum;
-        hb_fence_proxy_async();
-        hb_mbar_arrive(&bar->p_full);
-        if (threadIdx.x == 0) FT_STAMP(5 + 6 * i);
+        if (hh == 1) {
+          if (threadIdx.x == 0) FT_STAMP(4 + 6 * i);
+          if (!__all_sync(0xffffffffu, hb_mbar_wait(&bar->p_free, (i & 1) ^ 1, abort_flag))) { ok = false; break; }
+        }
+        // 64 keys = eight 16-byte chunks of this row in K block hh of P
+#pragma unroll
+        for (int cc = 0; cc < 8; cc++) {
+          const uint32_t dst = hb_smem_u32(sP + hh * FT_TILE) + r * 128 + ((cc ^ (r & 7)) << 4);
+          asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(sr[4 * cc]), "r"(sr[4 * cc + 1]),
+                       "r"(sr[4 * cc + 2]), "r"(sr[4 * cc + 3]) : "memory");
+        }
       }
-      if (i > 0) {  // the output tile of the tile before: o = o * corr_{i-1} + O_{i-1}
-        const int j = i - 1, b = FT_B(j);
-        if (!hb_mbar_wait(&bar->o_full[b], FT_PH(j), abort_flag)) break;
-        if (threadIdx.x == 0) FT_STAMP(6 + 6 * i);
+      if (!ok) break;
+      l_run = l_run * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+      // a raised maximum: the rows of O so far, which the product of the tile before has to have finished writing
+      // (it is the only one that can still be running: the scores of this tile were committed after the one before it)
+      if (i > 0 && __any_sync(0xffffffffu, grow)) {
+        if (!__all_sync(0xffffffffu, hb_mbar_wait(&bar->o_full, (i - 1) & 1, abort_flag))) { ok = false; break; }
         hb_tc_fence_after();
 #pragma unroll
         for (int hf = 0; hf < NH; hf++) {
-          uint32_t orr[64];
-          hb_tmem_ld64_nowait(tmem_o + b * FT_D + hf * 64 + lane_base, orr);
+          hb_tmem_ld64_nowait(tmem_o + hf * 64 + lane_base, sr);
           hb_tmem_ld_wait();
-          hb_tmem_ld_fence64(orr);
-          if (hf == NH - 1) {
-            hb_tc_fence_before();
-            hb_mbar_arrive(&bar->o_free[b]);
-          }
+          hb_tmem_ld_fence64(sr);
 #pragma unroll
-          for (int d = 0; d < 64; d++) o[hf * 64 + d] = fmaf(o[hf * 64 + d], corr_prev, __uint_as_float(orr[d]));
+          for (int d = 0; d < 64; d++) sr[d] = __float_as_uint(__uint_as_float(sr[d]) * corr);
+          hb_tmem_st64(tmem_o + hf * 64 + lane_base, sr);
         }
+        hb_tmem_st_wait();
       }
-      corr_prev = corr;
-      if (i == n_tiles && r < rows_here) {
-        const float inv = 1.f / l_run;
-        __nv_bfloat16* dst = out + ((size_t)(row0 + r) * Hq + hq) * FT_D;
+      hb_tc_fence_before();
+      hb_fence_proxy_async();
+      hb_mbar_arrive(&bar->p_full);
+      if (threadIdx.x == 0) FT_STAMP(5 + 6 * i);
+    }
+    if (ok && __all_sync(0xffffffffu, hb_mbar_wait(&bar->o_full, (n_tiles - 1) & 1, abort_flag))) {
+      if (threadIdx.x == 0) FT_STAMP(6 + 6 * n_tiles);
+      hb_tc_fence_after();
+      const float inv = 1.f / l_run;
+      __nv_bfloat16* dst = out + ((size_t)(row0 + r) * Hq + hq) * FT_D;
 #pragma unroll
-        for (int d = 0; d < FT_D; d += 8) {
-          uint4 w;
-          w.x = hb_pack_bf16(o[d] * inv, o[d + 1] * inv); w.y = hb_pack_bf16(o[d + 2] * inv, o[d + 3] * inv);
-          w.z = hb_pack_bf16(o[d + 4] * inv, o[d + 5] * inv); w.w = hb_pack_bf16(o[d + 6] * inv, o[d + 7] * inv);
-          *(uint4*)(dst + d) = w;
+      for (int hf = 0; hf < NH; hf++) {
+        uint32_t orr[64];
+        hb_tmem_ld64_nowait(tmem_o + hf * 64 + lane_base, orr);
+        hb_tmem_ld_wait();
+        hb_tmem_ld_fence64(orr);
+        if (r < rows_here) {
+#pragma unroll
+          for (int d = 0; d < 64; d += 8) {
+            uint4 w;
+            w.x = hb_pack_bf16(__uint_as_float(orr[d]) * inv, __uint_as_float(orr[d + 1]) * inv);
+            w.y = hb_pack_bf16(__uint_as_float(orr[d + 2]) * inv, __uint_as_float(orr[d + 3]) * inv);
+            w.z = hb_pack_bf16(__uint_as_float(orr[d + 4]) * inv, __uint_as_float(orr[d + 5]) * inv);
+            w.w = hb_pack_bf16(__uint_as_float(orr[d + 6]) * inv, __uint_as_float(orr[d + 7]) * inv);
+            *(uint4*)(dst + hf * 64 + d) = w;
+          }
         }
       }
     }
@@ -336,7 +358,7 @@ __global__ void __launch_bounds__(192, FT_D == 64 ? 2 : 1) flash_prefill_tc_kern
   }
   if (warp == 5) {
     __syncwarp();
-    hb_tmem_dealloc(tmem_s, FT_D == 64 ? 256 : 512);
+    hb_tmem_dealloc(tmem_s, 256);
   }
 }
 
