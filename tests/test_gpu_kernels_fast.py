@@ -319,6 +319,51 @@ def test_flash_prefill_far_key_and_cutting(impl):
     assert torch.equal(tail, whole[cut:])
 
 
+@pytest.mark.parametrize("impl", FLASH)
+@pytest.mark.parametrize("D", [64, 128])
+def test_flash_prefill_running_maximum(impl, D):
+    """Scores that climb along the keys, so that the running maximum of a row keeps rising: by about 5
+    binary orders a key tile (a kernel that follows the maximum lazily lets several tiles pass before
+    it rescales the output), by about 20 (rescaled at every tile), falling (the first tile holds the
+    maximum and later tiles add almost nothing), and flat at a large magnitude."""
+    Hq, Hkv, ps, n = 4, 2, 16, 1100
+    if impl == "flash_prefill_tc" and not fast().flash_prefill_tc_supported(Hq, Hkv, D, ps):
+        pytest.skip("not a size of the tcgen05 kernel")
+    g = torch.Generator().manual_seed(51)
+    u = (torch.randint(0, 2, (D,), generator=g).float() * 2 - 1)            # +-1: |u|^2 = D
+    pos = torch.arange(n, dtype=torch.float32)
+    slope = 5.0 / 1.4427 / 128 / math.sqrt(D)                                 # q.k / sqrt(D) grows by 5 / log2(e) in 128 keys
+    k = torch.randn(n, Hkv, D, generator=g) * 0.05
+    k[:, 0] += u[None] * (pos * slope)[:, None]                              # kv head 0: climbing
+    k[:, 1] += u[None] * ((n - pos) * slope)[:, None]                        # kv head 1: falling
+    k = k.to(torch.bfloat16)
+    v = torch.randn(n, Hkv, D, generator=g).to(torch.bfloat16)
+    q = torch.randn(n, Hq, D, generator=g) * 0.05
+    q[:, 0] += u      # slow climb
+    q[:, 1] += 4 * u  # fast climb
+    q[:, 2] += u      # falling
+    q[:, 3] += 0      # flat and small; made large below
+    q[:, 3] *= 40
+    q = q.to(torch.bfloat16)
+    n_pages = -(-n // ps)
+    kc = torch.zeros(n_pages, Hkv, ps, D, dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    for lp in range(n_pages):
+        m = min(ps, n - lp * ps)
+        kc[lp, :, :m] = k[lp * ps:lp * ps + m].transpose(0, 1)
+        vc[lp, :, :m] = v[lp * ps:lp * ps + m].transpose(0, 1)
+    bt = torch.arange(n_pages, dtype=torch.int32).view(1, -1).to(DEV)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    out = torch.empty(n, Hq * D, dtype=torch.bfloat16, device=DEV)
+    getattr(fast(), impl)(q.reshape(n, Hq * D).to(DEV), kc.to(DEV), vc.to(DEV), bt, i32([0]), i32([n]), i32([0]), out, n,
+                          Hq, Hkv, D, ps, 0, 1 / math.sqrt(D))
+    sync_check()
+    ref = plain.attention_scores_softmax_values(q.float(), k.float(), v.float(), list(range(n)), list(range(n)))
+    got = out.float().cpu().reshape(n, Hq, D)
+    for h in range(Hq):
+        torch.testing.assert_close(got[:, h], ref[:, h], rtol=2e-2, atol=2e-2, msg=lambda m: f"head {h}: {m}")
+
+
 # ------------------------------------------------------------------------------------------
 # small products left as K slices, and the kernels that consume them
 # ------------------------------------------------------------------------------------------
