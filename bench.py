@@ -2,6 +2,7 @@
 """Decode and prefill throughput of hipinfer_b200 at Llama-3.2-1B shape with random weights.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L] [--impl ours|reference]
+                    [--shape 1b|3b|8b] [--prompt N] [--prefill-tokens N]      (further sizes; the default is 1b, 2048, 2048)
 
 One JSON line on stdout. `value` is decoded tokens a second at the given batch: K decode steps
 (forward from the paged cache + on-device sampling, the sampled tokens feeding the next step on
@@ -35,6 +36,29 @@ MODEL = dict(architectures=["LlamaForCausalLM"], vocab_size=128256, hidden_size=
                                original_max_position_embeddings=8192),
              tie_word_embeddings=True, hidden_act="silu")
 CONTEXT_LEN, PROMPT_LEN, PREFILL_TOKENS, PAGE = 4096, 2048, 2048, 16
+# further layer shapes of the same architecture (BASELINE configs[3] and [4]) for --shape; the default stays configs[2]
+SHAPES = {
+    "1b": dict(name="Llama-3.2-1B shape"),
+    "3b": dict(name="Llama-3.2-3B shape", hidden_size=3072, intermediate_size=8192, num_hidden_layers=28,
+               num_attention_heads=24, num_key_value_heads=8, head_dim=128, tie_word_embeddings=True),
+    "8b": dict(name="Llama-3.1-8B shape", hidden_size=4096, intermediate_size=14336, num_hidden_layers=32,
+               num_attention_heads=32, num_key_value_heads=8, head_dim=128, tie_word_embeddings=False, rope_factor=8.0),
+}
+SHAPE_NAME = SHAPES["1b"]["name"]
+
+
+def choose_shape(shape: str, prompt_len: int, prefill_tokens: int, steps: int) -> None:
+    """Other sizes than the default run: the layer shape, the length of the prompts behind the
+    decode steps and the length of the prefill. The context length grows with them."""
+    global SHAPE_NAME, CONTEXT_LEN, PROMPT_LEN, PREFILL_TOKENS
+    spec = dict(SHAPES[shape])
+    SHAPE_NAME = spec.pop("name")
+    factor = spec.pop("rope_factor", None)
+    MODEL.update(spec)
+    if factor is not None:
+        MODEL["rope_scaling"] = dict(MODEL["rope_scaling"], factor=factor)
+    PROMPT_LEN, PREFILL_TOKENS = prompt_len, prefill_tokens
+    CONTEXT_LEN = max(CONTEXT_LEN, -(-(max(prompt_len, prefill_tokens) + steps + 256) // 1024) * 1024)
 FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0)
 
 
@@ -103,15 +127,16 @@ def build_engine(layers: int, max_batch: int, total_steps: int):
 
     cfg = dict(MODEL, num_hidden_layers=layers)
     pages_per_seq = -(-(PROMPT_LEN + total_steps + 2 * max_batch + 4 * PAGE) // PAGE)
+    num_pages = max(max_batch * pages_per_seq, -(-PREFILL_TOKENS // PAGE)) + 8
     return Engine(config=cfg, random_weights=0, std=0.02, dtype="bfloat16", max_batch=max_batch, max_seq=CONTEXT_LEN,
-                  max_prefill=PREFILL_TOKENS, page_size=PAGE, num_pages=max_batch * pages_per_seq + 8)
+                  max_prefill=max(PREFILL_TOKENS, PROMPT_LEN), page_size=PAGE, num_pages=num_pages)
 
 
-def prompts(n, seed):
+def prompts(n, seed, length=None):
     import torch
 
     g = torch.Generator().manual_seed(seed)
-    return torch.randint(0, MODEL["vocab_size"], (n, PROMPT_LEN), generator=g).tolist()
+    return torch.randint(0, MODEL["vocab_size"], (n, length or PROMPT_LEN), generator=g).tolist()
 
 
 def decode_device(eng, batch: int, steps: int, warmup: int, sampler=None):
@@ -197,7 +222,7 @@ def prefill_device(eng, warmup: int, reps: int):
     from hipinfer_b200.kernels import fast
 
     runner = eng.runner
-    toks = prompts(1, 3)[0][:PREFILL_TOKENS]
+    toks = prompts(1, 3, PREFILL_TOKENS)[0]
     times = []
     for i in range(warmup + reps):
         torch.cuda.synchronize()
@@ -311,8 +336,11 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--layers", type=int, default=MODEL["num_hidden_layers"],
+    ap.add_argument("--layers", type=int, default=None,
                     help="fewer layers than the configuration has (both numbers are reported)")
+    ap.add_argument("--shape", default="1b", choices=sorted(SHAPES), help="layer sizes: 1b (the default run), 3b, 8b")
+    ap.add_argument("--prompt", type=int, default=PROMPT_LEN, help="tokens of each prompt behind the decode steps")
+    ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="tokens of the timed prefill step")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 decode points")
     ap.add_argument("--breakdown", action="store_true", help="print per-kernel times of a decode step and exit")
@@ -322,10 +350,14 @@ def main() -> int:
     if a.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {a.gpus} is not supported")
         return 2
-    if a.breakdown:
-        return breakdown(a.layers, a.batch)
     if a.warmup < 3:
         a.warmup = 3
+    if (a.shape, a.prompt, a.prefill_tokens) != ("1b", PROMPT_LEN, PREFILL_TOKENS):
+        choose_shape(a.shape, a.prompt, a.prefill_tokens, a.steps + a.warmup + 8)
+    if a.layers is None:
+        a.layers = MODEL["num_hidden_layers"]
+    if a.breakdown:
+        return breakdown(a.layers, a.batch)
     import torch
 
     pk = peaks()
@@ -345,13 +377,12 @@ def main() -> int:
     pre_frac = prefill_flops(a.layers) / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12)
     e2e_ms, h2d, d2h = decode_e2e(eng, a.batch, min(a.steps, 64), a.warmup)
     out = {
-        "metric": "decode tok/s at batch 8 (Llama-3.2-1B shape, 2,048-token prompts)" if a.batch == 8 else
-                  f"decode tok/s at batch {a.batch} (Llama-3.2-1B shape, 2,048-token prompts)",
+        "metric": f"decode tok/s at batch {a.batch} ({SHAPE_NAME}, {PROMPT_LEN:,}-token prompts)",
         "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": a.steps, "warmup": a.warmup,
         "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: uniform-random token ids, random N(0, 0.02) bf16 weights",
         "impl": "ours",
-        "config": {"model": "Llama-3.2-1B shape", "layers": a.layers, "layers_full": MODEL["num_hidden_layers"],
+        "config": {"model": SHAPE_NAME, "layers": a.layers, "layers_full": MODEL["num_hidden_layers"],
                    "hidden": MODEL["hidden_size"], "heads": MODEL["num_attention_heads"],
                    "kv_heads": MODEL["num_key_value_heads"], "head_dim": MODEL["head_dim"],
                    "intermediate": MODEL["intermediate_size"], "vocab": MODEL["vocab_size"], "global_batch": a.batch,
