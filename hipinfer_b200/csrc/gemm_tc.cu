@@ -11,11 +11,24 @@
 // Epilogues: store fp32 / store bf16 / add into the fp32 residual stream (the reference's
 // epilogue 1, src/kernels.cuh:881-889) / SwiGLU over gate and up columns interleaved in groups
 // of 16 (its epilogue 2, src/kernels.cuh:850-863). Replaces gemm_mma_kernel (src/kernels.cuh:585).
+// A fifth epilogue rotates a q/k/v product and writes q and the cache pages (EPI_ROPE_KV below).
 // Every mbarrier wait is bounded; a wait that runs out raises the status word and the kernel
 // drains and returns.
 #include "tc_common.cuh"
 
-enum { EPI_F32 = 0, EPI_BF16 = 1, EPI_ADD_F32 = 2, EPI_SWIGLU_BF16 = 3 };
+enum { EPI_F32 = 0, EPI_BF16 = 1, EPI_ADD_F32 = 2, EPI_SWIGLU_BF16 = 3, EPI_ROPE_KV = 4 };
+
+// EPI_ROPE_KV: the product is a q/k/v projection of heads of 64; the epilogue rotates the q and k heads (half-split
+// pairs (d, d + 32), the angles from a table of (cos, sin) per position) and writes q as bf16 [M, Hq * 64], k and v
+// into their pages of the cache; nothing goes to C. What rope_kv_vec_kernel does from an fp32 copy of the product,
+// product by product in the same fp32 operations (src/kernels.cuh:127-136, 1126-1150 rotate and store in one kernel too).
+struct RopeEpi {
+  const int* pos;         // [M] position of each row
+  const int* slot_map;    // [M] page * page_size + offset of each row's token in the cache, -1: not stored; or null
+  const float2* table;    // [positions][32] (cos, sin)
+  __nv_bfloat16 *q_out, *kc, *vc;
+  int Hq, Hkv, page_size;
+};
 
 constexpr int BM = 128, BK = 64;
 #ifndef HB_GEMM_PAIR
@@ -84,6 +97,40 @@ __device__ __forceinline__ void epilogue_store(const float* v, void* C, long ldc
   }
 }
 
+// One head of 64 columns of one row (x1: columns 0-31, x2: 32-63) of a q/k/v product: rotated if it is a q or k
+// head, then 128 bytes of bf16 to q_out or to the row's place in the cache. The products and sums are single fp32
+// operations in the order of rope_kv_vec_kernel, so both paths give the same bits.
+__device__ __forceinline__ void rope_head_store(float* x1, float* x2, int head, int row, bool live, const float2* cs,
+                                                int slot, const RopeEpi& rp) {
+  __nv_bfloat16* dst = nullptr;
+  if (head < rp.Hq) {
+    dst = rp.q_out + ((size_t)row * rp.Hq + head) * 64;
+  } else if (slot >= 0) {
+    const size_t page = slot / rp.page_size, off = slot % rp.page_size;
+    const bool is_k = head < rp.Hq + rp.Hkv;
+    dst = (is_k ? rp.kc : rp.vc) + ((page * rp.Hkv + (head - rp.Hq - (is_k ? 0 : rp.Hkv))) * rp.page_size + off) * 64;
+  }
+  if (!live || !dst) return;
+  if (head < rp.Hq + rp.Hkv) {
+#pragma unroll
+    for (int j = 0; j < 32; j += 2) {
+      const float4 c = *(const float4*)(cs + j);   // (cos, sin) of pairs j and j + 1
+      const float a0 = x1[j], b0 = x2[j], a1 = x1[j + 1], b1 = x2[j + 1];
+      x1[j] = __fsub_rn(__fmul_rn(a0, c.x), __fmul_rn(b0, c.y));
+      x2[j] = __fadd_rn(__fmul_rn(b0, c.x), __fmul_rn(a0, c.y));
+      x1[j + 1] = __fsub_rn(__fmul_rn(a1, c.z), __fmul_rn(b1, c.w));
+      x2[j + 1] = __fadd_rn(__fmul_rn(b1, c.z), __fmul_rn(a1, c.w));
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 4; j++) {
+    *(uint4*)(dst + 8 * j) = make_uint4(hb_pack_bf16(x1[8 * j], x1[8 * j + 1]), hb_pack_bf16(x1[8 * j + 2], x1[8 * j + 3]),
+                                        hb_pack_bf16(x1[8 * j + 4], x1[8 * j + 5]), hb_pack_bf16(x1[8 * j + 6], x1[8 * j + 7]));
+    *(uint4*)(dst + 32 + 8 * j) = make_uint4(hb_pack_bf16(x2[8 * j], x2[8 * j + 1]), hb_pack_bf16(x2[8 * j + 2], x2[8 * j + 3]),
+                                             hb_pack_bf16(x2[8 * j + 4], x2[8 * j + 5]), hb_pack_bf16(x2[8 * j + 6], x2[8 * j + 7]));
+  }
+}
+
 // 32 accumulator columns (chunk c of the tile at column n0) of 32 rows, one row a lane, through this warp's two
 // 4 KB boxes of swizzled shared memory and out by a TMA tensor store (or reduce). PER chunks fill one box of
 // 128-byte rows: 1 (fp32), 2 (bf16), 4 (SwiGLU: 16 outputs each). row0: the first of the warp's 32 rows in C.
@@ -142,7 +189,7 @@ template <int BN, int STAGES, int EPI, bool TS>
 __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                                                          const __grid_constant__ CUtensorMap map_w,
                                                          const __grid_constant__ CUtensorMap map_c, void* C, long ldc,
-                                                         int M, int N, int K, int* status) {
+                                                         int M, int N, int K, int* status, const RopeEpi rp) {
   using S = GemmSmem<BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -226,15 +273,29 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
       hb_tc_fence_after();
       const int row = m0 + warp * 32 + lane;
       const uint32_t t0 = tmem_base + ((uint32_t)(warp * 32) << 16) + buf * BN;
+      if constexpr (EPI == EPI_ROPE_KV) {
+        const bool live = row < M;
+        const float2* cs = rp.table + (size_t)(live ? rp.pos[row] : 0) * 32;
+        const int slot = live && rp.slot_map ? rp.slot_map[row] : -1;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; c++) {
-        float v[32];
-        hb_tmem_ld32(t0 + c * 32, v);
-        if (n0 + c * 32 >= N) continue;
-        if constexpr (TS) {
-          ts_chunk<EPI>(v, c, n0, N, m0 + warp * 32, smem + S::STAGING_OFFSET + warp * 8192, lane, &map_c);
-        } else {
-          epilogue_store<EPI>(v, C, ldc, row, n0 + c * 32, M, N);
+        for (int hd = 0; hd < BN / 64; hd++) {   // a head = two chunks of 32 columns
+          float x1[32], x2[32];
+          hb_tmem_ld32(t0 + hd * 64, x1);
+          hb_tmem_ld32(t0 + hd * 64 + 32, x2);
+          if (n0 + hd * 64 >= N) continue;
+          rope_head_store(x1, x2, (n0 >> 6) + hd, row, live, cs, slot, rp);
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; c++) {
+          float v[32];
+          hb_tmem_ld32(t0 + c * 32, v);
+          if (n0 + c * 32 >= N) continue;
+          if constexpr (TS) {
+            ts_chunk<EPI>(v, c, n0, N, m0 + warp * 32, smem + S::STAGING_OFFSET + warp * 8192, lane, &map_c);
+          } else {
+            epilogue_store<EPI>(v, C, ldc, row, n0 + c * 32, M, N);
+          }
         }
       }
       hb_tc_fence_before();
@@ -457,7 +518,7 @@ static int sm_count() {
 
 template <int BN, int STAGES, int EPI, bool TS>
 static int launch_gemm_tc_ts(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap& mc, void* C, long ldc, int M,
-                             int N, int K, int* status, cudaStream_t s) {
+                             int N, int K, int* status, cudaStream_t s, const RopeEpi& rp = RopeEpi()) {
   using S = GemmSmem<BN, STAGES>;
   constexpr int smem = TS ? S::TOTAL_TS : S::TOTAL;
   auto kern = gemm_tc_kernel<BN, STAGES, EPI, TS>;
@@ -469,7 +530,7 @@ static int launch_gemm_tc_ts(const CUtensorMap& ma, const CUtensorMap& mw, const
   }
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  cudaError_t e = hb_launch(kern, grid, 192, smem, s, ma, mw, mc, C, ldc, M, N, K, status);
+  cudaError_t e = hb_launch(kern, grid, 192, smem, s, ma, mw, mc, C, ldc, M, N, K, status, rp);
   if (e != cudaSuccess) HB_FAIL("hb_gemm_tc: %s", cudaGetErrorString(e));
   return 0;
 }
@@ -588,5 +649,32 @@ HB_EXPORT int hb_gemm_tc(const void* A, long lda, const void* W, long ldw, void*
                           : launch_gemm_tc<192, 4, EPI_ADD_F32>(ma, mw, C, ldc, M, N, K, status, s);
   if (r) return r;
   HB_CHECK_LAUNCH("hb_gemm_tc");
+  return 0;
+}
+
+// q/k/v projection with rotation and cache write in the epilogue (EPI_ROPE_KV): A [M, K] bf16, W [(Hq + 2 Hkv) * 64, K]
+// bf16 with the rows q heads, k heads, v heads; pos [M]; slot_map [M] or null (then only q is written); table
+// [positions][32] (cos, sin) fp32; q_out [M, Hq * 64] bf16; caches [pages, Hkv, page_size, 64] bf16. Heads of 64 only.
+HB_EXPORT int hb_gemm_tc_rope_kv(const void* A, long lda, const void* W, long ldw, int M, int K, const int* pos,
+                                 const int* slot_map, const void* table, void* q_out, void* kc, void* vc, int Hq, int Hkv,
+                                 int D, int page_size, int* status, cudaStream_t s) {
+  if (M <= 0) return 0;
+  if (D != 64) HB_FAIL("hb_gemm_tc_rope_kv: heads of %d (64 only)", D);
+  if (Hq <= 0 || Hkv <= 0 || page_size <= 0) HB_FAIL("hb_gemm_tc_rope_kv: %d/%d heads, pages of %d", Hq, Hkv, page_size);
+  if (K <= 0 || (K & 7)) HB_FAIL("hb_gemm_tc_rope_kv: K = %d must be a positive multiple of 8 (16-byte rows for TMA)", K);
+  if (!status || !pos || !table || !q_out) HB_FAIL("hb_gemm_tc_rope_kv: a null argument");
+  if (slot_map && (!kc || !vc)) HB_FAIL("hb_gemm_tc_rope_kv: a slot map without caches");
+  if (((uintptr_t)q_out | (uintptr_t)kc | (uintptr_t)vc | (uintptr_t)table) & 15) HB_FAIL("hb_gemm_tc_rope_kv: q, caches and table must be 16-byte aligned");
+  const int N = (Hq + 2 * Hkv) * 64;
+  CUtensorMap ma, mw, mc;
+  memset(&mc, 0, sizeof(mc));
+  if (hb_make_tensor_map_bf16(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM)) return -1;
+  if (hb_make_tensor_map_bf16(&mw, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, 192)) return -1;
+  RopeEpi rp;
+  rp.pos = pos; rp.slot_map = slot_map; rp.table = (const float2*)table;
+  rp.q_out = (__nv_bfloat16*)q_out; rp.kc = (__nv_bfloat16*)kc; rp.vc = (__nv_bfloat16*)vc;
+  rp.Hq = Hq; rp.Hkv = Hkv; rp.page_size = page_size;
+  if (launch_gemm_tc_ts<192, 4, EPI_ROPE_KV, false>(ma, mw, mc, nullptr, 0, M, N, K, status, s, rp)) return -1;
+  HB_CHECK_LAUNCH("hb_gemm_tc_rope_kv");
   return 0;
 }

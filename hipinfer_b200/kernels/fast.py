@@ -31,10 +31,11 @@ _SIGS = {
     "hb_flash_prefill_supported": [_i, _i, _i],
     "hb_flash_prefill_tc": [_p, _p, _p, _l, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p, _p],
     "hb_flash_prefill_tc_supported": [_i, _i, _i, _i],
+    "hb_gemm_tc_rope_kv": [_p, _l, _p, _l, _i, _i, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p, _p],
     "hb_attn_decode_supported": [_i, _i, _i],
 }
 _fns = {}
-_LAUNCHES = {"hb_gemm_stream_finish": 1, "hb_add_rmsnorm_slices": 1, "hb_rope_kv_slices": 1, "hb_gemm_tc": 1, "hb_gemm_skinny": 1, "hb_gemm_stream": 1, "hb_attn_decode": 1, "hb_flash_prefill": 1, "hb_flash_prefill_tc": 1}
+_LAUNCHES = {"hb_gemm_tc_rope_kv": 1, "hb_gemm_stream_finish": 1, "hb_add_rmsnorm_slices": 1, "hb_rope_kv_slices": 1, "hb_gemm_tc": 1, "hb_gemm_skinny": 1, "hb_gemm_stream": 1, "hb_attn_decode": 1, "hb_flash_prefill": 1, "hb_flash_prefill_tc": 1}
 _status = None
 
 EPI_F32, EPI_BF16, EPI_ADD_F32, EPI_SWIGLU_BF16, EPI_SLICES = 0, 1, 2, 3, 4
@@ -255,6 +256,28 @@ def linear(a, w, out, accumulate) -> bool:
     else:
         return False
     _gemm(a, w.t, out, epi)
+    return True
+
+
+ROPE_FUSED_OFF = os.environ.get("HIPINFER_B200_ROPE_FUSED", "1") == "0"   # "0": the projection and the rotation as two kernels
+
+
+def linear_rope_kv(a, w, positions, slot_map, table, q_out, k_cache, v_cache, n_heads, n_kv_heads, head_dim, rotary_dim,
+                   page_size) -> bool:
+    """The q/k/v projection of more than a few rows with the rotation and the cache write in its epilogue
+    (csrc/gemm_tc.cu, EPI_ROPE_KV); False where no kernel takes these sizes (heads of 64, rotated whole)."""
+    if (ROPE_FUSED_OFF or a.shape[0] <= SKINNY_MAX_ROWS or head_dim != 64 or rotary_dim != 64 or not _tc_ok(a, w.t)
+            or w.shape[0] != (n_heads + 2 * n_kv_heads) * 64 or q_out.dtype != torch.bfloat16 or not q_out.is_contiguous()
+            or table.dtype != torch.float32 or not table.is_contiguous()):
+        return False
+    if slot_map is not None and not (k_cache.dtype == torch.bfloat16 and k_cache.is_contiguous() and v_cache.is_contiguous()
+                                     and v_cache.dtype == torch.bfloat16):
+        return False
+    p = lambda t: None if t is None else t.data_ptr()
+    _call("hb_gemm_tc_rope_kv", a.data_ptr(), a.stride(0), w.t.data_ptr(), w.t.stride(0), a.shape[0], a.shape[1],
+          positions.data_ptr(), p(slot_map), table.data_ptr(), q_out.data_ptr(), p(k_cache) if slot_map is not None else None,
+          p(v_cache) if slot_map is not None else None, n_heads, n_kv_heads, head_dim, page_size, status_word().data_ptr(),
+          _stream())
     return True
 
 

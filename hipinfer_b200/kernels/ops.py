@@ -191,6 +191,20 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, slot_map: Optional
     return q_out
 
 
+def linear_rope_kv_write(a: torch.Tensor, w: "Weight", positions: torch.Tensor, slot_map: Optional[torch.Tensor],
+                         table: torch.Tensor, q_out: torch.Tensor, k_cache: Optional[torch.Tensor],
+                         v_cache: Optional[torch.Tensor], n_heads: int, n_kv_heads: int, head_dim: int, rotary_dim: int,
+                         page_size: int) -> bool:
+    """rope_kv_write of a @ w.T in one kernel, where one takes these sizes; False: nothing was done
+    (the caller projects, then rotates). The results are the same bits either way."""
+    from . import fast
+
+    if not a.is_cuda:
+        return False
+    return fast.linear_rope_kv(a, w, positions, slot_map, table, q_out, k_cache, v_cache, n_heads, n_kv_heads, head_dim,
+                               rotary_dim, page_size)
+
+
 ATTN_CHUNK = 256  # keys per split of the plain attention kernel: absolute positions, so batch-independent
 
 

@@ -58,10 +58,13 @@ class AttentionMixer(Mixer):
     def forward(self, xn, x, batch, cache, state):
         T = xn.shape[0]
         Hq, Hkv, D = self.n_heads, self.n_kv_heads, self.head_dim
-        qkv = torch.empty(T, (Hq + 2 * Hkv) * D, dtype=torch.float32, device=xn.device)
-        pending = ops.linear_deferred(xn, self.wqkv, qkv)      # a few rows: the rotation adds the product's slices
         q = torch.empty(T, Hq * D, dtype=self.ctx.dtype, device=xn.device)
         slot_map = batch.slot_maps[cache.group] if cache.write else None
+        fused = getattr(self.position, "project_rotate_and_store", None)    # many rows: the rotation in the product's epilogue
+        if fused is not None and fused(xn, self.wqkv, batch.positions, slot_map, q, cache.k, cache.v, Hq, Hkv):
+            return self._attend_and_project(q, x, batch, cache)
+        qkv = torch.empty(T, (Hq + 2 * Hkv) * D, dtype=torch.float32, device=xn.device)
+        pending = ops.linear_deferred(xn, self.wqkv, qkv)      # a few rows: the rotation adds the product's slices
         if pending is not None and not self.position.takes_pending:
             pending.finish()
             pending = None

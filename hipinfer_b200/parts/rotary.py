@@ -70,4 +70,13 @@ class RotaryEmbedding(Part):
                                  self.head_dim, self.rotary_dim, self.ctx.page_size, pending)
 
 
+    def project_rotate_and_store(self, xn, weight, positions, slot_map, q_out, k_cache, v_cache, n_heads, n_kv_heads) -> bool:
+        """rotate_and_store of xn @ weight.T as one kernel (the rotation in the product's epilogue)
+        where one exists for these sizes; False: nothing was done. A position part need not have this method."""
+        if not self.rotary_dim:
+            return False
+        return ops.linear_rope_kv_write(xn, weight, positions, slot_map, self.table, q_out, k_cache, v_cache, n_heads,
+                                        n_kv_heads, self.head_dim, self.rotary_dim, self.ctx.page_size)
+
+
 register_part("position", "rope", RotaryEmbedding)

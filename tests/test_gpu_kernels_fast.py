@@ -74,6 +74,43 @@ def test_gemm_tc_swiglu(M, I, K, tile_n):
     assert bool((out[M] == 7.0).all())
 
 
+@pytest.mark.parametrize("M,Hq,Hkv,K,ps,write", [(300, 5, 2, 256, 16, True), (65, 3, 1, 72, 8, True), (2048, 32, 8, 2048, 16, True),
+                                               (130, 4, 4, 128, 32, False)])
+def test_gemm_tc_rotation_and_cache_write_in_the_epilogue(M, Hq, Hkv, K, ps, write):
+    """The q/k/v projection with the rotation and the page writes in its epilogue against the same
+    product written out in fp32 and rotated by the kernel of its own: the same bits in q and in
+    the pages, pages of rows that are not stored (slot -1) and of other tokens untouched."""
+    from hipinfer_b200.kernels import ops
+
+    D = 64
+    N = (Hq + 2 * Hkv) * D
+    a, w = rnd(M, K, seed=61), ops.Weight(rnd(N, K, seed=62, scale=0.1))
+    g = torch.Generator().manual_seed(63)
+    n_pos = 4096
+    inv_freq = (10000.0 ** (-torch.arange(0, D, 2, dtype=torch.float64) / D)).float().to(DEV)
+    table = ops.rope_table(inv_freq, n_pos)
+    positions = torch.randint(0, n_pos, (M,), generator=g, dtype=torch.int32).to(DEV)
+    n_pages = -(-M // ps) + 4
+    slots = torch.randperm(n_pages * ps, generator=g)[:M].to(torch.int32)
+    slots[::7] = -1                                             # rows whose keys and values are not stored
+    slot_map = slots.to(DEV) if write else None
+    fill = lambda: torch.full((n_pages, Hkv, ps, D), 3.0, dtype=torch.bfloat16, device=DEV)
+    kc1, vc1, kc2, vc2 = fill(), fill(), fill(), fill()
+    q1 = torch.empty(M, Hq * D, dtype=torch.bfloat16, device=DEV)
+    q2 = torch.empty_like(q1)
+    assert fast().linear_rope_kv(a, w, positions, slot_map, table, q1, kc1, vc1, Hq, Hkv, D, D, ps)
+    qkv = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    fast().gemm_tc(a, w.t, qkv, fast().EPI_F32)
+    ops.rope_kv_write(qkv, positions, slot_map, table, q2, kc2, vc2, Hq, Hkv, D, D, ps)
+    sync_check()
+    assert torch.equal(q1, q2)
+    assert torch.equal(kc1, kc2) and torch.equal(vc1, vc2)
+    if write:
+        assert float((kc1 != 3.0).float().mean()) > 0.5          # most of the pages were written
+    else:
+        assert bool((kc1 == 3.0).all()) and bool((vc1 == 3.0).all())
+
+
 def test_gemm_tc_row_does_not_depend_on_batch():
     """The same row gives the same bits alone, in a small batch and deep inside a large one."""
     a, w = rnd(300, 256, seed=7), rnd(384, 256, seed=8, scale=0.1)
