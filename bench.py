@@ -248,8 +248,9 @@ def prefill_flops(layers: int) -> float:
     return linear + attention + 2.0 * V * H
 
 
-def breakdown(layers: int, batch: int) -> int:
-    """The time line of one graph-replayed decode step at `batch` from torch's CUPTI profiler (a
+def breakdown(layers: int, batch: int, prefill: bool = False) -> int:
+    """With prefill: the same for one prefill step of PREFILL_TOKENS tokens (not graph-replayed). Otherwise:
+    the time line of one graph-replayed decode step at `batch` from torch's CUPTI profiler (a
     table on stdout, not the JSON line). Kernels overlap (programmatic dependent launch: they start
     early and wait), so besides start and duration the table gives, for the kernels of one layer in
     the middle of the step, the time from the end of the kernel before to the kernel's own end: its
@@ -265,14 +266,22 @@ def breakdown(layers: int, batch: int) -> int:
 
     eng = build_engine(layers, max(batch, 2), 64)
     runner = eng.runner
-    ids = [("bd", i) for i in range(batch)]
-    first = [ops.sample(runner.step([StepEntry(rid, p, [PROMPT_LEN - 1])]), None, None, None)
-             for rid, p in zip(ids, prompts(batch, 1))]
-    tokens = torch.cat(first).contiguous()
-    entries = [StepEntry(rid, [0], [0]) for rid in ids]
+    if prefill:
+        toks, count = prompts(1, 3, PREFILL_TOKENS)[0], [0]
 
-    def one():
-        ops.sample(runner.step(entries, device_tokens=tokens), None, None, None, out=tokens)
+        def one():
+            count[0] += 1
+            runner.step([StepEntry(("bd", count[0]), toks, [PREFILL_TOKENS - 1])])
+            runner.end(("bd", count[0]))
+    else:
+        ids = [("bd", i) for i in range(batch)]
+        first = [ops.sample(runner.step([StepEntry(rid, p, [PROMPT_LEN - 1])]), None, None, None)
+                 for rid, p in zip(ids, prompts(batch, 1))]
+        tokens = torch.cat(first).contiguous()
+        entries = [StepEntry(rid, [0], [0]) for rid in ids]
+
+        def one():
+            ops.sample(runner.step(entries, device_tokens=tokens), None, None, None, out=tokens)
 
     for _ in range(5):
         one()
@@ -292,9 +301,10 @@ def breakdown(layers: int, batch: int) -> int:
     step = events[2 * per: 3 * per]                      # the third of the four steps
     t0 = step[0]["ts"]
     span = step[-1]["ts"] + step[-1]["dur"] - t0
-    print(f"decode step at batch {batch}, context {PROMPT_LEN}+: {per} kernels, {span:.1f} us from the first kernel's start "
-          f"to the last one's end")
-    per_layer = max(1, (per - 5) // max(1, layers))      # besides the layers: embedding, last norm, head, two of sampling
+    what = f"prefill step of {PREFILL_TOKENS} tokens" if prefill else f"decode step at batch {batch}, context {PROMPT_LEN}+"
+    print(f"{what}: {per} kernels, {span:.1f} us from the first kernel's start to the last one's end")
+    # besides the layers: embedding, last norm, head, and in a decode step two kernels of sampling
+    per_layer = max(1, (per - (3 if prefill else 5)) // max(1, layers))
     lo = min(len(step) - 1, 1 + per_layer * (layers // 2))
     print(f"kernels {lo}..{lo + per_layer - 1} (one layer): start, duration, end minus the end of the kernel before")
     prev_end = max(e["ts"] + e["dur"] for e in step[:lo]) if lo else t0
@@ -344,6 +354,7 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 decode points")
     ap.add_argument("--breakdown", action="store_true", help="print per-kernel times of a decode step and exit")
+    ap.add_argument("--prefill", action="store_true", help="with --breakdown: the prefill step instead of a decode step")
     a = ap.parse_args()
     if a.impl == "reference":
         return reference_arm(a)
@@ -357,7 +368,7 @@ def main() -> int:
     if a.layers is None:
         a.layers = MODEL["num_hidden_layers"]
     if a.breakdown:
-        return breakdown(a.layers, a.batch)
+        return breakdown(a.layers, a.batch, a.prefill)
     import torch
 
     pk = peaks()

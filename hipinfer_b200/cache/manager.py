@@ -192,10 +192,11 @@ class CacheManager:
     def can_append(self, request_id, n_tokens: int) -> bool:
         return all(n <= pool.free_count for n, pool in zip(self.pages_needed(request_id, n_tokens), self.pools))
 
-    def append(self, request_id, n_tokens: int) -> List[List[int]]:
+    def append(self, request_id, n_tokens: int, as_arrays: bool = False) -> List[List[int]]:
         """Make room for positions [length, length + n_tokens) in every group and advance the
         length. Returns, per group, the cache slot (page id * page_size + offset) of each new
-        position. Raises OutOfPages, leaving everything as it was, if a pool is too small."""
+        position (lists; with as_arrays the maps of longer portions stay the integer arrays they
+        were computed as). Raises OutOfPages, leaving everything as it was, if a pool is too small."""
         rc = self.get(request_id)
         need = self.pages_needed(request_id, n_tokens)
         for g, (n, pool) in enumerate(zip(need, self.pools)):
@@ -214,7 +215,8 @@ class CacheManager:
                 p = np.arange(rc.length, rc.length + n_tokens)
                 first = rc.length // ps
                 pages = np.asarray(table[first:(rc.length + n_tokens - 1) // ps + 1], dtype=np.int64)
-                slot_maps.append((pages[p // ps - first] * ps + p % ps).tolist())
+                m = pages[p // ps - first] * ps + p % ps
+                slot_maps.append(m if as_arrays else m.tolist())
         rc.length += n_tokens
         return slot_maps
 

@@ -55,12 +55,13 @@ def build_step_batch(entries: Sequence[StepEntry], ctx_lens: Sequence[int], stat
                      tables: Sequence[Sequence[Sequence[int]]], slot_maps: Sequence[Sequence[Sequence[int]]],
                      n_groups: int, device, table_widths: Optional[Sequence[int]] = None,
                      static: Optional[torch.Tensor] = None, max_pos: Optional[int] = None,
-                     token_map: Optional[Sequence[int]] = None) -> StepBatch:
+                     token_map: Optional[Sequence[int]] = None, token_arrays: Optional[Sequence] = None) -> StepBatch:
     """entries[r] runs at positions ctx_lens[r].. ; tables[r][g] is the request's block table of
     group g AFTER room was made for this step; slot_maps[r][g][i] the cache slot of its i-th token.
     `table_widths` fixes the block tables' widths and `static` is a device buffer to fill instead
     of a fresh one (both for steps replayed from a CUDA graph, whose addresses and launch
-    geometry must not change); `max_pos` then states the bound the geometry was made for."""
+    geometry must not change); `max_pos` then states the bound the geometry was made for.
+    `token_arrays`: the entries' tokens as integer arrays, where the caller has them already."""
     R = len(entries)
     q_len = [len(e.tokens) for e in entries]
     T = sum(q_len)
@@ -86,7 +87,9 @@ def build_step_batch(entries: Sequence[StepEntry], ctx_lens: Sequence[int], stat
         return o
 
     # (numpy, not comprehensions: a prompt portion has thousands of rows)
-    toks = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries]) if R else np.zeros(0, np.int64)
+    if token_arrays is None:
+        token_arrays = [np.asarray(e.tokens, dtype=np.int64) for e in entries]
+    toks = np.concatenate(token_arrays) if R else np.zeros(0, np.int64)
     pos = np.concatenate([np.arange(ctx_lens[r], ctx_lens[r] + q_len[r]) for r in range(R)]) if R else np.zeros(0, np.int64)
     rowreq = np.repeat(np.arange(R), q_len)
     o_tok, o_pos, o_rr = put(toks, T), put(pos, T), put(rowreq, T)

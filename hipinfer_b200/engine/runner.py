@@ -89,8 +89,9 @@ class ModelRunner:
     def length(self, request_id) -> int:
         return self.cache.get(request_id).length if self.cache.has_request(request_id) else 0
 
-    def check_entries(self, entries: Sequence[StepEntry]) -> None:
-        seen = set()
+    def check_entries(self, entries: Sequence[StepEntry]) -> list:
+        """Raises StepError for a batch that cannot run; returns the entries' tokens as int64 arrays."""
+        seen, arrays = set(), []
         for e in entries:
             if e.request_id in seen:
                 raise StepError(f"request {e.request_id!r} appears twice in one step")
@@ -98,16 +99,21 @@ class ModelRunner:
             n = len(e.tokens)
             if n < 1:
                 raise StepError(f"request {e.request_id!r}: an entry needs at least one token")
-            for t in e.tokens:
-                if not (0 <= int(t) < self.vocab_size):
-                    raise StepError(f"request {e.request_id!r}: token {t} is outside the vocabulary of "
-                                    f"{self.vocab_size}")
+            toks = np.asarray(e.tokens, dtype=np.int64)          # one pass, not a Python loop: a portion may have thousands
+            if toks.ndim != 1:
+                raise StepError(f"request {e.request_id!r}: tokens must be a flat sequence of ints")
+            bad = (toks < 0) | (toks >= self.vocab_size)
+            if bad.any():
+                raise StepError(f"request {e.request_id!r}: token {int(toks[bad][0])} is outside the vocabulary of "
+                                f"{self.vocab_size}")
             if self.length(e.request_id) + n > self.max_model_len:
                 raise StepError(f"request {e.request_id!r}: {self.length(e.request_id)} + {n} tokens exceed the "
                                 f"longest sequence of {self.max_model_len}")
             for w in e.want:
                 if not (0 <= int(w) < n):
                     raise StepError(f"request {e.request_id!r}: want {w} is outside its {n} tokens")
+            arrays.append(toks)
+        return arrays
 
     def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None,
              token_map: Optional[Sequence[int]] = None) -> torch.Tensor:
@@ -119,7 +125,7 @@ class ModelRunner:
         README.md:510-512). With `token_map` (one int per row) only rows with an entry >= 0 take
         their token from device_tokens[entry]; the others keep the value the entry gives."""
         entries = list(entries)
-        self.check_entries(entries)
+        token_arrays = self.check_entries(entries)
         if not entries:
             return torch.empty(0, self.vocab_size, dtype=torch.float32, device=self.device)
         # room for everything first, so that a failure leaves no request half advanced
@@ -144,13 +150,13 @@ class ModelRunner:
             rc = self.cache.get(e.request_id)
             ctx_lens.append(rc.length)
             slots.append(rc.state_slot)
-            slot_maps.append(self.cache.append(e.request_id, len(e.tokens)))
+            slot_maps.append(self.cache.append(e.request_id, len(e.tokens), as_arrays=True))
             tables.append(self._table_rows(rc))
         if self.cuda_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
             logits = self._graph_step(entries, ctx_lens, slots, tables, slot_maps, device_tokens, token_map)
         else:
             batch = build_step_batch(entries, ctx_lens, slots, tables, slot_maps, len(self.cache.groups), self.device,
-                                     token_map=token_map)
+                                     token_map=token_map, token_arrays=token_arrays)
             self._feed(batch.tokens, batch.token_map, device_tokens, token_map)
             logits = self.model.forward(batch, self.storage)
         for e in entries:
