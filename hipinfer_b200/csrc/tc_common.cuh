@@ -75,15 +75,6 @@ template <int N> __device__ __forceinline__ void hb_tma_store_wait_read() {
   asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
 }
 __device__ __forceinline__ void hb_tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-// The same tile brought into L2 only (nothing arrives in shared memory, nothing to wait for).
-__device__ __forceinline__ void hb_tma_prefetch_l2_2d(const CUtensorMap* m, int c0, int c1) {
-  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"((uint64_t)m), "r"(c0), "r"(c1)
-               : "memory");
-}
-// `bytes` (a multiple of 16) from a 16-byte aligned address brought into L2 only.
-__device__ __forceinline__ void hb_prefetch_l2_bulk(const void* p, uint32_t bytes) {
-  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
-}
 
 // ---------------------------------------------------------------- tensor memory
 __device__ __forceinline__ void hb_tmem_alloc(uint32_t* dst_smem, uint32_t ncols) {  // one whole warp
