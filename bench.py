@@ -11,7 +11,8 @@ prompts, so the steps run at contexts 2,048 + W .. 2,048 + W + K. `e2e` is the s
 `Engine.step()` (scheduler, host tokens in and out). `prefill` is one 2,048-token prompt in one
 step. `roofline` divides the bytes a decode step has to read (every weight it uses once, and the
 cache of the live requests) by its time. Peaks come from MEASURED_PEAKS.json beside this file,
-else from the fallback figures. The reference measures the same quantities in
+else from the fallback figures. The batch-1 and batch-64 points are the faster of two runs of 64
+steps each. The reference measures the same quantities in
 scripts/bench.py:384-449 (decode over many replayed steps, floor = weight + cache bytes / peak).
 """
 from __future__ import annotations
