@@ -33,6 +33,26 @@ def test_pages_and_block_tables():
     cm.check()
 
 
+def test_slot_maps_as_arrays_are_the_same_maps():
+    """A long portion's slot maps kept as integer arrays (what the runner asks for) hold the same
+    slots as the lists, also when the portion starts inside a page and pages are not consecutive."""
+    import numpy as np
+
+    def run(as_arrays):
+        cm = CacheManager([FULL], page_size=16, num_pages=40, num_state_slots=3)
+        out = []
+        for rid in ("a", "b"):
+            cm.add_request(rid)
+        for rid, n in (("a", 5), ("b", 21), ("a", 150), ("b", 3), ("a", 40)):
+            (m,) = cm.append(rid, n, as_arrays=as_arrays)
+            out.append(np.asarray(m, dtype=np.int64))
+        cm.check()
+        return out
+
+    for got, want in zip(run(True), run(False)):
+        assert got.dtype == np.int64 and got.tolist() == want.tolist()
+
+
 def test_out_of_pages_changes_nothing_and_misuse_raises():
     cm = CacheManager([FULL], 16, 2, 2)
     cm.add_request("a")
