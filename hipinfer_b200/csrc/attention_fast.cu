@@ -104,7 +104,12 @@ HB_EXPORT int hb_ad_stamps(unsigned long long* out) {
 // of the warp that will use it and awaited on that warp's own mbarrier (bounded). The copy engine
 // keeps far more bytes in flight than 16-byte loads from 128 threads can: this is the kernel for
 // whole pages (no window, page size 8 to 64); the other one takes the rest.
-template <int D, int G, bool TMA>
+//
+// RW (TMA only): rows of shared memory a warp has for its 64 keys. 64: the whole chunk lies in shared memory. 32
+// (head_dim 128): a warp walks its keys in two passes through 32 rows, asking for the second half when it is done
+// with the first: a block holds 64 KB instead of 128 KB of keys and values and three blocks share an SM instead
+// of one, which keeps more bytes in flight; the warps' partial results then lie over the keys (after a barrier).
+template <int D, int G, bool TMA, int RW>
 __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
     const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, int* __restrict__ status,
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc,
@@ -115,9 +120,12 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
   constexpr int CH = D / 8, KS = D / 16, NT_O = D / 8, WK = 64;  // WK: keys per warp pass
   extern __shared__ __align__(128) uint8_t smem_dyn[];
   uint8_t* smem_raw = TMA ? (uint8_t*)(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023) : smem_dyn;   // the swizzle wants 1 KB
-  const uint32_t sK = hb_smem_u32(smem_raw), sV = sK + chunk * D * 2, sQ = sV + chunk * D * 2;
-  const uint32_t hs = (uint32_t)chunk * 128;                            // bytes between the 64-column halves of a TMA tile
-  float* red_o = (float*)(smem_raw + 2 * chunk * D * 2 + 16 * D * 2);  // [warps][G][D]
+  static_assert(RW == WK || (TMA && RW == 32), "a warp's rows: all 64, or 32 with TMA");
+  constexpr int NSUB = WK / RW;                                         // passes of a warp through its rows
+  const int tile_rows = RW == WK ? chunk : AD_WARPS * RW;               // key rows of shared memory
+  const uint32_t sK = hb_smem_u32(smem_raw), sV = sK + tile_rows * D * 2, sQ = sV + tile_rows * D * 2;
+  const uint32_t hs = (uint32_t)tile_rows * 128;                        // bytes between the 64-column halves of a TMA tile
+  float* red_o = RW == WK ? (float*)(smem_raw + 2 * tile_rows * D * 2 + 16 * D * 2) : (float*)smem_raw;  // [warps][G][D]
   float* red_ml = red_o + AD_WARPS * G * D;                             // [warps][G][2]
   __shared__ int is_last;
   __shared__ __align__(8) uint64_t bars[AD_WARPS];
@@ -156,22 +164,25 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
       hb_fence_barrier_init();
     }
     __syncthreads();
-    const int r_w = warp * WK, page_bytes = page_size * D * 2 * 2;   // a page's keys and values of one kv head
-    const int pages_w = r_w < nk ? min(WK / page_size, (nk - r_w + page_size - 1) / page_size) : 0;
+    // warp w's keys are 64 w .. 64 w + 63 of the chunk; its rows of shared memory RW w .. RW w + RW - 1 hold the
+    // first RW of them now (all of them when RW is 64)
+    const int r_w = warp * WK, rb = warp * RW, page_bytes = page_size * D * 2 * 2;   // a page's keys and values of one kv head
+    const int pages_w = r_w < nk ? min(RW / page_size, (nk - r_w + page_size - 1) / page_size) : 0;
     const int old_w = min(pages_w, max(0, n_old - r_w) / page_size);  // pages wholly from earlier steps
     const int page0 = (k0 + r_w) / page_size;
     if (pages_w > 0) {
-      // rows of this warp beyond its last page are never written: the values there must be finite (they meet P = 0)
-      for (int i = (r_w + pages_w * page_size) * CH + lane; i < (r_w + WK) * CH; i += 32)
+      // rows of this warp beyond its last page are never written: the values there must be finite (they meet P = 0;
+      // in a second pass they are values of the first)
+      for (int i = (rb + pages_w * page_size) * CH + lane; i < (rb + RW) * CH; i += 32)
         asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(sV + ad_off<D, true>(i / CH, i % CH, hs)), "r"(0u) : "memory");
       if (lane == 0) {
         hb_mbar_expect_tx(&bars[warp], (uint32_t)(old_w * page_bytes));
         for (int j = 0; j < old_w; j++) {
-          const int row = (__ldg(table + page0 + j) * Hkv + h) * page_size, dst = (r_w + j * page_size) * 128;
+          const int row = (__ldg(table + page0 + j) * Hkv + h) * page_size, dst = (rb + j * page_size) * 128;
 #pragma unroll
           for (int hf = 0; hf < D / 64; hf++) {
             hb_tma_load_2d(smem_raw + hf * hs + dst, &map_k, &bars[warp], hf * 64, row);
-            hb_tma_load_2d(smem_raw + chunk * D * 2 + hf * hs + dst, &map_v, &bars[warp], hf * 64, row);
+            hb_tma_load_2d(smem_raw + tile_rows * D * 2 + hf * hs + dst, &map_v, &bars[warp], hf * 64, row);
           }
         }
       }
@@ -183,11 +194,11 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
     if (pages_w > 0 && lane == 0) {   // the pages that hold this step's keys
       hb_mbar_expect_tx(&bars[warp], (uint32_t)((pages_w - old_w) * page_bytes));
       for (int j = old_w; j < pages_w; j++) {
-        const int row = (__ldg(table + page0 + j) * Hkv + h) * page_size, dst = (r_w + j * page_size) * 128;
+        const int row = (__ldg(table + page0 + j) * Hkv + h) * page_size, dst = (rb + j * page_size) * 128;
 #pragma unroll
         for (int hf = 0; hf < D / 64; hf++) {
           hb_tma_load_2d(smem_raw + hf * hs + dst, &map_k, &bars[warp], hf * 64, row);
-          hb_tma_load_2d(smem_raw + chunk * D * 2 + hf * hs + dst, &map_v, &bars[warp], hf * 64, row);
+          hb_tma_load_2d(smem_raw + tile_rows * D * 2 + hf * hs + dst, &map_v, &bars[warp], hf * 64, row);
         }
       }
     }
@@ -219,6 +230,7 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
     if (warp * WK < nk) loaded = hb_mbar_wait(&bars[warp], 0, &abort_flag);
     if (!loaded && lane == 0) atomicExch(status, 1);   // the result is not valid; the host raises
   }
+  const int* table_w = table;   // (the loop below asks for a warp's second half itself)
 #if HB_AD_LATE_TRIGGER
   // the kernels behind this one start (and ask for their weights) only when every block here
   // has its keys and values: until then the memory system serves the attention alone
@@ -237,18 +249,46 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
 #pragma unroll
     for (int kk = 0; kk < KS; kk++) hb_ldmatrix_x4(qf[kk], sQ + ad_swz<D>((mi & 1) * 8 + r, kk * 2 + (mi >> 1)));
   }
-  for (int kb = warp * WK; kb < nk; kb += AD_WARPS * WK) {
-    float sc[8][4];
+  for (int pass = 0;; pass++) {
+    // keys kb .. kb + RW - 1 of the chunk, in rows rb .. of shared memory
+    const int kb = TMA ? warp * WK + pass * RW : warp * WK + pass * AD_WARPS * WK;
+    if (kb >= nk || (TMA && pass >= NSUB)) break;
+    const int rb = TMA ? warp * RW : kb;
+    if constexpr (TMA && NSUB > 1) {
+      if (pass > 0) {   // the second half of the warp's keys goes where the first was: every lane is done reading it
+        __syncwarp();
+        const int pages = min(RW / page_size, (nk - kb + page_size - 1) / page_size), page0 = (k0 + kb) / page_size;
+        if (lane == 0) {
+          hb_fence_proxy_async();
+          hb_mbar_expect_tx(&bars[warp], (uint32_t)(pages * page_size * D * 2 * 2));
+          hb_mbar_arrive(&bars[warp]);   // the barrier counts two arrivals a phase
+          for (int j = 0; j < pages; j++) {
+            const int row = (__ldg(table_w + page0 + j) * Hkv + h) * page_size, dst = (rb + j * page_size) * 128;
 #pragma unroll
-    for (int i = 0; i < 8; i++) sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.f;
+            for (int hf = 0; hf < D / 64; hf++) {
+              hb_tma_load_2d(smem_raw + hf * hs + dst, &map_k, &bars[warp], hf * 64, row);
+              hb_tma_load_2d(smem_raw + tile_rows * D * 2 + hf * hs + dst, &map_v, &bars[warp], hf * 64, row);
+            }
+          }
+        }
+        if (loaded) loaded = hb_mbar_wait(&bars[warp], pass & 1, &abort_flag);
+        if (!loaded) {
+          if (lane == 0) atomicExch(status, 1);
+          break;
+        }
+      }
+    }
+    float sc[RW / 8][4];
+#pragma unroll
+    for (int i = 0; i < RW / 8; i++) sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.f;
     {
       const int mi = lane >> 3, r = lane & 7;
 #pragma unroll
       for (int kk = 0; kk < KS; kk++) {
 #pragma unroll
-        for (int np = 0; np < 4; np++) {
+        for (int np = 0; np < RW / 16; np++) {
           uint32_t b[4];
-          hb_ldmatrix_x4(b, sK + ad_off<D, TMA>(kb + np * 16 + (mi >> 1) * 8 + r, kk * 2 + (mi & 1), hs));
+          hb_ldmatrix_x4(b, sK + ad_off<D, TMA>(rb + np * 16 + (mi >> 1) * 8 + r, kk * 2 + (mi & 1), hs));
           hb_mma_16816(sc[2 * np], qf[kk], b);
           hb_mma_16816(sc[2 * np + 1], qf[kk], b + 2);
         }
@@ -256,7 +296,7 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
     }
     float mx = -INFINITY;
 #pragma unroll
-    for (int i = 0; i < 8; i++)
+    for (int i = 0; i < RW / 8; i++)
 #pragma unroll
       for (int e = 0; e < 2; e++) {
         if (kb + i * 8 + 2 * tq + e >= nk) sc[i][e] = -INFINITY;
@@ -268,9 +308,9 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
     const float corr = hb_exp2(m_run - mn);
     m_run = mn;
     float sum = 0.f;
-    uint32_t pf[4][4];
+    uint32_t pf[RW / 16][4];
 #pragma unroll
-    for (int i = 0; i < 8; i++) {
+    for (int i = 0; i < RW / 8; i++) {
       const float p0 = hb_exp2(sc[i][0] * scale_log2 - mn), p1 = hb_exp2(sc[i][1] * scale_log2 - mn);
       sum += p0 + p1;
       pf[i >> 1][(i & 1) * 2] = hb_pack_bf16(p0, p1);
@@ -282,11 +322,11 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
     {
       const int mi = lane >> 3, r = lane & 7;
 #pragma unroll
-      for (int j2 = 0; j2 < 4; j2++) {
+      for (int j2 = 0; j2 < RW / 16; j2++) {
 #pragma unroll
         for (int cp = 0; cp < NT_O / 2; cp++) {
           uint32_t b[4];
-          hb_ldmatrix_x4_trans(b, sV + ad_off<D, TMA>(kb + j2 * 16 + (mi & 1) * 8 + r, cp * 2 + (mi >> 1), hs));
+          hb_ldmatrix_x4_trans(b, sV + ad_off<D, TMA>(rb + j2 * 16 + (mi & 1) * 8 + r, cp * 2 + (mi >> 1), hs));
           hb_mma_16816(o[2 * cp], pf[j2], b);
           hb_mma_16816(o[2 * cp + 1], pf[j2], b + 2);
         }
@@ -295,6 +335,7 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
   }
   l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
   l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+  if constexpr (RW != WK) __syncthreads();   // the partial results lie over the keys: every warp is done with them
   if (g < G) {
 #pragma unroll
     for (int i = 0; i < NT_O; i++) {
@@ -401,7 +442,7 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
   HB_TL_MARK(0, 3);
 }
 
-template <int D, bool TMA>
+template <int D, bool TMA, int RW>
 static int launch_decode(int G, dim3 grid, size_t smem, cudaStream_t st, const CUtensorMap& mk, const CUtensorMap& mv,
                          int* status, const __nv_bfloat16* q, const __nv_bfloat16* kc, const __nv_bfloat16* vc,
                          const int* bt, int bt_stride, const int* row_req, const int* pos, __nv_bfloat16* out, float* pa,
@@ -412,11 +453,11 @@ static int launch_decode(int G, dim3 grid, size_t smem, cudaStream_t st, const C
     {                                                                                                               \
       static bool configured = false;                                                                               \
       if (!configured) {                                                                                            \
-        cudaFuncSetAttribute(attn_decode_kernel<D, GG, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
+        cudaFuncSetAttribute(attn_decode_kernel<D, GG, TMA, RW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
         configured = true;                                                                                          \
       }                                                                                                             \
     }                                                                                                               \
-    hb_launch(attn_decode_kernel<D, GG, TMA>, grid, AD_THREADS, smem, st, mk, mv, status, q, kc, vc, bt, bt_stride,  \
+    hb_launch(attn_decode_kernel<D, GG, TMA, RW>, grid, AD_THREADS, smem, st, mk, mv, status, q, kc, vc, bt, bt_stride,  \
               row_req, pos, out, pa, pm, Hq, Hkv, page_size, window, scale, chunk, S, q_len, row_limit, ctx_len,    \
               counters);                                                                                            \
     return 0;
@@ -454,8 +495,12 @@ HB_EXPORT int hb_attn_decode(const void* q, const void* kc, const void* vc, long
   const long cache_rows = n_pages * Hkv * page_size;
   const bool tma = HB_AD_TMA && status && n_pages > 0 && window == 0 && chunk == AD_WARPS * 64 && page_size % 8 == 0 &&
                    page_size <= 64 && 64 % page_size == 0 && cache_rows < (1L << 31) && !(((uintptr_t)kc | (uintptr_t)vc) & 15);
-  const size_t smem = 2 * (size_t)chunk * D * 2 + 16 * (size_t)D * 2 + AD_WARPS * (size_t)G * (D + 2) * sizeof(float) +
-                      (tma ? 1024 : 0);
+  // head_dim 128 by TMA with pages of at most 32 tokens: a warp's 64 keys in two passes through 32 rows (64 KB of
+  // keys and values a block, the warps' partial results over them), three blocks an SM instead of one
+  const bool halves = tma && D == 128 && page_size <= 32;
+  const size_t smem = halves ? 2 * (size_t)(AD_WARPS * 32) * D * 2 + 16 * (size_t)D * 2 + 1024
+                             : 2 * (size_t)chunk * D * 2 + 16 * (size_t)D * 2 + AD_WARPS * (size_t)G * (D + 2) * sizeof(float) +
+                                   (tma ? 1024 : 0);
   if (smem > 200 * 1024) HB_FAIL("hb_attn_decode: %zu bytes of shared memory (chunk %d, head_dim %d)", smem, chunk, D);
   float* pa = workspace;
   float* pm = workspace ? workspace + (size_t)T * Hq * S * D : nullptr;
@@ -476,8 +521,9 @@ HB_EXPORT int hb_attn_decode(const void* q, const void* kc, const void* vc, long
   int r = 1;
 #define HB_AD_ARGS G, grid, smem, st, mk, mv, status, qq, kk, vv, bt, bt_stride, row_req, pos, (__nv_bfloat16*)out, pa, pm, Hq, Hkv, \
                    page_size, window, sl2, chunk, S, q_len, row_limit, ctx_len, counters
-  if (D == 64) r = tma ? launch_decode<64, true>(HB_AD_ARGS) : launch_decode<64, false>(HB_AD_ARGS);
-  else if (D == 128) r = tma ? launch_decode<128, true>(HB_AD_ARGS) : launch_decode<128, false>(HB_AD_ARGS);
+  if (D == 64) r = tma ? launch_decode<64, true, 64>(HB_AD_ARGS) : launch_decode<64, false, 64>(HB_AD_ARGS);
+  else if (halves) r = launch_decode<128, true, 32>(HB_AD_ARGS);
+  else if (D == 128) r = tma ? launch_decode<128, true, 64>(HB_AD_ARGS) : launch_decode<128, false, 64>(HB_AD_ARGS);
 #undef HB_AD_ARGS
   if (r) HB_FAIL("hb_attn_decode: no kernel for group %d", G);
   HB_CHECK_LAUNCH("hb_attn_decode");

@@ -214,7 +214,8 @@ from test_gpu_kernels_plain import _paged_setup
 
 
 @pytest.mark.parametrize("Hq,Hkv,D,ps,window", [(8, 2, 64, 16, 0), (3, 1, 128, 8, 0), (10, 2, 128, 16, 0), (8, 8, 64, 32, 0),
-                                                (8, 1, 64, 16, 0), (6, 2, 64, 16, 40), (4, 2, 64, 16, 300), (7, 1, 64, 16, 0)])
+                                                (8, 1, 64, 16, 0), (6, 2, 64, 16, 40), (4, 2, 64, 16, 300), (7, 1, 64, 16, 0),
+                                                (4, 1, 128, 32, 0), (4, 2, 128, 64, 0), (8, 1, 128, 16, 0)])
 def test_attention_decode(Hq, Hkv, D, ps, window):
     lens = [700, 37, 1, 300]
     kc, vc, bt, ks, vs = _paged_setup(lens, Hkv, D, ps, torch.bfloat16, 21)
@@ -243,9 +244,10 @@ def test_attention_decode(Hq, Hkv, D, ps, window):
         torch.testing.assert_close(got[t:t + 1], ref, rtol=1e-2, atol=1e-2, msg=lambda m: f"row {t} {rows[t]}: {m}")
 
 
-def test_attention_decode_long_context_many_chunks():
+@pytest.mark.parametrize("D", [64, 128])
+def test_attention_decode_long_context_many_chunks(D):
     """4,500 keys: 18 chunks of 256, more than the merge keeps in registers at once (its other path)."""
-    Hq, Hkv, D, ps = 4, 1, 64, 16
+    Hq, Hkv, ps = 4, 1, 16
     kc, vc, bt, ks, vs = _paged_setup([4500, 300], Hkv, D, ps, torch.bfloat16, 25)
     rows = [(0, 4499), (1, 299), (0, 4096), (0, 4095)]
     q = rnd(len(rows), Hq * D, seed=26)
