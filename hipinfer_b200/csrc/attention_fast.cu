@@ -109,7 +109,12 @@ HB_EXPORT int hb_ad_stamps(unsigned long long* out) {
 // (head_dim 128): a warp walks its keys in two passes through 32 rows, asking for the second half when it is done
 // with the first: a block holds 64 KB instead of 128 KB of keys and values and three blocks share an SM instead
 // of one, which keeps more bytes in flight; the warps' partial results then lie over the keys (after a barrier).
-template <int D, int G, bool TMA, int RW>
+// KW (TMA only): keys of the chunk a warp owns (chunk / 4): 64, or 128 (head_dim 64: chunks of 512 keys, two passes
+// through 64 rows: half as many blocks and partial results, and a step of 8 requests fits the SMs at once).
+// SR (TMA only): rows of shared memory a warp has: RW (it asks for the keys of a pass when it is done with the pass
+// before) or KW (all its keys are asked for at the start: 128 KB a block, for launches of so few blocks that every one
+// has an SM of its own; the passes and their arithmetic are the same).
+template <int D, int G, bool TMA, int RW, int KW, int SR>
 __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
     const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, int* __restrict__ status,
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc,
@@ -120,12 +125,13 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
   constexpr int CH = D / 8, KS = D / 16, NT_O = D / 8, WK = 64;  // WK: keys per warp pass
   extern __shared__ __align__(128) uint8_t smem_dyn[];
   uint8_t* smem_raw = TMA ? (uint8_t*)(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023) : smem_dyn;   // the swizzle wants 1 KB
-  static_assert(RW == WK || (TMA && RW == 32), "a warp's rows: all 64, or 32 with TMA");
-  constexpr int NSUB = WK / RW;                                         // passes of a warp through its rows
-  const int tile_rows = RW == WK ? chunk : AD_WARPS * RW;               // key rows of shared memory
+  static_assert((RW == WK && KW == WK) || (TMA && (RW == 32 || RW == 64) && KW % RW == 0), "a warp's keys and rows");
+  static_assert(SR == RW || SR == KW, "a warp's rows of shared memory: one pass or all its keys");
+  constexpr int NSUB = KW / RW;                                         // passes of a warp over its keys
+  const int tile_rows = TMA ? AD_WARPS * SR : chunk;                    // key rows of shared memory
   const uint32_t sK = hb_smem_u32(smem_raw), sV = sK + tile_rows * D * 2, sQ = sV + tile_rows * D * 2;
   const uint32_t hs = (uint32_t)tile_rows * 128;                        // bytes between the 64-column halves of a TMA tile
-  float* red_o = RW == WK ? (float*)(smem_raw + 2 * tile_rows * D * 2 + 16 * D * 2) : (float*)smem_raw;  // [warps][G][D]
+  float* red_o = NSUB == 1 ? (float*)(smem_raw + 2 * tile_rows * D * 2 + 16 * D * 2) : (float*)smem_raw;  // [warps][G][D]
   float* red_ml = red_o + AD_WARPS * G * D;                             // [warps][G][2]
   __shared__ int is_last;
   __shared__ __align__(8) uint64_t bars[AD_WARPS];
@@ -164,16 +170,16 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
       hb_fence_barrier_init();
     }
     __syncthreads();
-    // warp w's keys are 64 w .. 64 w + 63 of the chunk; its rows of shared memory RW w .. RW w + RW - 1 hold the
-    // first RW of them now (all of them when RW is 64)
-    const int r_w = warp * WK, rb = warp * RW, page_bytes = page_size * D * 2 * 2;   // a page's keys and values of one kv head
-    const int pages_w = r_w < nk ? min(RW / page_size, (nk - r_w + page_size - 1) / page_size) : 0;
+    // warp w's keys are KW w .. KW w + KW - 1 of the chunk; its rows of shared memory SR w .. SR w + SR - 1 hold the
+    // first SR of them now
+    const int r_w = warp * KW, rb = warp * SR, page_bytes = page_size * D * 2 * 2;   // a page's keys and values of one kv head
+    const int pages_w = r_w < nk ? min(SR / page_size, (nk - r_w + page_size - 1) / page_size) : 0;
     const int old_w = min(pages_w, max(0, n_old - r_w) / page_size);  // pages wholly from earlier steps
     const int page0 = (k0 + r_w) / page_size;
     if (pages_w > 0) {
       // rows of this warp beyond its last page are never written: the values there must be finite (they meet P = 0;
       // in a second pass they are values of the first)
-      for (int i = (rb + pages_w * page_size) * CH + lane; i < (rb + RW) * CH; i += 32)
+      for (int i = (rb + pages_w * page_size) * CH + lane; i < (rb + SR) * CH; i += 32)
         asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(sV + ad_off<D, true>(i / CH, i % CH, hs)), "r"(0u) : "memory");
       if (lane == 0) {
         hb_mbar_expect_tx(&bars[warp], (uint32_t)(old_w * page_bytes));
@@ -227,7 +233,7 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
   if constexpr (!TMA) hb_cp_async_wait<0>();
   __syncthreads();
   if constexpr (TMA) {
-    if (warp * WK < nk) loaded = hb_mbar_wait(&bars[warp], 0, &abort_flag);
+    if (warp * KW < nk) loaded = hb_mbar_wait(&bars[warp], 0, &abort_flag);
     if (!loaded && lane == 0) atomicExch(status, 1);   // the result is not valid; the host raises
   }
   const int* table_w = table;   // (the loop below asks for a warp's second half itself)
@@ -251,10 +257,10 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
   }
   for (int pass = 0;; pass++) {
     // keys kb .. kb + RW - 1 of the chunk, in rows rb .. of shared memory
-    const int kb = TMA ? warp * WK + pass * RW : warp * WK + pass * AD_WARPS * WK;
+    const int kb = TMA ? warp * KW + pass * RW : warp * WK + pass * AD_WARPS * WK;
     if (kb >= nk || (TMA && pass >= NSUB)) break;
-    const int rb = TMA ? warp * RW : kb;
-    if constexpr (TMA && NSUB > 1) {
+    const int rb = TMA ? warp * SR + (SR == RW ? 0 : pass * RW) : kb;
+    if constexpr (TMA && NSUB > 1 && SR == RW) {
       if (pass > 0) {   // the second half of the warp's keys goes where the first was: every lane is done reading it
         __syncwarp();
         const int pages = min(RW / page_size, (nk - kb + page_size - 1) / page_size), page0 = (k0 + kb) / page_size;
@@ -335,7 +341,7 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
   }
   l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
   l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
-  if constexpr (RW != WK) __syncthreads();   // the partial results lie over the keys: every warp is done with them
+  if constexpr (NSUB > 1) __syncthreads();   // the partial results lie over the keys: every warp is done with them
   if (g < G) {
 #pragma unroll
     for (int i = 0; i < NT_O; i++) {
@@ -442,7 +448,7 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
   HB_TL_MARK(0, 3);
 }
 
-template <int D, bool TMA, int RW>
+template <int D, bool TMA, int RW, int KW, int SR>
 static int launch_decode(int G, dim3 grid, size_t smem, cudaStream_t st, const CUtensorMap& mk, const CUtensorMap& mv,
                          int* status, const __nv_bfloat16* q, const __nv_bfloat16* kc, const __nv_bfloat16* vc,
                          const int* bt, int bt_stride, const int* row_req, const int* pos, __nv_bfloat16* out, float* pa,
@@ -453,11 +459,11 @@ static int launch_decode(int G, dim3 grid, size_t smem, cudaStream_t st, const C
     {                                                                                                               \
       static bool configured = false;                                                                               \
       if (!configured) {                                                                                            \
-        cudaFuncSetAttribute(attn_decode_kernel<D, GG, TMA, RW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
+        cudaFuncSetAttribute(attn_decode_kernel<D, GG, TMA, RW, KW, SR>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
         configured = true;                                                                                          \
       }                                                                                                             \
     }                                                                                                               \
-    hb_launch(attn_decode_kernel<D, GG, TMA, RW>, grid, AD_THREADS, smem, st, mk, mv, status, q, kc, vc, bt, bt_stride,  \
+    hb_launch(attn_decode_kernel<D, GG, TMA, RW, KW, SR>, grid, AD_THREADS, smem, st, mk, mv, status, q, kc, vc, bt, bt_stride,  \
               row_req, pos, out, pa, pm, Hq, Hkv, page_size, window, scale, chunk, S, q_len, row_limit, ctx_len,    \
               counters);                                                                                            \
     return 0;
@@ -493,14 +499,25 @@ HB_EXPORT int hb_attn_decode(const void* q, const void* kc, const void* vc, long
   if (S > 1 && (!workspace || !counters)) HB_FAIL("hb_attn_decode: rows that span %d chunks need a workspace and counters", S);
   if (chunk % 64) HB_FAIL("hb_attn_decode: chunk %d must be a multiple of 64", chunk);
   const long cache_rows = n_pages * Hkv * page_size;
-  const bool tma = HB_AD_TMA && status && n_pages > 0 && window == 0 && chunk == AD_WARPS * 64 && page_size % 8 == 0 &&
-                   page_size <= 64 && 64 % page_size == 0 && cache_rows < (1L << 31) && !(((uintptr_t)kc | (uintptr_t)vc) & 15);
-  // head_dim 128 by TMA with pages of at most 32 tokens: a warp's 64 keys in two passes through 32 rows (64 KB of
-  // keys and values a block, the warps' partial results over them), three blocks an SM instead of one
-  const bool halves = tma && D == 128 && page_size <= 32;
-  const size_t smem = halves ? 2 * (size_t)(AD_WARPS * 32) * D * 2 + 16 * (size_t)D * 2 + 1024
-                             : 2 * (size_t)chunk * D * 2 + 16 * (size_t)D * 2 + AD_WARPS * (size_t)G * (D + 2) * sizeof(float) +
-                                   (tma ? 1024 : 0);
+  const bool tma = HB_AD_TMA && status && n_pages > 0 && window == 0 && page_size % 8 == 0 && page_size <= 64 &&
+                   64 % page_size == 0 && cache_rows < (1L << 31) && !(((uintptr_t)kc | (uintptr_t)vc) & 15) &&
+                   (chunk == AD_WARPS * 64 || (chunk == AD_WARPS * 128 && D == 64));
+  // by TMA a block has 4 x RW rows of keys and values. head_dim 128 with pages of at most 32 tokens: a warp's 64 keys
+  // in two passes through 32 rows (64 KB a block, three blocks an SM instead of one). head_dim 64 with chunks of 512
+  // keys: a warp's 128 keys in two passes through 64 rows (64 KB a block as with chunks of 256). In both the warps'
+  // partial results lie over the keys at the end.
+  const bool halves = tma && D == 128 && page_size <= 32, wide = tma && chunk == AD_WARPS * 128;
+  // so few blocks that each has an SM of its own: all the keys of a chunk of 512 at once (the same passes)
+  static int n_sm = 0;
+  if (!n_sm) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) n_sm = 1;
+  }
+  const bool resident = wide && (long)S * Hkv * T <= n_sm;
+  const int rw = halves ? 32 : resident ? 128 : 64;
+  const size_t smem = tma ? 2 * (size_t)(AD_WARPS * rw) * D * 2 + 16 * (size_t)D * 2 + 1024 +
+                                (halves || wide ? 0 : AD_WARPS * (size_t)G * (D + 2) * sizeof(float))
+                          : 2 * (size_t)chunk * D * 2 + 16 * (size_t)D * 2 + AD_WARPS * (size_t)G * (D + 2) * sizeof(float);
   if (smem > 200 * 1024) HB_FAIL("hb_attn_decode: %zu bytes of shared memory (chunk %d, head_dim %d)", smem, chunk, D);
   float* pa = workspace;
   float* pm = workspace ? workspace + (size_t)T * Hq * S * D : nullptr;
@@ -521,9 +538,11 @@ HB_EXPORT int hb_attn_decode(const void* q, const void* kc, const void* vc, long
   int r = 1;
 #define HB_AD_ARGS G, grid, smem, st, mk, mv, status, qq, kk, vv, bt, bt_stride, row_req, pos, (__nv_bfloat16*)out, pa, pm, Hq, Hkv, \
                    page_size, window, sl2, chunk, S, q_len, row_limit, ctx_len, counters
-  if (D == 64) r = tma ? launch_decode<64, true, 64>(HB_AD_ARGS) : launch_decode<64, false, 64>(HB_AD_ARGS);
-  else if (halves) r = launch_decode<128, true, 32>(HB_AD_ARGS);
-  else if (D == 128) r = tma ? launch_decode<128, true, 64>(HB_AD_ARGS) : launch_decode<128, false, 64>(HB_AD_ARGS);
+  if (D == 64 && resident) r = launch_decode<64, true, 64, 128, 128>(HB_AD_ARGS);
+  else if (D == 64 && wide) r = launch_decode<64, true, 64, 128, 64>(HB_AD_ARGS);
+  else if (D == 64) r = tma ? launch_decode<64, true, 64, 64, 64>(HB_AD_ARGS) : launch_decode<64, false, 64, 64, 64>(HB_AD_ARGS);
+  else if (halves) r = launch_decode<128, true, 32, 64, 32>(HB_AD_ARGS);
+  else if (D == 128) r = tma ? launch_decode<128, true, 64, 64, 64>(HB_AD_ARGS) : launch_decode<128, false, 64, 64, 64>(HB_AD_ARGS);
 #undef HB_AD_ARGS
   if (r) HB_FAIL("hb_attn_decode: no kernel for group %d", G);
   HB_CHECK_LAUNCH("hb_attn_decode");

@@ -289,6 +289,12 @@ def linear_swiglu(a, w, act_out, group) -> bool:
 
 
 DECODE_CHUNK = 256      # keys per split of the decode attention kernel (absolute positions)
+DECODE_CHUNK_64 = int(os.environ.get("HIPINFER_B200_DECODE_CHUNK_64", "512"))
+
+
+def decode_chunk(head_dim: int) -> int:
+    """Keys per split: a constant of the model, never of the batch (a row's split depends on its position alone)."""
+    return DECODE_CHUNK_64 if head_dim == 64 else DECODE_CHUNK
 
 
 _attn_counters = {}
@@ -305,7 +311,7 @@ def _decode_counters(device, n):
 
 
 def attention_decode(q, k_cache, v_cache, block_table, row_request, positions, out, n_heads, n_kv_heads, head_dim,
-                     page_size, window, scale, max_pos, chunk=DECODE_CHUNK, q_len=None, row_limit=0, ctx_len=None):
+                     page_size, window, scale, max_pos, chunk=None, q_len=None, row_limit=0, ctx_len=None):
     """The bf16 row-attention kernel itself (see csrc/attention_fast.cu); rows whose keys span several
     chunks are finished inside it. With q_len (int32 per request) rows of requests with row_limit
     rows or more are skipped. row_request None: row t is the only row of request t (a decode-only
@@ -315,6 +321,7 @@ def attention_decode(q, k_cache, v_cache, block_table, row_request, positions, o
     from . import ops
 
     T = q.shape[0]
+    chunk = chunk or decode_chunk(head_dim)
     ws = ops.attention_workspace(T, n_heads, head_dim, max_pos, chunk, q.device)
     cnt = None if ws is None else _decode_counters(q.device, T * n_kv_heads)
     _call("hb_attn_decode", q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), k_cache.shape[0], block_table.data_ptr(),

@@ -263,6 +263,32 @@ def test_attention_decode_long_context_many_chunks(D):
         torch.testing.assert_close(got[t:t + 1], ref, rtol=1e-2, atol=1e-2, msg=lambda m: f"row {t} {rows[t]}: {m}")
 
 
+def test_attention_decode_few_and_many_rows_give_the_same_bits():
+    """With few rows every block has an SM of its own and takes all its keys at once; with many a warp
+    asks for its keys pass by pass: the passes are the same, so a row's result is bit-identical."""
+    Hq, Hkv, D, ps = 32, 8, 64, 16
+    lens = [1500, 700, 2300]
+    kc, vc, bt, ks, vs = _paged_setup(lens, Hkv, D, ps, torch.bfloat16, 71)
+    rows = [(r, p) for r, n in enumerate(lens) for p in range(n - 14, n)]          # 42 rows: 42 * 8 * 5 blocks
+    q = rnd(len(rows), Hq * D, seed=72)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    scale = 1 / math.sqrt(D)
+    many = torch.empty(len(rows), Hq * D, dtype=torch.bfloat16, device=DEV)
+    fast().attention_decode(q, kc, vc, bt, i32([r for r, _ in rows]), i32([p for _, p in rows]), many, Hq, Hkv, D, ps, 0, scale,
+                            max(lens) - 1)
+    for pick in ([0], [13, 14], [41]):
+        few = torch.empty(len(pick), Hq * D, dtype=torch.bfloat16, device=DEV)
+        fast().attention_decode(q[pick].contiguous(), kc, vc, bt, i32([rows[i][0] for i in pick]), i32([rows[i][1] for i in pick]),
+                                few, Hq, Hkv, D, ps, 0, scale, max(lens) - 1)
+        sync_check()
+        assert torch.equal(few, many[pick])
+    t = 41
+    r, p = rows[t]
+    ref = plain.attention_scores_softmax_values(q[t:t + 1].float().cpu().reshape(1, Hq, D), ks[r][:p + 1], vs[r][:p + 1], [p],
+                                                list(range(p + 1)))
+    torch.testing.assert_close(many[t:t + 1].float().cpu().reshape(1, Hq, D), ref, rtol=1e-2, atol=1e-2)
+
+
 def test_attention_decode_rows_that_are_requests():
     """A decode-only step: row t is request t, which the kernel then does not look up: the same bits."""
     Hq, Hkv, D, ps = 8, 2, 64, 16
