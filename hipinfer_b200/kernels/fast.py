@@ -292,9 +292,10 @@ DECODE_CHUNK = 256      # keys per split of the decode attention kernel (absolut
 DECODE_CHUNK_64 = int(os.environ.get("HIPINFER_B200_DECODE_CHUNK_64", "512"))
 
 
-def decode_chunk(head_dim: int) -> int:
-    """Keys per split: a constant of the model, never of the batch (a row's split depends on its position alone)."""
-    return DECODE_CHUNK_64 if head_dim == 64 else DECODE_CHUNK
+def decode_chunk(head_dim: int, window: int = 0) -> int:
+    """Keys per split: a constant of the layer, never of the batch (a row's split depends on its position alone).
+    512 at head_dim 64 without a window (the TMA kernel walks them in two passes), else 256."""
+    return DECODE_CHUNK_64 if head_dim == 64 and not window else DECODE_CHUNK
 
 
 _attn_counters = {}
@@ -321,7 +322,7 @@ def attention_decode(q, k_cache, v_cache, block_table, row_request, positions, o
     from . import ops
 
     T = q.shape[0]
-    chunk = chunk or decode_chunk(head_dim)
+    chunk = chunk or decode_chunk(head_dim, int(window))
     ws = ops.attention_workspace(T, n_heads, head_dim, max_pos, chunk, q.device)
     cnt = None if ws is None else _decode_counters(q.device, T * n_kv_heads)
     _call("hb_attn_decode", q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), k_cache.shape[0], block_table.data_ptr(),
