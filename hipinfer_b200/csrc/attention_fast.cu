@@ -486,7 +486,7 @@ HB_EXPORT int hb_attn_decode_supported(int Hq, int Hkv, int D) {
 // or null): the tokens that were in the cache before this step; their keys may be read before
 // the kernel ahead in the stream has ended. row_req null: row t is request t's only row. n_pages: the pages the cache holds (its first
 // extent); status: the word a bounded wait that ran out sets to 1. With both, no window, a chunk
-// of 256 and pages of 8 to 64 tokens the keys and values come by TMA.
+// of 256 (or of 512 at head_dim 64) and pages of 8 to 64 tokens the keys and values come by TMA.
 HB_EXPORT int hb_attn_decode(const void* q, const void* kc, const void* vc, long n_pages, const int* bt, int bt_stride,
                              const int* row_req, const int* pos, void* out, float* workspace, int* counters, int T,
                              int Hq, int Hkv, int D, int page_size, int window, float scale, int chunk, int max_pos,
