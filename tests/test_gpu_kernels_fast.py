@@ -263,10 +263,11 @@ def test_attention_decode_long_context_many_chunks(D):
         torch.testing.assert_close(got[t:t + 1], ref, rtol=1e-2, atol=1e-2, msg=lambda m: f"row {t} {rows[t]}: {m}")
 
 
-def test_attention_decode_few_and_many_rows_give_the_same_bits():
+@pytest.mark.parametrize("D", [64, 128])
+def test_attention_decode_few_and_many_rows_give_the_same_bits(D):
     """With few rows every block has an SM of its own and takes all its keys at once; with many a warp
     asks for its keys pass by pass: the passes are the same, so a row's result is bit-identical."""
-    Hq, Hkv, D, ps = 32, 8, 64, 16
+    Hq, Hkv, ps = 32, 8, 16
     lens = [1500, 700, 2300]
     kc, vc, bt, ks, vs = _paged_setup(lens, Hkv, D, ps, torch.bfloat16, 71)
     rows = [(r, p) for r, n in enumerate(lens) for p in range(n - 14, n)]          # 42 rows: 42 * 8 * 5 blocks
