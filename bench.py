@@ -326,19 +326,62 @@ def breakdown(layers: int, batch: int, prefill: bool = False) -> int:
 
 
 def reference_arm(a) -> int:
-    """The unmodified reference through its own API. It is installed offline into baseline/_ref by
-    the one pip command the contract names; where that cannot be done this arm says so."""
-    why = reference_unavailable()
-    print(json.dumps({"impl": "reference", "unavailable": why}))
+    """The unmodified reference through its own binding (baseline/reference_arm.py builds it with its
+    own make line and drives `Engine.prefill` / `Engine.decode`): the same metric, sizes, steps and
+    warm-up as the other arm, fp16 as the reference computes. Nothing of hipinfer_b200 is imported."""
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    import reference_arm as ra
+
+    if a.gpus != 1:
+        print(json.dumps({"impl": "reference", "unavailable": "this bench compares on one GPU"}))
+        return 0
+    a.warmup = max(a.warmup, 3)
+    if (a.shape, a.prompt, a.prefill_tokens) != ("1b", PROMPT_LEN, PREFILL_TOKENS):
+        choose_shape(a.shape, a.prompt, a.prefill_tokens, a.steps + a.warmup + 8)
+    layers = a.layers or MODEL["num_hidden_layers"]
+    point_batches = [] if a.no_points else [b for b in (1, 64) if b != a.batch]
+    clocks = ClockSampler().start()
+    try:
+        r = ra.run(MODEL, layers, a.batch, a.steps, a.warmup, CONTEXT_LEN, PROMPT_LEN, PREFILL_TOKENS, point_batches, clocks)
+    except ra.ReferenceUnavailable as e:
+        print(json.dumps({"impl": "reference", "unavailable": str(e)}))
+        return 0
+    pk = peaks()
+    ms = r["ms_per_step"]
+    mean_ctx = PROMPT_LEN + a.warmup + (a.steps - 1) / 2.0 + 1
+    step_bytes = r["weight_bytes"] + a.batch * mean_ctx * r["kv_bytes_per_token"]
+    achieved = step_bytes / ms / 1e6
+    pre_ms = r["prefill_ms"]
+    out = {
+        "metric": f"decode tok/s at batch {a.batch} ({SHAPE_NAME}, {PROMPT_LEN:,}-token prompts)",
+        "value": round(a.batch / ms * 1e3, 1), "unit": "tok/s", "n_gpus": 1, "steps": a.steps, "warmup": a.warmup,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "fp16", "data": "synthetic: uniform-random token ids, random N(0, 0.02) fp16 weights",
+        "impl": "reference",
+        "config": bench_config(a.batch, layers, f"inputs larger than L2: {r['weight_bytes'] / 1e9:.2f} GB of weights read per step",
+                               kv_dtype="fp16", page_size=None),
+        "clocks": clocks.summary(),
+        "e2e": {"value": round(a.batch / r["e2e_ms_per_step"] * 1e3, 1), "unit": "tok/s",
+                "ms_per_step": round(r["e2e_ms_per_step"], 4), "h2d_bytes_per_step": 0, "d2h_bytes_per_step": a.batch * 4},
+        "prefill": {"value": round(PREFILL_TOKENS / pre_ms * 1e3, 1), "tokens": PREFILL_TOKENS, "ms": round(pre_ms, 4),
+                    "frac": round(prefill_flops(layers) / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
+                    "peak_tflops": pk["bf16_tflops"], "peaks": pk["source"]},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4), "peaks": pk["source"],
+                     "bytes_per_step": int(step_bytes), "mean_context": mean_ctx},
+        "points": {k: round(v, 1) for k, v in r["points"].items()},
+    }
+    print(json.dumps(out))
     return 0
 
 
-def reference_unavailable() -> str:
-    ref = os.path.join(ROOT, "baseline", "_ref")
-    if not os.path.isdir(ref) or not os.listdir(ref):
-        return ("Sky1219/hipinfer has no setup.py/pyproject.toml: it is a Makefile project (one nvcc line building "
-                "libhipinfer.so) and cannot be pip-installed offline into baseline/_ref")
-    return "baseline/_ref holds no importable hipinfer package"
+def bench_config(batch: int, layers: int, l2: str, kv_dtype: str = "bf16", page_size=PAGE) -> dict:
+    return {"model": SHAPE_NAME, "layers": layers, "layers_full": MODEL["num_hidden_layers"],
+            "hidden": MODEL["hidden_size"], "heads": MODEL["num_attention_heads"],
+            "kv_heads": MODEL["num_key_value_heads"], "head_dim": MODEL["head_dim"],
+            "intermediate": MODEL["intermediate_size"], "vocab": MODEL["vocab_size"], "global_batch": batch,
+            "seq_len": CONTEXT_LEN, "prompt_len": PROMPT_LEN, "page_size": page_size, "kv_dtype": kv_dtype,
+            "parallelism": "single GPU", "l2": l2}
 
 
 def main() -> int:
@@ -394,13 +437,7 @@ def main() -> int:
         "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: uniform-random token ids, random N(0, 0.02) bf16 weights",
         "impl": "ours",
-        "config": {"model": SHAPE_NAME, "layers": a.layers, "layers_full": MODEL["num_hidden_layers"],
-                   "hidden": MODEL["hidden_size"], "heads": MODEL["num_attention_heads"],
-                   "kv_heads": MODEL["num_key_value_heads"], "head_dim": MODEL["head_dim"],
-                   "intermediate": MODEL["intermediate_size"], "vocab": MODEL["vocab_size"], "global_batch": a.batch,
-                   "seq_len": CONTEXT_LEN, "prompt_len": PROMPT_LEN, "page_size": PAGE, "kv_dtype": "bf16",
-                   "parallelism": "single GPU",
-                   "l2": f"inputs larger than L2: {eng.weight_bytes / 1e9:.2f} GB of weights read per step"},
+        "config": bench_config(a.batch, a.layers, f"inputs larger than L2: {eng.weight_bytes / 1e9:.2f} GB of weights read per step"),
         "clocks": clocks.summary(),
         "e2e": {"value": round(a.batch / e2e_ms * 1e3, 1), "unit": "tok/s", "ms_per_step": round(e2e_ms, 4),
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},

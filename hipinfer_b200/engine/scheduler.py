@@ -77,6 +77,7 @@ class Scheduler:
         self.running: List[Request] = []   # in admission order
         self.finished: List[Request] = []
         self.n_preemptions = 0
+        self._preempted_now: set = set()   # requests preempted by the schedule() call that is running
 
     # ---------------------------------------------------------------- admission
     def add(self, request: Request) -> None:
@@ -115,10 +116,12 @@ class Scheduler:
         victim.n_cached, victim.status = 0, WAITING
         victim.preemptions += 1
         self.n_preemptions += 1
+        self._preempted_now.add(victim.request_id)
         self.waiting.appendleft(victim)
 
     def schedule(self) -> List[Scheduled]:
         out: List[Scheduled] = []
+        self._preempted_now = set()
         promised = [0] * len(self.cache.pools)
         budget = self.budget
         order = [r for r in self.running if r.decoding] + [r for r in self.running if not r.decoding]
@@ -143,13 +146,15 @@ class Scheduler:
             self._promise(req, n, promised)
             out.append(Scheduled(req, req.n_cached, n, req.n_cached + n == len(req.tokens)))
             budget -= n
-        preempted_now = {r.request_id for r in self.waiting if r.preemptions and r.n_cached == 0}
         admitted = 0
         while self.waiting and budget > 0 and len(self.running) < self.max_num_seqs \
                 and admitted < self.cache.slots.free_count:
             req = self.waiting[0]
-            if req.request_id in preempted_now and out:
-                break                     # just preempted for lack of room: not in this same step
+            if req.status != WAITING:     # ended while it waited (finish()): it leaves the queue
+                self.waiting.popleft()
+                continue
+            if req.request_id in self._preempted_now and out:
+                break                     # preempted by this very call for lack of room: not in the same step
             n = min(len(req.tokens), budget)
             if not self._fits(req, n, promised):
                 break
@@ -163,10 +168,12 @@ class Scheduler:
         return out
 
     def finish(self, req: Request, reason: str) -> None:
-        """End a running request now (a stop condition noticed outside update): free its cache."""
+        """End a request now, running or waiting (a stop condition noticed outside update): free its cache."""
         req.status, req.finish_reason = FINISHED, reason
         if req in self.running:
             self.running.remove(req)
+        if req in self.waiting:           # preempted earlier and still queued: it must not be admitted again
+            self.waiting.remove(req)
         if self.cache.has_request(req.request_id):
             self.cache.free_request(req.request_id)
         self.finished.append(req)

@@ -263,6 +263,53 @@ def test_when_pages_run_out_the_youngest_is_preempted_and_recomputed():
     assert cm.free_pages() == [6] and cm.slots.free_count == 2
 
 
+def test_a_preempted_request_comes_back_while_others_still_run():
+    """A victim waits only until its next portion fits: not until every running request has ended."""
+    cm, sch = make(num_pages=12, page_size=16, budget=64, max_seqs=3)
+    sch.add(req("a", 60, 40))         # 4 pages, grows to 7
+    sch.add(req("b", 60, 5))          # 4 pages, ends early
+    sch.add(req("c", 60, 40))         # 4 pages: the pool is full after the three prompts
+    for _ in range(3):
+        run_step(cm, sch)
+    assert cm.free_pages() == [0] and len(sch.running) == 3
+    back = None
+    for step in range(60):
+        s, _ = run_step(cm, sch)
+        ids = [x.request.request_id for x in s]
+        if sch.n_preemptions and back is None and "c" in ids:
+            back = step
+            assert "a" in ids, "the victim came back only after the others had ended"
+            assert next(x for x in s if x.request.request_id == "c").start == 0
+            break
+    assert sch.n_preemptions >= 1 and back is not None
+    while sch.has_work():
+        run_step(cm, sch)
+    assert {r.request_id: len(r.output) for r in sch.finished} == {"a": 40, "b": 5, "c": 40}
+    assert cm.free_pages() == [12] and cm.slots.free_count == 3
+
+
+def test_a_request_finished_while_it_waits_is_never_scheduled_again():
+    """finish() on a request that a later schedule() preempted (a stop token read back one step late):
+    it leaves the waiting queue, is reported once and produces nothing more."""
+    cm, sch = make(num_pages=6, page_size=16, budget=128, max_seqs=2)
+    sch.add(req("old", 40, 30))
+    sch.add(req("young", 40, 30))
+    for _ in range(9):
+        run_step(cm, sch)
+    s, _ = run_step(cm, sch)                         # young is preempted here
+    young = sch.waiting[0]
+    assert young.request_id == "young" and sch.n_preemptions == 1
+    n_out = len(young.output)
+    sch.finish(young, "stop")
+    assert young not in sch.waiting and young.status == "finished"
+    while sch.has_work():
+        s, _ = run_step(cm, sch)
+        assert all(x.request.request_id == "old" for x in s)
+    assert len(young.output) == n_out
+    assert [r.request_id for r in sch.finished].count("young") == 1
+    assert cm.free_pages() == [6] and cm.slots.free_count == 2
+
+
 @pytest.mark.parametrize("seed", range(5))
 def test_random_workloads_finish_with_nothing_lost(seed):
     rng = random.Random(seed)
