@@ -36,10 +36,11 @@ __device__ __forceinline__ bool hb_mbar_try_wait(uint64_t* bar, uint32_t parity)
       : "memory");
   return ok != 0;
 }
-// Waits for the phase of `parity` to complete. Gives up after HB_WAIT_LIMIT polls or as soon as
+// Waits for the phase of `parity` to complete. Gives up after `limit` polls or as soon as
 // another role raised *abort (shared memory); then it raises *abort itself and returns false.
-__device__ __forceinline__ bool hb_mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort) {
-  for (uint32_t i = 0; i < HB_WAIT_LIMIT; i++) {
+__device__ __forceinline__ bool hb_mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort,
+                                             uint32_t limit = HB_WAIT_LIMIT) {
+  for (uint32_t i = 0; i < limit; i++) {
     if (hb_mbar_try_wait(bar, parity)) return true;
     if ((i & 63u) == 63u && *abort) return false;
   }

@@ -23,6 +23,7 @@ import torch
 
 from ..cache import OutOfPages
 from ..config import ModelConfig, config_from_dict, load_config
+from ..kernels import ops
 from ..sampling import Sampler, SamplingParams
 from .batch import StepEntry
 from .runner import ModelRunner, StepError
@@ -153,6 +154,7 @@ class Engine:
             pending, self._pending = self._pending, None
         if pending is not None and pending["event"] is not None:
             pending["event"].synchronize()
+            ops.check_device_status()          # raises KernelTimeout if a kernel of the step gave up on a wait
             eos = self.scheduler.eos
             for (req, idx), tok in zip(pending["slots"], pending["host"].tolist()):
                 if idx >= len(req.output):
@@ -280,6 +282,7 @@ class Engine:
             raise ValueError(str(e)) from None
         stop.record()
         stop.synchronize()
+        ops.check_device_status()
         return start.elapsed_time(stop)
 
     def history(self, slot: int, start: int, n: int) -> List[int]:

@@ -38,7 +38,7 @@ def main(argv=None) -> int:
 
     from .runner import ModelRunner
     from .batch import StepEntry
-    from ..kernels import library
+    from ..kernels import library, ops
     import torch
 
     os.makedirs(a.out, exist_ok=True)
@@ -61,6 +61,7 @@ def main(argv=None) -> int:
             arr.tofile(os.path.join(a.out, f"{step}.f32"))
         else:
             torch.cuda.synchronize()
+        ops.check_device_status()              # a kernel that gave up on a bounded wait ends the replay with an error
         for rid in rec.get("end", []):
             runner.end(rid)
         print(f"done {step}", flush=True)

@@ -33,6 +33,7 @@ _SIGS = {
     "hb_flash_prefill_tc_supported": [_i, _i, _i, _i],
     "hb_gemm_tc_rope_kv": [_p, _l, _p, _l, _i, _i, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p, _p],
     "hb_attn_decode_supported": [_i, _i, _i],
+    "hb_wait_selftest": [_p, _i, _p, _p],
 }
 _fns = {}
 _LAUNCHES = {"hb_gemm_tc_rope_kv": 1, "hb_gemm_stream_finish": 1, "hb_add_rmsnorm_slices": 1, "hb_rope_kv_slices": 1, "hb_gemm_tc": 1, "hb_gemm_skinny": 1, "hb_gemm_stream": 1, "hb_attn_decode": 1, "hb_flash_prefill": 1, "hb_flash_prefill_tc": 1}
@@ -78,6 +79,15 @@ def check_status() -> None:
     if _status is not None and int(_status[0]) != 0:
         _status[0] = 0
         raise KernelTimeout("a tensor-core kernel gave up on a bounded wait (TMA or MMA pipeline); its output is invalid")
+
+
+def wait_selftest(polls: int = 4096) -> torch.Tensor:
+    """Launches the one kernel whose bounded wait cannot complete (csrc/wait_selftest.cu): it gives up after
+    `polls` polls, raises the status word, frees its tensor memory and returns. Returns its two result words
+    (on the device): [the wait completed, the block's abort flag]. check_status() raises after it."""
+    out = torch.zeros(2, dtype=torch.int32, device="cuda")
+    _call("hb_wait_selftest", status_word().data_ptr(), int(polls), out.data_ptr(), _stream())
+    return out
 
 
 def _stream():

@@ -67,6 +67,16 @@ def _stream() -> int:
     return library.current_stream()
 
 
+def check_device_status() -> None:
+    """To be called where the host has just waited for the device: raises `fast.KernelTimeout` if a kernel
+    gave up on one of its bounded waits since the last call (its output is not valid), and clears the word.
+    It reads one word of pinned host memory. The reference's counterpart: HI_CHECK after its calls
+    (src/hip_compat.h:95-97) and the -1 of its entry points (src/api.cu:1827-1839)."""
+    from . import fast
+
+    fast.check_status()
+
+
 def _dt(t: torch.Tensor) -> int:
     try:
         return _DT[t.dtype]

@@ -54,4 +54,6 @@ class Sampler:
         """The same, brought to the host (this waits for the device)."""
         if logits.shape[0] == 0:
             return []
-        return self.sample_device(logits, params, positions).cpu().tolist()
+        toks = self.sample_device(logits, params, positions).cpu().tolist()
+        ops.check_device_status()          # the copy has waited for the step: a kernel that gave up shows here
+        return toks

@@ -23,3 +23,21 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+def pytest_terminal_summary(terminalreporter):
+    """The measured error of the logits comparisons: per configuration and precision, the largest
+    |difference| over the largest |logit| of a request under each plan (worst request)."""
+    try:
+        import tiny
+    except Exception:
+        return
+    worst = {}
+    for (config, plan), dtype, rel in tiny.MEASURED:
+        plans = worst.setdefault((config, dtype), {})
+        plans[plan] = max(plans.get(plan, 0.0), rel)
+    if worst:
+        terminalreporter.write_line("logits against the plain implementation, largest |diff| / largest |logit| (bound: "
+                                    + ", ".join(f"{k} {v:.0e}" for k, v in tiny.TOL.items()) + "):")
+        for (config, dtype), plans in sorted(worst.items()):
+            terminalreporter.write_line(f"  {config:22s} {dtype:9s} " + "  ".join(f"{p or 'all'} {r:.1e}" for p, r in sorted(plans.items())))

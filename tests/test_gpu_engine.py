@@ -208,3 +208,64 @@ def test_smoke_entry_point():
     import __graft_entry__ as entry
 
     entry.smoke()
+
+
+# ------------------------------------------------------------------------------------------
+# a kernel that gave up on a bounded wait is an error of the step, not silent wrong tokens
+# ------------------------------------------------------------------------------------------
+def test_a_wait_that_runs_out_returns_and_raises(folders):
+    """The one kernel whose wait cannot complete (its barrier expects bytes that nothing brings) gives up after
+    a few thousand polls: the launch returns, the status word is 1, the host raises KernelTimeout and clears it,
+    the block's tensor memory was freed (the tensor-core kernels run right afterwards), and the engine's
+    own entry points raise where they next wait for the device."""
+    from hipinfer_b200.kernels import fast, ops
+
+    fast.check_status()
+    out = fast.wait_selftest(polls=3000)
+    torch.cuda.synchronize()
+    assert out.tolist() == [0, 1], "the wait cannot have completed, and the abort flag must be up"
+    assert int(fast.status_word()[0]) == 1
+    with pytest.raises(fast.KernelTimeout):
+        ops.check_device_status()
+    assert int(fast.status_word()[0]) == 0
+    ops.check_device_status()                      # cleared: no second error
+    # the tensor-core product afterwards (it allocates all of its block's tensor memory) is right
+    g = torch.Generator(device="cuda").manual_seed(0)
+    a = (torch.randn(256, 512, generator=g, device="cuda") * 0.5).bfloat16()
+    w = (torch.randn(384, 512, generator=g, device="cuda") * 0.5).bfloat16()
+    got = torch.empty(256, 384, dtype=torch.float32, device="cuda")
+    for _ in range(4):
+        fast.gemm_tc(a, w, got, fast.EPI_F32)
+    torch.cuda.synchronize()
+    ops.check_device_status()
+    assert torch.allclose(got, a.float() @ w.float().t(), rtol=1e-3, atol=1e-2)
+    # through the engine: the word raised by a kernel of a step ends generation with the error
+    folder, cfg, weights = folders["c"]
+    prompt = tiny.random_tokens(40, cfg["vocab_size"], 3)
+    for pipeline in (True, False):
+        eng = engine(folder, "bfloat16", max_batch=2, max_seq=128, pipeline=pipeline)
+        fast.wait_selftest(polls=2000)
+        with pytest.raises(fast.KernelTimeout):
+            eng.generate(prompt, 4)
+        eng.close()
+    want, steps = plain.generate_greedy(cfg, weights, prompt, 4)
+    eng = engine(folder, "bfloat16", max_batch=2, max_seq=128)
+    check_tokens(eng.generate(prompt, 4), want, steps, "bfloat16", "after a timeout")
+    eng.close()
+
+
+def test_replay_ends_with_the_error(folders, tmp_path, monkeypatch):
+    """trace_run's loop: a status word raised during a step ends the replay with KernelTimeout."""
+    import io
+    import json
+
+    from hipinfer_b200.engine import replay
+    from hipinfer_b200.kernels import fast
+
+    folder, cfg, _ = folders["c"]
+    fast.check_status()
+    fast.status_word()[0] = 1                  # as a kernel's give-up path would leave it
+    monkeypatch.setattr("sys.stdin", io.StringIO(json.dumps({"step": 0, "entries": [{"id": "a", "tokens": [1, 2, 3], "want": [2]}]}) + "\n"))
+    with pytest.raises(fast.KernelTimeout):
+        replay.main(["--model", folder, "--dtype", "bfloat16", "--out", str(tmp_path), "--max-tokens", "64"])
+    assert int(fast.status_word()[0]) == 0

@@ -35,7 +35,8 @@ def setup(request, tmp_path_factory):
 def _check(setup, plan, what):
     got = tiny.run_plan(setup["tr"], setup["requests"], plan)
     for rid, ref in setup["ref"].items():
-        tiny.assert_logits_close(got[rid], ref, setup["dtype"], f"{what} {setup['which']} {setup['dtype']} {rid}")
+        tiny.assert_logits_close(got[rid], ref, setup["dtype"], f"{what} {setup['which']} {setup['dtype']} {rid}",
+                                 group=(f"tiny {setup['which']}", what))
 
 
 def test_whole(setup):
@@ -53,6 +54,17 @@ def test_portions(setup):
 @pytest.mark.parametrize("seed", [0, 1, 2])
 def test_mixed(setup, seed):
     _check(setup, tiny.plan_mixed(setup["requests"], seed), f"mixed{seed}")
+
+
+@pytest.mark.parametrize("seed", [0, 1, 2])
+def test_mixed_long_portions(setup, seed):
+    """The scheduler's ordinary step: a portion of more than 64 rows of one request (where it has that many left)
+    beside short portions and single decode rows of the others, on a pool so small that pages are used again."""
+    plan = tiny.plan_mixed_long(setup["requests"], seed)
+    if setup["which"] == "c":
+        mixed = [s for s in plan if any(n > 64 for _, n in s) and any(n == 1 for _, n in s)]
+        assert mixed, "the plan has no step with a long portion beside a decode row"
+    _check(setup, plan, f"mixed-long{seed}")
 
 
 def test_wanted_subset_and_no_want(setup):

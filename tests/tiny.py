@@ -32,7 +32,18 @@ TINY_C = dict(architectures=["LlamaForCausalLM"], vocab_size=1000, hidden_size=2
                                 original_max_position_embeddings=256),
               tie_word_embeddings=True, hidden_act="silu")
 
-WEIGHTS = {"a": dict(cfg=TINY_A, seed=0, std=0.02, norm_std=0.0),
+# the real layer sizes of the Llama-3.2-1B shape (width, heads, feed-forward, vocabulary, llama3 scaling, tied head)
+# with 2 of its 16 layers, so that the plain implementation on the CPU stays within seconds
+LLAMA_1B_LAYERS_FULL, LLAMA_1B_LAYERS_TESTED = 16, 2
+LLAMA_1B_2L = dict(architectures=["LlamaForCausalLM"], vocab_size=128256, hidden_size=2048, intermediate_size=8192,
+                   num_hidden_layers=LLAMA_1B_LAYERS_TESTED, num_attention_heads=32, num_key_value_heads=8, head_dim=64,
+                   max_position_embeddings=131072, rms_norm_eps=1e-5, rope_theta=500000.0,
+                   rope_scaling=dict(rope_type="llama3", factor=32.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                                     original_max_position_embeddings=8192),
+                   tie_word_embeddings=True, hidden_act="silu")
+
+WEIGHTS = {"1b2l": dict(cfg=LLAMA_1B_2L, seed=11, std=0.02, norm_std=0.1),
+           "a": dict(cfg=TINY_A, seed=0, std=0.02, norm_std=0.0),
            "b": dict(cfg=TINY_B, seed=2, std=0.05, norm_std=0.1),
            "c": dict(cfg=TINY_C, seed=5, std=0.04, norm_std=0.1)}
 
@@ -167,6 +178,43 @@ def plan_mixed(requests, seed=0, max_live=4, decode_tail=12):
     return plan
 
 
+def plan_mixed_long(requests, seed=0, max_live=4, decode_tail=24, long=(65, 300), short=(2, 15)):
+    """plan_mixed with the portions a scheduler with a budget of some hundred tokens makes: in a step one live
+    request may take a long portion (more than 64 rows: the tensor-core products and the flash kernel over
+    several key tiles, on top of what it has cached), the others short ones (2 to 15 rows) or, in their last
+    `decode_tail` tokens, single rows. Requests sit out steps and end in another order than they started."""
+    g = torch.Generator().manual_seed(1000 + seed)
+
+    def rnd(lo, hi):
+        return int(torch.randint(lo, hi + 1, (1,), generator=g))
+
+    waiting = list(requests)
+    left = {rid: len(t) for rid, t in requests.items()}
+    live, plan = [], []
+    while waiting or live:
+        while waiting and len(live) < max_live and (not live or rnd(0, 2) > 0):
+            live.append(waiting.pop(0))
+        step, long_taken = [], False
+        for rid in sorted(live, key=lambda r: -left[r]):       # the request with most left gets the long portion
+            if len(live) > 1 and rnd(0, 6) == 0:
+                continue  # sits this step out
+            room = left[rid] - decode_tail
+            if room <= 0:
+                n = 1
+            elif not long_taken and room > short[1] and rnd(0, 3) > 0:
+                n, long_taken = min(rnd(*long), room), True
+            else:
+                n = min(rnd(*short), room)
+            step.append((rid, n))
+            left[rid] -= n
+            if left[rid] == 0:
+                live.remove(rid)
+        if step:
+            step.sort(key=lambda e: list(requests).index(e[0]))
+            plan.append(step)
+    return plan
+
+
 def run_plan(stepper, requests, plan):
     """Feed `plan` (steps of (id, n tokens)) wanting every position; {id: logits [len, vocab]}."""
     fed = {rid: 0 for rid in requests}
@@ -192,13 +240,16 @@ def run_plan(stepper, requests, plan):
 # another order. bfloat16: activations, q, k, v and the attention output are rounded to 8 bits
 # of mantissa a few times per layer.
 TOL = {"float32": 2e-5, "bfloat16": 3e-2}
+MEASURED = []      # ((configuration, plan), dtype, largest |difference| / largest |logit|) of every comparison: printed at the end of a run
 
 
-def assert_logits_close(got, ref, dtype, what=""):
+def assert_logits_close(got, ref, dtype, what="", group=None):
+    """group: (configuration, plan) under which the measured error is listed at the end of the run."""
     scale = float(ref.abs().max())
     err = float((got.float() - ref.float()).abs().max())
     assert got.shape == ref.shape, f"{what}: shape {tuple(got.shape)} != {tuple(ref.shape)}"
     assert torch.isfinite(got).all(), f"{what}: non-finite logits"
+    MEASURED.append((group or (what, ""), dtype, err / scale if scale else 0.0))
     if err > TOL[dtype] * scale:
         bad = (got.float() - ref.float()).abs().amax(-1)
         first = int((bad > TOL[dtype] * scale).nonzero()[0])
