@@ -1,9 +1,10 @@
 """Weights by tensor name: what the model expects against what the folder holds.
 
 Every part declares the tensors it needs as `ParamSpec`s (name, shape, kind). `load_weights`
-compares the whole list with the file's names and shapes first and raises ONE `WeightError`
-that lists every missing tensor, every unexpected tensor and every wrong shape; only then does
-it read. Storage policy: 16-bit floats are kept in bfloat16, integer tables become int32, and
+compares the whole list with the file's names, shapes and element types first and raises ONE
+`WeightError` that lists every missing tensor, every unexpected tensor, every wrong shape and
+every wrong element type (an integer tensor under a weight's name, a float tensor where a table
+of integers is expected); only then does it read. Storage policy: 16-bit floats are kept in bfloat16, integer tables become int32, and
 a tensor stored in 32-bit floats stays in 32-bit.
 
 `random_weights` / `write_random_model` are the random-weights mode: a model folder
@@ -33,14 +34,15 @@ class ParamSpec:
     shape: Tuple[int, ...]
     init: str = "normal"
     optional: bool = False
+    numbers: str = "float"       # "float": a weight (any float type in the file); "int": a table of integers
 
 
 class WeightError(ValueError):
-    """The folder's tensors do not fit the model. `.missing`, `.unexpected`, `.wrong_shape` hold the details."""
+    """The folder's tensors do not fit the model. `.missing`, `.unexpected`, `.wrong_shape`, `.wrong_dtype` hold the details."""
 
-    def __init__(self, folder, missing, unexpected, wrong_shape, other=()):
+    def __init__(self, folder, missing, unexpected, wrong_shape, other=(), wrong_dtype=()):
         self.folder, self.missing, self.unexpected = folder, list(missing), list(unexpected)
-        self.wrong_shape, self.other = list(wrong_shape), list(other)
+        self.wrong_shape, self.other, self.wrong_dtype = list(wrong_shape), list(other), list(wrong_dtype)
         lines = [f"{folder}: the weights do not fit the model"]
         if self.missing:
             lines.append(f"  missing ({len(self.missing)}): " + ", ".join(self.missing))
@@ -49,6 +51,9 @@ class WeightError(ValueError):
         if self.wrong_shape:
             lines.append(f"  wrong shape ({len(self.wrong_shape)}): " + ", ".join(
                 f"{n} is {list(got)}, expected {list(want)}" for n, got, want in self.wrong_shape))
+        if self.wrong_dtype:
+            lines.append(f"  wrong element type ({len(self.wrong_dtype)}): " + ", ".join(
+                f"{n} is {got}, expected {want}" for n, got, want in self.wrong_dtype))
         for o in self.other:
             lines.append("  " + o)
         super().__init__("\n".join(lines))
@@ -66,16 +71,26 @@ def storage_dtype(dt: torch.dtype, half_as: torch.dtype = torch.bfloat16) -> tor
     return torch.int32
 
 
+_FLOATS = (torch.float16, torch.bfloat16, torch.float32, torch.float64)
+
+
 def check_names(folder: str, specs: Sequence[ParamSpec], have: Dict[str, Tuple[int, ...]],
-                ignore: Iterable[str] = ()) -> None:
-    """Raise the one WeightError if `have` (name -> shape) does not fit `specs`."""
+                ignore: Iterable[str] = (), dtypes: Optional[Dict[str, torch.dtype]] = None) -> None:
+    """Raise the one WeightError if `have` (name -> shape) and `dtypes` (name -> element type in the file) do not fit `specs`."""
     want = {s.name: s for s in specs}
     ignore = set(ignore)
     missing = [n for n, s in want.items() if n not in have and not s.optional]
     unexpected = [n for n in have if n not in want and n not in ignore]
     wrong = [(n, have[n], s.shape) for n, s in want.items() if n in have and tuple(have[n]) != tuple(s.shape)]
-    if missing or unexpected or wrong:
-        raise WeightError(folder, sorted(missing), sorted(unexpected), sorted(wrong))
+    wrong_dt = []
+    for n, s in want.items():
+        if dtypes is None or n not in dtypes:
+            continue
+        is_float = dtypes[n] in _FLOATS
+        if (s.numbers == "float") != is_float or dtypes[n] == torch.bool:
+            wrong_dt.append((n, str(dtypes[n]).replace("torch.", ""), "a float type" if s.numbers == "float" else "an integer type"))
+    if missing or unexpected or wrong or wrong_dt:
+        raise WeightError(folder, sorted(missing), sorted(unexpected), sorted(wrong), wrong_dtype=sorted(wrong_dt))
 
 
 def load_weights(folder: str, specs: Sequence[ParamSpec], device="cpu", ignore: Iterable[str] = (),
@@ -87,7 +102,7 @@ def load_weights(folder: str, specs: Sequence[ParamSpec], device="cpu", ignore: 
         raise WeightError(folder, [], [], [], [str(e)]) from None
     try:
         have = {n: files.info(n)[1] for n in files.names()}
-        check_names(folder, specs, have, ignore)
+        check_names(folder, specs, have, ignore, {n: files.info(n)[0] for n in files.names()})
         out = {}
         for s in specs:
             if s.name not in have:

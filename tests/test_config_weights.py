@@ -97,11 +97,12 @@ def test_storage_policy(tmp_path):
     t = {"h": torch.randn(4).to(torch.float16), "b": torch.randn(4).to(torch.bfloat16), "f": torch.randn(4),
          "i": torch.arange(4, dtype=torch.int64)}
     save_safetensors(t, str(tmp_path / "model.safetensors"))
-    w = load_weights(str(tmp_path), [ParamSpec(k, (4,)) for k in t])
+    specs = [ParamSpec(k, (4,), numbers="int" if k == "i" else "float") for k in t]
+    w = load_weights(str(tmp_path), specs)
     assert w["h"].dtype == torch.bfloat16 and w["b"].dtype == torch.bfloat16
     assert w["f"].dtype == torch.float32 and torch.equal(w["f"], t["f"])
     assert w["i"].dtype == torch.int32 and w["i"].tolist() == [0, 1, 2, 3]
-    exact = load_weights(str(tmp_path), [ParamSpec(k, (4,)) for k in t], half_as=torch.float32)   # the 32-bit engine
+    exact = load_weights(str(tmp_path), specs, half_as=torch.float32)   # the 32-bit engine
     assert exact["h"].dtype == torch.float32 and torch.equal(exact["h"], t["h"].float()) and exact["b"].dtype == torch.bfloat16
 
 
@@ -124,6 +125,19 @@ def test_random_model_folder_and_seed(tmp_path):
     assert abs(float(n.mean()) - 1.0) < 0.05 and 0.05 < float(n.std()) < 0.15
 
 
+def test_a_table_of_integers_must_be_stored_as_integers(tmp_path):
+    """The other direction: a spec that asks for integers refuses floats, and keeps integers as int32."""
+    specs = [ParamSpec("table", (4,), "zeros", numbers="int"), ParamSpec("w", (2, 2))]
+    save_safetensors({"table": torch.zeros(4), "w": torch.zeros(2, 2)}, str(tmp_path / "model.safetensors"))
+    with pytest.raises(WeightError) as ei:
+        load_weights(str(tmp_path), specs)
+    assert ei.value.wrong_dtype == [("table", "float32", "an integer type")]
+    save_safetensors({"table": torch.arange(4, dtype=torch.int64), "w": torch.zeros(2, 2, dtype=torch.float16)},
+                     str(tmp_path / "model.safetensors"))
+    got = load_weights(str(tmp_path), specs)
+    assert got["table"].dtype == torch.int32 and got["table"].tolist() == [0, 1, 2, 3] and got["w"].dtype == torch.bfloat16
+
+
 def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
     cfg = config_from_dict(tiny.TINY_A)
     spec = get_architecture(cfg.architecture).build_spec(cfg)
@@ -134,10 +148,13 @@ def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
     t["model.layers.0.self_attn.q_proj.bias"] = torch.zeros(64)
     t["lm_head.weight"] = torch.zeros(256, 64)                # tied model with a head of its own
     t["model.layers.0.mlp.down_proj.weight"] = torch.zeros(64, 127)
+    t["model.layers.0.self_attn.o_proj.weight"] = torch.zeros(64, 64, dtype=torch.int32)   # integers under a weight's name
     save_safetensors(t, str(tmp_path / "model.safetensors"))
     with pytest.raises(WeightError) as ei:
         load_weights(str(tmp_path), specs)
     e = ei.value
+    assert e.wrong_dtype == [("model.layers.0.self_attn.o_proj.weight", "int32", "a float type")]
+    assert "wrong element type (1)" in str(e) and "o_proj.weight is int32" in str(e)
     assert e.missing == ["model.layers.1.mlp.up_proj.weight", "model.norm.weight"]
     assert e.unexpected == ["lm_head.weight", "model.layers.0.self_attn.q_proj.bias"]
     assert e.wrong_shape == [("model.layers.0.mlp.down_proj.weight", (64, 127), (64, 128))]

@@ -57,6 +57,56 @@ def test_llama3_scaling_bands():
     assert bool(mid.any()) and bool(((scaled[mid] < base[mid]) & (scaled[mid] > base[mid] / 8)).all())
 
 
+LLAMA3_PINNED = {
+    # (head_dim, theta, factor, low, high, original): {index: (inv_freq, band)}. The values were worked out once from
+    # the rule itself in 50-digit decimal arithmetic, outside every implementation compared here: unscaled
+    # frequency f = theta^(-2i/D), wavelength 2 pi / f; kept below original/high, divided by factor above
+    # original/low, between them f * ((1 - s) / factor + s) with s = (original / wavelength - low) / (high - low).
+    (64, 500000.0, 32.0, 1.0, 4.0, 8192): {0: (1.0, "keep"), 1: (0.6636012376960885, "keep"), 15: (0.0012905479282092638, "mid"),
+                                           17: (9.708287802627673e-05, "mid"), 18: (1.9461638184831125e-05, "div"),
+                                           31: (9.41830672543491e-08, "div")},
+    (128, 500000.0, 8.0, 1.0, 4.0, 8192): {0: (1.0, "keep"), 1: (0.8146172338565447, "keep"), 29: (0.0021665707635033587, "mid"),
+                                           34: (0.0001785078127679964, "mid"), 35: (9.556212353964683e-05, "div"),
+                                           63: (3.068925988914511e-07, "div")},
+    (32, 500000.0, 32.0, 1.0, 4.0, 64): {0: (1.0, "keep"), 1: (0.44036660267178046, "keep"), 2: (0.06713303751104989, "mid"),
+                                         3: (0.0026686593839301753, "div"), 15: (1.4192720251899592e-07, "div")},
+}
+
+
+def test_llama3_scaling_values_are_pinned():
+    """The Llama-3 frequency rule at the 1B's, the 8B's and tiny B's parameters: the product's table builder, the
+    plain implementation and the reference arm's writer (three separately written statements of the rule: vectorised
+    float64, the same in the tests, scalar Python floats) against values worked out by hand in decimal arithmetic,
+    at the first and last index of every band. The reference takes these numbers as data from its exporter
+    (scripts/export.py:104-108), so its golden outputs cover their use and this test covers the rule."""
+    import os
+    import sys
+
+    from hipinfer_b200.parts.rotary import rope_inv_freq
+
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "baseline"))
+    import reference_arm
+
+    for (D, theta, factor, low, high, orig), pins in LLAMA3_PINNED.items():
+        sc = dict(rope_type="llama3", factor=factor, low_freq_factor=low, high_freq_factor=high,
+                  original_max_position_embeddings=orig)
+        ours, plain_v = rope_inv_freq(D, theta, sc), plain.rope_inv_freq(D, theta, sc)
+        arm = torch.tensor(reference_arm.llama3_inv_freq(D, theta, sc), dtype=torch.float64)
+        assert ours.dtype == torch.float32 and ours.shape == (D // 2,)
+        assert torch.equal(ours, plain_v)
+        assert float(((arm - ours.double()).abs() / arm).max()) < 1e-7       # float32 rounding of the stored table
+        for i, (want, _) in pins.items():
+            assert abs(float(ours[i]) - want) <= 6e-8 * want, (D, i, float(ours[i]), want)
+            assert abs(float(arm[i]) - want) <= 1e-12 * want, (D, i, float(arm[i]), want)
+        # the bands are where the pins say: the count of kept, blended and divided frequencies
+        base = plain.rope_inv_freq(D, theta).double()
+        ratio = ours.double() / base
+        kept, divided = int((ratio > 1 - 1e-6).sum()), int((ratio < 1 / factor + 1e-6).sum())
+        first_mid = min(i for i, (_, b) in pins.items() if b == "mid")
+        first_div = min(i for i, (_, b) in pins.items() if b == "div")
+        assert (kept, divided) == (first_mid, D // 2 - first_div)
+
+
 def test_greedy_rules_and_sampling_noise():
     assert plain.argmax_lowest(torch.tensor([1.0, 3.0, 3.0])) == 1
     assert plain.argmax_lowest(torch.tensor([1.0, float("nan"), 9.0])) == 1
