@@ -10,12 +10,6 @@
 
 HB_TL_DEFINE(attn)
 
-#ifndef HB_AD_LATE_TRIGGER
-#define HB_AD_LATE_TRIGGER 0   // 1: dependents start only when every block has its keys; measured 1 to 3 % slower at batch 1 and 8
-#endif
-#ifndef HB_AD_HEAD_FIRST
-#define HB_AD_HEAD_FIRST 0   // 1: blocks next to each other read pieces of the same pages; measured: no difference
-#endif
 #ifndef HB_AD_TMA
 #define HB_AD_TMA 1
 #endif
@@ -66,26 +60,6 @@ __device__ __forceinline__ void ad_load_rows(const __nv_bfloat16* __restrict__ k
   }
 }
 
-#ifdef HB_AD_TIMING
-// A timing build: every block of the last launch leaves its time stamps (entry, loads asked for,
-// the wait over, tile in shared memory, end) and the SM it ran on.
-__device__ unsigned long long g_ad_stamps[8192 * 6];
-__device__ __forceinline__ void ad_stamp(int i) {
-  const unsigned b = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
-  if (threadIdx.x == 0 && b < 8192) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    if (i == 5) { unsigned sm; asm volatile("mov.u32 %0, %%smid;" : "=r"(sm)); t = sm; }
-    g_ad_stamps[b * 6 + i] = t;
-  }
-}
-HB_EXPORT int hb_ad_stamps(unsigned long long* out) {
-  return cudaMemcpyFromSymbol(out, g_ad_stamps, sizeof(g_ad_stamps)) == cudaSuccess ? 0 : -1;
-}
-#define AD_STAMP(i) ad_stamp(i)
-#else
-#define AD_STAMP(i)
-#endif
 
 // One block = one (key chunk, kv head, row). The chunk's keys and values are requested at once
 // with cp.async into swizzled shared memory; each warp then takes 64 keys: S = Q K^T and
@@ -136,17 +110,9 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
   __shared__ int is_last;
   __shared__ __align__(8) uint64_t bars[AD_WARPS];
   __shared__ int abort_flag;
-#if !HB_AD_LATE_TRIGGER
   hb_pdl_launch();
-#endif
-  AD_STAMP(0);
   HB_TL_MARK(0, 0);
-  AD_STAMP(5);
-#if HB_AD_HEAD_FIRST
-  const int t = blockIdx.z, h = blockIdx.x, s = blockIdx.y;   // blocks next to each other read pieces of the same pages
-#else
   const int t = blockIdx.z, h = blockIdx.y, s = blockIdx.x;
-#endif
   // row_req null: a step of single decode rows, row t being request t (and its position the length its request had):
   // one round trip to memory less before the keys can be asked for
   const int rq = row_req ? row_req[t] : t;
@@ -193,9 +159,7 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
         }
       }
     }
-    AD_STAMP(1);
     hb_pdl_wait();
-    AD_STAMP(2);
     HB_TL_MARK(0, 1);
     if (pages_w > 0 && lane == 0) {   // the pages that hold this step's keys
       hb_mbar_expect_tx(&bars[warp], (uint32_t)((pages_w - old_w) * page_bytes));
@@ -217,9 +181,7 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
   }
   ad_load_rows<D>(kc, vc, table, Hkv, h, page_size, k0, 0, n_old, sK, sV, tid);
   hb_cp_async_commit();
-  AD_STAMP(1);
   hb_pdl_wait();
-  AD_STAMP(2);
   ad_load_rows<D>(kc, vc, table, Hkv, h, page_size, k0, n_old, nk, sK, sV, tid);   // this step's keys
   hb_cp_async_commit();
   }
@@ -237,12 +199,6 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
     if (!loaded && lane == 0) atomicExch(status, 1);   // the result is not valid; the host raises
   }
   const int* table_w = table;   // (the loop below asks for a warp's second half itself)
-#if HB_AD_LATE_TRIGGER
-  // the kernels behind this one start (and ask for their weights) only when every block here
-  // has its keys and values: until then the memory system serves the attention alone
-  hb_pdl_launch();
-#endif
-  AD_STAMP(3);
   HB_TL_MARK(0, 2);
 
   float m_run = -INFINITY, l_run = 0.f;  // of row g (a head when g < G), over this warp's keys
@@ -310,7 +266,7 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
       }
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-    const float mn = fmaxf(m_run, mx * scale_log2);   // finite: the pass has at least one key
+    const float mn = fmaxf(m_run, mx * scale_log2);   // mx is a real score here: a pass never runs without a visible key
     const float corr = hb_exp2(m_run - mn);
     m_run = mn;
     float sum = 0.f;
@@ -376,7 +332,6 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
       }
     }
   }
-  AD_STAMP(4);
   HB_TL_MARK(1, 3);   // slot 1: the end of the chunk work; slot 0: the end of the merge
   if (whole) return;
   // the block of this (row, kv head) that ends last adds the chunks, lowest first
@@ -521,11 +476,7 @@ HB_EXPORT int hb_attn_decode(const void* q, const void* kc, const void* vc, long
   if (smem > 200 * 1024) HB_FAIL("hb_attn_decode: %zu bytes of shared memory (chunk %d, head_dim %d)", smem, chunk, D);
   float* pa = workspace;
   float* pm = workspace ? workspace + (size_t)T * Hq * S * D : nullptr;
-#if HB_AD_HEAD_FIRST
-  dim3 grid(Hkv, S, T);
-#else
   dim3 grid(S, Hkv, T);
-#endif
   const __nv_bfloat16 *qq = (const __nv_bfloat16*)q, *kk = (const __nv_bfloat16*)kc, *vv = (const __nv_bfloat16*)vc;
   CUtensorMap mk, mv;
   memset(&mk, 0, sizeof(mk));

@@ -38,31 +38,6 @@ __device__ __forceinline__ uint64_t ft_desc_mn128(uint32_t smem_addr) {
 // kind::f16 instruction descriptor as hb_umma_idesc_bf16, with B read MN-major.
 __host__ __device__ constexpr uint32_t ft_idesc_b_mn(int M, int N) { return hb_umma_idesc_bf16(M, N) | (1u << 16); }
 
-#ifdef HB_FT_TIMING
-__device__ unsigned long long g_ft_stamps[256];
-__device__ unsigned long long g_ft_blocks[4 * 1024];   // every block's entry, set-up, end and SM
-__device__ __forceinline__ void ft_stamp(int i) {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && i < 256) g_ft_stamps[i] = t;
-  const int lin = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
-  if (i >= 200 && lin < 1024) {
-    g_ft_blocks[4 * lin + (i - 200)] = t;
-    unsigned sm;
-    asm volatile("mov.u32 %0, %%smid;" : "=r"(sm));
-    g_ft_blocks[4 * lin + 3] = sm;
-  }
-}
-HB_EXPORT int hb_ft_blocks(unsigned long long* out) {
-  return cudaMemcpyFromSymbol(out, g_ft_blocks, sizeof(g_ft_blocks)) == cudaSuccess ? 0 : -1;
-}
-HB_EXPORT int hb_ft_stamps(unsigned long long* out) {
-  return cudaMemcpyFromSymbol(out, g_ft_stamps, sizeof(g_ft_stamps)) == cudaSuccess ? 0 : -1;
-}
-#define FT_STAMP(i) ft_stamp(i)
-#else
-#define FT_STAMP(i)
-#endif
 
 struct FtBars {
   uint64_t q_full, k_full[2], k_free[2], v_full[2], v_free[2], s_full, s_free, o_full, p_full, p_free;
@@ -100,7 +75,6 @@ __global__ void __launch_bounds__(FT_D == 64 ? 256 : 192, FT_D == 64 ? 2 : 1) fl
   // the step's own metadata (lengths, tables) was copied before the step's first kernel began; everything else
   // that an earlier kernel wrote is read after hb_pdl_wait() below
   hb_pdl_launch();
-  if (threadIdx.x == 0) FT_STAMP(200);   // (timing build) entry; 201: set-up done; 202: the end
   const int n_rows = q_len[req];
   if (n_rows < min_rows || qt * FT_BM >= n_rows) {
     if ((blockIdx.x | blockIdx.y | blockIdx.z) == 0) hb_pdl_wait();   // the grid never ends before the one ahead of it
@@ -144,7 +118,6 @@ __global__ void __launch_bounds__(FT_D == 64 ? 256 : 192, FT_D == 64 ? 2 : 1) fl
   hb_tc_fence_after();
   const uint32_t tmem_s = bar->tmem_slot, tmem_o = tmem_s + FT_BN;  // S: 128 columns, O: head_dim columns
   hb_pdl_wait();   // barriers, shared and tensor memory were set up while the kernel ahead was still running
-  if (threadIdx.x == 0) FT_STAMP(201);
 
   if (warp == 4) {  // ---------------- TMA: lane l brings page l of the tile (the page ids come in one load)
     if (lane == 0) {
@@ -228,9 +201,7 @@ __global__ void __launch_bounds__(FT_D == 64 ? 256 : 192, FT_D == 64 ? 2 : 1) fl
     for (int i = 0; i < n_tiles && ok; i++) {
       const int k_base = (kt_lo + i) * FT_BN;
       const bool need_mask = k_base + FT_BN - 1 > p_first || (window > 0 && k_base < p_last - window + 1);
-      if (threadIdx.x == 0) FT_STAMP(1 + 6 * i);
       if (!__all_sync(0xffffffffu, hb_mbar_wait(&bar->s_full, i & 1, abort_flag))) { ok = false; break; }
-      if (threadIdx.x == 0) FT_STAMP(2 + 6 * i);
       hb_tc_fence_after();
       // the row of S in two halves of 64 keys, the first one read twice (once for the maximum, once for the
       // exponentials): 128 registers a thread is all that lets a new CTA start beside one that is still
@@ -256,7 +227,6 @@ __global__ void __launch_bounds__(FT_D == 64 ? 256 : 192, FT_D == 64 ? 2 : 1) fl
           for (int j = 0; j < 64; j++) mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(sr[j]));
         }
       }
-      if (threadIdx.x == 0) FT_STAMP(3 + 6 * i);
       const float m_tile = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
       const bool grow = m_tile > m_run + FT_SLACK;   // also the first tile with a visible key: m_run is -inf
       float corr = 1.f;
@@ -289,7 +259,6 @@ __global__ void __launch_bounds__(FT_D == 64 ? 256 : 192, FT_D == 64 ? 2 : 1) fl
           sr[j >> 1] = hb_pack_bf16(p0, p1);
         }
         if (hh == 1) {
-          if (threadIdx.x == 0) FT_STAMP(4 + 6 * i);
           if (!__all_sync(0xffffffffu, hb_mbar_wait(&bar->p_free, (i & 1) ^ 1, abort_flag))) { ok = false; break; }
         }
         // 64 keys = eight 16-byte chunks of this row in K block hh of P
@@ -321,10 +290,8 @@ __global__ void __launch_bounds__(FT_D == 64 ? 256 : 192, FT_D == 64 ? 2 : 1) fl
       hb_tc_fence_before();
       hb_fence_proxy_async();
       hb_mbar_arrive(&bar->p_full);
-      if (threadIdx.x == 0) FT_STAMP(5 + 6 * i);
     }
     if (ok && __all_sync(0xffffffffu, hb_mbar_wait(&bar->o_full, (n_tiles - 1) & 1, abort_flag))) {
-      if (threadIdx.x == 0) FT_STAMP(6 + 6 * n_tiles);
       hb_tc_fence_after();
       const float inv = 1.f / l_run;
       __nv_bfloat16* dst = out + ((size_t)(row0 + r) * Hq + hq) * FT_D;
@@ -351,7 +318,6 @@ __global__ void __launch_bounds__(FT_D == 64 ? 256 : 192, FT_D == 64 ? 2 : 1) fl
 
   hb_tc_fence_before();
   __syncthreads();
-  if (threadIdx.x == 0) FT_STAMP(202);
   if (*abort_flag) {
     if (threadIdx.x == 0) atomicExch(status, 1);
     __nanosleep(100000);

@@ -505,16 +505,44 @@ HB_EXPORT int hb_attn_merge(float* workspace, const int* pos, void* out, int out
 }
 
 // ---------------------------------------------------------------------------------------
-// Sampling from 32-bit logits, one block per row. temperature 0: the largest value, the
-// lowest index on ties, NaN above every number, index 0 when all are -inf
-// (src/kernels.cuh:1883-1913). temperature > 0: arg max of logit / temperature + Gumbel noise,
+// Sampling from 32-bit logits. temperature 0: the largest value, the lowest index on ties, NaN
+// above every number, index 0 when all are -inf (the reference's rules, src/kernels.cuh:1883-1913). temperature > 0: arg max of logit / temperature + Gumbel noise,
 // the noise a counter-based hash of (seed, position, index), so a draw does not depend on what
 // else is in the batch.
 // ---------------------------------------------------------------------------------------
-__device__ __forceinline__ bool better(float v, int i, float best, int idx) {
-  const bool vn = v != v, bn = best != best;
-  if (vn != bn) return vn;
-  return (vn || v == best) ? i < idx : v > best;
+// A candidate (value, index) as one 64-bit key whose unsigned order is the rule above, so that the
+// choice over any split of a row is a plain maximum: the high word is the value's bits made
+// monotone (negative floats inverted, the others with the sign bit set; -0 counts as +0; every NaN
+// becomes the largest word), the low word is ~index, so of equal values the lower index wins. Key 0
+// stands for "no candidate" and lies below every real key.
+__device__ __forceinline__ unsigned long long pick_key(float v, int i) {
+  uint32_t hi;
+  if (v != v) {
+    hi = 0xFFFFFFFFu;
+  } else {
+    const uint32_t b = __float_as_uint(v + 0.0f);
+    hi = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+  }
+  return ((unsigned long long)hi << 32) | (uint32_t)~(uint32_t)i;
+}
+__device__ __forceinline__ int pick_index(unsigned long long key) { return key ? (int)~(uint32_t)key : 0; }
+// The largest key of the block in thread 0 (`sh`: one slot per warp).
+__device__ __forceinline__ unsigned long long pick_block_max(unsigned long long key, unsigned long long* sh) {
+  for (int o = 16; o > 0; o >>= 1) {
+    const unsigned long long other = __shfl_xor_sync(0xffffffffu, key, o);
+    key = other > key ? other : key;
+  }
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  if (lane == 0) sh[w] = key;
+  __syncthreads();
+  if (w == 0) {
+    key = lane < nw ? sh[lane] : 0ull;
+    for (int o = 16; o > 0; o >>= 1) {
+      const unsigned long long other = __shfl_xor_sync(0xffffffffu, key, o);
+      key = other > key ? other : key;
+    }
+  }
+  return key;
 }
 __device__ __forceinline__ uint32_t mix32(uint32_t x) {
   x ^= x >> 16; x *= 0x7FEB352Du; x ^= x >> 15; x *= 0x846CA68Bu; x ^= x >> 16;
@@ -527,47 +555,13 @@ __device__ __forceinline__ float sample_uniform(uint32_t seed, uint32_t position
   return ((float)(h >> 8) + 0.5f) * (1.0f / 16777216.0f);
 }
 
-__global__ void __launch_bounds__(1024) sample_kernel(const float* __restrict__ logits, long ld, int V,
-                                                      const float* __restrict__ temperature,
-                                                      const uint32_t* __restrict__ seed, const int* __restrict__ position,
-                                                      int* __restrict__ out) {
-  __shared__ float bv[32];
-  __shared__ int bi[32];
-  hb_pdl_launch();
-  hb_pdl_wait();
-  const float* l = logits + (size_t)blockIdx.x * ld;
-  const float temp = temperature ? temperature[blockIdx.x] : 0.f;
-  const uint32_t sd = seed ? seed[blockIdx.x] : 0u, ps = position ? (uint32_t)position[blockIdx.x] : 0u;
-  float best = -INFINITY;
-  int idx = 0;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    float v = l[i];
-    if (temp > 0.f) v = v / temp - logf(-logf(sample_uniform(sd, ps, (uint32_t)i)));
-    if (better(v, i, best, idx)) { best = v; idx = i; }
-  }
-  for (int o = 16; o > 0; o >>= 1) {
-    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-    const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
-    if (better(ov, oi, best, idx)) { best = ov; idx = oi; }
-  }
-  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-  if (lane == 0) { bv[w] = best; bi[w] = idx; }
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    for (int i = 1; i < (int)(blockDim.x >> 5); i++)
-      if (better(bv[i], bi[i], best, idx)) { best = bv[i]; idx = bi[i]; }
-    out[blockIdx.x] = idx;
-  }
-}
-
-// Two stages for large vocabularies: slices of a row in parallel, then the best of the slices.
-// The comparison is a total order (value, then lower index), so the split does not change the result.
-__global__ void __launch_bounds__(256) sample_slice_kernel(const float* __restrict__ logits, long ld, int V, int slice,
-                                                           const float* __restrict__ temperature,
-                                                           const uint32_t* __restrict__ seed, const int* __restrict__ position,
-                                                           float* __restrict__ part_v, int* __restrict__ part_i) {
-  __shared__ float bv[8];
-  __shared__ int bi[8];
+// Entries [s * slice, (s + 1) * slice) of row blockIdx.y: the best key of the slice to part[row][s], or, when the
+// slice is the whole row (part null), its index to out[row].
+__global__ void __launch_bounds__(1024) sample_slice_kernel(const float* __restrict__ logits, long ld, int V, int slice,
+                                                            const float* __restrict__ temperature,
+                                                            const uint32_t* __restrict__ seed, const int* __restrict__ position,
+                                                            unsigned long long* __restrict__ part, int* __restrict__ out) {
+  __shared__ unsigned long long sh[32];
   hb_pdl_launch();
   hb_pdl_wait();
   const int row = blockIdx.y, s = blockIdx.x;
@@ -575,49 +569,36 @@ __global__ void __launch_bounds__(256) sample_slice_kernel(const float* __restri
   const float temp = temperature ? temperature[row] : 0.f;
   const uint32_t sd = seed ? seed[row] : 0u, ps = position ? (uint32_t)position[row] : 0u;
   const int i0 = s * slice, i1 = min(V, i0 + slice);
-  float best = -INFINITY;
-  int idx = i0 < V ? i0 : 0;
-  for (int i = i0 + threadIdx.x; i < i1; i += 256) {
+  unsigned long long key = 0ull;
+  for (int i = i0 + threadIdx.x; i < i1; i += blockDim.x) {
     float v = l[i];
     if (temp > 0.f) v = v / temp - logf(-logf(sample_uniform(sd, ps, (uint32_t)i)));
-    if (better(v, i, best, idx)) { best = v; idx = i; }
+    const unsigned long long k = pick_key(v, i);
+    key = k > key ? k : key;
   }
-  for (int o = 16; o > 0; o >>= 1) {
-    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-    const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
-    if (better(ov, oi, best, idx)) { best = ov; idx = oi; }
-  }
-  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-  if (lane == 0) { bv[w] = best; bi[w] = idx; }
-  __syncthreads();
+  key = pick_block_max(key, sh);
   if (threadIdx.x == 0) {
-    for (int i = 1; i < 8; i++)
-      if (better(bv[i], bi[i], best, idx)) { best = bv[i]; idx = bi[i]; }
-    part_v[(size_t)row * gridDim.x + s] = best;
-    part_i[(size_t)row * gridDim.x + s] = idx;
+    if (part) part[(size_t)row * gridDim.x + s] = key;
+    else out[row] = pick_index(key);
   }
 }
 
-__global__ void __launch_bounds__(32) sample_final_kernel(const float* __restrict__ part_v, const int* __restrict__ part_i,
-                                                          int n, int* __restrict__ out) {
+// The second stage for large vocabularies: the best of a row's slices (one warp per row).
+__global__ void __launch_bounds__(32) sample_final_kernel(const unsigned long long* __restrict__ part, int n,
+                                                          int* __restrict__ out) {
   hb_pdl_launch();
   hb_pdl_wait();
   const int row = blockIdx.x;
-  float best = -INFINITY;
-  int idx = 0;
-  bool have = false;
+  unsigned long long key = 0ull;
   for (int i = threadIdx.x; i < n; i += 32) {
-    const float v = part_v[(size_t)row * n + i];
-    const int ix = part_i[(size_t)row * n + i];
-    if (!have || better(v, ix, best, idx)) { best = v; idx = ix; have = true; }
+    const unsigned long long k = part[(size_t)row * n + i];
+    key = k > key ? k : key;
   }
   for (int o = 16; o > 0; o >>= 1) {
-    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-    const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
-    const int oh = __shfl_xor_sync(0xffffffffu, (int)have, o);
-    if (oh && (!have || better(ov, oi, best, idx))) { best = ov; idx = oi; have = true; }
+    const unsigned long long other = __shfl_xor_sync(0xffffffffu, key, o);
+    key = other > key ? other : key;
   }
-  if (threadIdx.x == 0) out[row] = idx;
+  if (threadIdx.x == 0) out[row] = pick_index(key);
 }
 
 // Slices per row that hb_sample uses for a vocabulary of V (its workspace holds 2 * rows * slices 32-bit words).
@@ -628,15 +609,17 @@ HB_EXPORT int hb_sample(const float* logits, long ld, int rows, int V, const flo
   if (rows <= 0) return 0;
   if (V <= 0) HB_FAIL("hb_sample: empty vocabulary");
   const int n = hb_sample_slices(V);
+  if (rows > 65535) HB_FAIL("hb_sample: %d rows are beyond the grid limit", rows);
+  if (((uintptr_t)workspace & 7) != 0) HB_FAIL("hb_sample: the workspace must be 8-byte aligned");
   if (n == 1 || !workspace) {
-    hb_launch(sample_kernel, rows, 1024, 0, s, logits, ld, V, temperature, seed, position, out);
+    hb_launch(sample_slice_kernel, dim3(1, rows), 1024, 0, s, logits, ld, V, V, temperature, seed, position,
+              (unsigned long long*)nullptr, out);
   } else {
-    if (rows > 65535) HB_FAIL("hb_sample: %d rows are beyond the grid limit", rows);
-    float* pv = (float*)workspace;
-    int* pi = (int*)workspace + (size_t)rows * n;
+    unsigned long long* part = (unsigned long long*)workspace;     // rows * n keys
     const int slice = (V + n - 1) / n;
-    hb_launch(sample_slice_kernel, dim3(n, rows), 256, 0, s, logits, ld, V, slice, temperature, seed, position, pv, pi);
-    hb_launch(sample_final_kernel, rows, 32, 0, s, (const float*)pv, (const int*)pi, n, out);
+    hb_launch(sample_slice_kernel, dim3(n, rows), 256, 0, s, logits, ld, V, slice, temperature, seed, position, part,
+              (int*)nullptr);
+    hb_launch(sample_final_kernel, rows, 32, 0, s, (const unsigned long long*)part, n, out);
   }
   HB_CHECK_LAUNCH("hb_sample");
   return 0;

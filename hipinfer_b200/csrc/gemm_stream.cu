@@ -22,9 +22,6 @@ HB_TL_DEFINE(stream)
 
 enum { ST_F32 = 0, ST_BF16 = 1, ST_ADD_F32 = 2, ST_SWIGLU_BF16 = 3, ST_SLICES = 4 };
 constexpr int ST_ROWS = 128, ST_BK = 64, ST_W_BYTES = ST_ROWS * ST_BK * 2;
-#ifndef HB_STREAM_L2_AHEAD
-#define HB_STREAM_L2_AHEAD 0   // weight tiles (16 KB) a CTA asks into L2 beyond its shared-memory stages before its inputs are ready; measured: 4, 8 and 16 each make a decode step 1 to 3 % slower
-#endif
 
 // DEEP: the pipeline of a product that is not split along K (many column blocks): six stages,
 // two CTAs per SM; otherwise four (three for 64 tokens) and three CTAs per SM.
@@ -48,29 +45,11 @@ __device__ __forceinline__ void stream_store(int epi, void* C, long ldc, int m, 
   }
 }
 
-#ifdef HB_STREAM_TIMING
-__device__ unsigned long long g_stream_stamps[16];
-__device__ __forceinline__ void hb_stamp(int i) {
-  if (blockIdx.x == 0 && blockIdx.y == 0) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    g_stream_stamps[i] = t;
-  }
-}
-HB_EXPORT int hb_stream_stamps(unsigned long long* out) {
-  return cudaMemcpyFromSymbol(out, g_stream_stamps, sizeof(g_stream_stamps)) == cudaSuccess ? 0 : -1;
-}
-#define HB_STAMP(i) hb_stamp(i)
-#else
-#define HB_STAMP(i)
-#endif
-
 template <int NT, bool DEEP>
 __global__ void __launch_bounds__(192) gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w,
                                                           const __grid_constant__ CUtensorMap map_x, void* C, long ldc,
                                                           int M, int N, int K, int kslice, float* ws, int* counters,
-                                                          int epi, int* status, int defer,
-                                                          const __nv_bfloat16* __restrict__ W, long ldw) {
+                                                          int epi, int* status, int defer) {
   using S = StreamCfg<NT, DEEP>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -82,10 +61,7 @@ __global__ void __launch_bounds__(192) gemm_stream_kernel(const __grid_constant_
   int* is_last = (int*)(tmem_slot + 2);
 
   hb_pdl_launch();
-  if (threadIdx.x == 0) HB_STAMP(0);
-  // timing slots: 0 q/k/v, 1 o, 2 gate/up, 3 down, 4 anything else (by the grid)
-  const int tl = gridDim.y == 8 ? (gridDim.x == 24 ? 0 : 1) : gridDim.y == 3 ? 2 : gridDim.y == 16 ? 3 : 4;
-  HB_TL_MARK(tl, 0);
+  HB_TL_MARK(0, 0);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nb = blockIdx.x, sp = blockIdx.y, ksplit = gridDim.y, NP = gridDim.x * ST_ROWS;
   const int n0 = nb * ST_ROWS, k_begin = sp * kslice, k_end = min(K, k_begin + kslice);
@@ -106,7 +82,6 @@ __global__ void __launch_bounds__(192) gemm_stream_kernel(const __grid_constant_
   __syncthreads();
   hb_tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  if (threadIdx.x == 0) HB_STAMP(1);
 
   if (warp == 4) {
     if (lane == 0) {
@@ -118,8 +93,7 @@ __global__ void __launch_bounds__(192) gemm_stream_kernel(const __grid_constant_
         hb_tma_load_2d(smem + kb * S::STAGE, &map_w, &full[kb], k_begin + kb * ST_BK, n0);
       }
       hb_pdl_wait();
-      HB_STAMP(2);
-      HB_TL_MARK_T(tl, 1, 128);
+      HB_TL_MARK_T(0, 1, 128);
       for (int kb = 0; kb < pre; kb++)
         hb_tma_load_2d(smem + kb * S::STAGE + ST_W_BYTES, &map_x, &full[kb], k_begin + kb * ST_BK, 0);
       for (int kb = pre; kb < num_kb; kb++) {
@@ -137,8 +111,6 @@ __global__ void __launch_bounds__(192) gemm_stream_kernel(const __grid_constant_
       for (int kb = 0; kb < num_kb; kb++) {
         const uint32_t s = kb % S::STAGES, ph = (kb / S::STAGES) & 1;
         if (!hb_mbar_wait(&full[s], ph, abort_flag)) { ok = false; break; }
-        if (kb == 0) HB_STAMP(3);
-        if (kb == num_kb - 1) HB_STAMP(4);
         hb_tc_fence_after();
         const uint64_t dw = hb_umma_desc_k128(hb_smem_u32(smem + s * S::STAGE));
         const uint64_t dx = hb_umma_desc_k128(hb_smem_u32(smem + s * S::STAGE + ST_W_BYTES));
@@ -150,23 +122,10 @@ __global__ void __launch_bounds__(192) gemm_stream_kernel(const __grid_constant_
     }
   } else {
     // epilogue warps: lane = output column n0 + 32 * warp + lane, v[m] = token m
-    if (HB_STREAM_L2_AHEAD > 0) {
-      // idle until the product is done: they ask the weight tiles that will not fit into the
-      // stages into L2 (one 128-byte line of one weight row per thread and tile)
-      const int pre = num_kb < S::STAGES ? num_kb : S::STAGES;
-      const int ahead = num_kb < pre + HB_STREAM_L2_AHEAD ? num_kb : pre + HB_STREAM_L2_AHEAD;
-      const int row = n0 + threadIdx.x;
-      if (row < N)
-        for (int kb = pre; kb < ahead; kb++) {
-          const int k = k_begin + kb * ST_BK;
-          if (k < K) asm volatile("prefetch.global.L2 [%0];" ::"l"(W + (size_t)row * ldw + k));
-        }
-    }
     const bool ok = hb_mbar_wait(done, 0, abort_flag);
-    if (threadIdx.x == 0) HB_STAMP(5);
     hb_tc_fence_after();
     hb_pdl_wait();  // before the first access to memory that earlier kernels wrote or still read
-    HB_TL_MARK(tl, 2);   // (thread 0 is an epilogue thread: the product is done)
+    HB_TL_MARK(0, 2);   // (thread 0 is an epilogue thread: the product is done)
     float v[NT];
 #pragma unroll
     for (int c = 0; c < NT / 16; c++) hb_tmem_ld16(tmem_base + ((uint32_t)(warp * 32) << 16) + c * 16, v + 16 * c);
@@ -187,11 +146,9 @@ __global__ void __launch_bounds__(192) gemm_stream_kernel(const __grid_constant_
     hb_tc_fence_before();
   }
 
-  if (threadIdx.x == 0) HB_STAMP(6);
-  HB_TL_MARK(tl, 3);
+  HB_TL_MARK(0, 3);
   if (ksplit > 1 && !defer) __threadfence();   // only the block that adds the slices in here has to see the others' partials
   __syncthreads();
-  if (threadIdx.x == 0) HB_STAMP(7);
   if (warp == 5) {
     __syncwarp();
     hb_tmem_dealloc(tmem_base, S::TMEM_COLS);
@@ -204,7 +161,6 @@ __global__ void __launch_bounds__(192) gemm_stream_kernel(const __grid_constant_
 
   if (threadIdx.x == 0) *is_last = atomicAdd(&counters[nb], 1) == ksplit - 1;
   __syncthreads();
-  if (threadIdx.x == 0) HB_STAMP(8);
   if (!*is_last) return;
   __threadfence();
   // four consecutive columns per thread, the slices' loads issued four at a time, added in slice order
@@ -243,7 +199,6 @@ __global__ void __launch_bounds__(192) gemm_stream_kernel(const __grid_constant_
     stream_store(epi, C, ldc, m, n + 3, N, acc.w, up.w, gate);
   }
   if (threadIdx.x == 0) counters[nb] = 0;
-  if (threadIdx.x == 0) HB_STAMP(9);
 }
 
 // The slices' partial sums added in slice order and the epilogue applied, four columns per thread,
@@ -318,20 +273,22 @@ HB_EXPORT int hb_gemm_stream_plan(int N, int K, int* kslice, int* ksplit, long* 
 }
 
 template <int NT, bool DEEP>
-static int launch_stream(const CUtensorMap& mw, const CUtensorMap& mx, const __nv_bfloat16* W, long ldw, void* C, long ldc, int M, int N, int K, int kslice,
+static int launch_stream(const CUtensorMap& mw, const CUtensorMap& mx, void* C, long ldc, int M, int N, int K, int kslice,
                          int ksplit, int n_blocks, float* ws, int* counters, int epi, int* status, cudaStream_t s) {
   // from 8 token rows on (measured) the slices are added by a kernel of its own; ST_SLICES leaves them to the consumer
   const int defer = epi == ST_SLICES || (ksplit > 1 && M >= 8);
   using S = StreamCfg<NT, DEEP>;
   auto kern = gemm_stream_kernel<NT, DEEP>;
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[64] = {};      // the attribute belongs to a device: set once on each
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
     if (e != cudaSuccess) HB_FAIL("hb_gemm_stream: %s", cudaGetErrorString(e));
-    configured = true;
+    if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   cudaError_t e = hb_launch(kern, dim3(n_blocks, ksplit), 192, S::TOTAL, s, mw, mx, C, ldc, M, N, K, kslice, ws, counters,
-                            epi, status, defer, W, ldw);
+                            epi, status, defer);
   if (e != cudaSuccess) HB_FAIL("hb_gemm_stream: %s", cudaGetErrorString(e));
   if (defer && epi != ST_SLICES) {
     const int NP = n_blocks * ST_ROWS;
@@ -367,7 +324,7 @@ HB_EXPORT int hb_gemm_stream(const void* A, long lda, const void* W, long ldw, v
   if (hb_make_tensor_map_bf16(&mw, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, ST_ROWS)) return -1;
   if (hb_make_tensor_map_bf16(&mx, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, (uint32_t)NT)) return -1;
   int r;
-#define HB_ST_ARGS mw, mx, (const __nv_bfloat16*)W, ldw, C, ldc, M, N, K, kslice, ksplit, n_blocks, ws, counters, epi, status, s
+#define HB_ST_ARGS mw, mx, C, ldc, M, N, K, kslice, ksplit, n_blocks, ws, counters, epi, status, s
   if (ksplit == 1) {
     if (NT == 16) r = launch_stream<16, true>(HB_ST_ARGS);
     else if (NT == 32) r = launch_stream<32, true>(HB_ST_ARGS);
@@ -431,6 +388,9 @@ HB_EXPORT int hb_gemm_stream_static(const void* A, long lda, const void* W, long
   }
   if (M > 64) HB_FAIL("hb_gemm_stream_static: M = %d is beyond 64 rows", M);
   if (K <= 0 || (K & 7)) HB_FAIL("hb_gemm_stream_static: K = %d must be a positive multiple of 8", K);
+  if (epi < 0 || epi > 3) HB_FAIL("hb_gemm_stream_static: unknown epilogue %d (0 to 3)", epi);
+  if (epi == ST_SWIGLU_BF16 && (N & 31)) HB_FAIL("hb_gemm_stream_static: SwiGLU needs N = %d to be a multiple of 32", N);
+  if (!status) HB_FAIL("hb_gemm_stream_static: no status word");
   int kslice, ksplit, n_blocks;
   long per_token;
   hb_gemm_stream_plan(N, K, &kslice, &ksplit, &per_token, &n_blocks);
@@ -439,7 +399,7 @@ HB_EXPORT int hb_gemm_stream_static(const void* A, long lda, const void* W, long
   if (per_token * NT > (long)HB_STATIC_WS_FLOATS)
     HB_FAIL("hb_gemm_stream_static: M = %d, N = %d, K = %d need %ld floats of scratch; the static array holds %ld", M, N, K,
             per_token * NT, (long)HB_STATIC_WS_FLOATS);
-  if (n_blocks > HB_STATIC_COUNTERS)
+  if (ksplit > 1 && n_blocks > HB_STATIC_COUNTERS)
     HB_FAIL("hb_gemm_stream_static: N = %d needs %d block counters; the static array holds %d", N, n_blocks, HB_STATIC_COUNTERS);
   if (ksplit > 1) {
     // every call shares the arrays and finds what the last one left: the counters this call uses must start at zero
@@ -447,5 +407,5 @@ HB_EXPORT int hb_gemm_stream_static(const void* A, long lda, const void* W, long
     if (e != cudaSuccess) HB_FAIL("hb_gemm_stream_static: clearing the counters: %s", cudaGetErrorString(e));
   }
   return hb_gemm_stream(A, lda, W, ldw, C, ldc, M, N, K, epi, g_static_ws_ptr[dev], (long)HB_STATIC_WS_FLOATS,
-                        g_static_cnt_ptr[dev], HB_STATIC_COUNTERS, status, s);
+                        g_static_cnt_ptr[dev], ksplit > 1 ? HB_STATIC_COUNTERS : n_blocks, status, s);
 }

@@ -162,6 +162,9 @@ class ModelRunner:
         for e in entries:
             if self.cache.release_behind_window(e.request_id):
                 self._np_tables.pop(e.request_id, None)
+        if len(self._np_tables) > len(self.cache.requests):      # requests freed through the cache manager (the scheduler does)
+            for rid in [r for r in self._np_tables if not self.cache.has_request(r)]:
+                del self._np_tables[rid]
         self.steps_run += 1
         return logits
 
@@ -204,15 +207,18 @@ class ModelRunner:
             static = torch.zeros(n_int, dtype=torch.int32, device=self.device)
             batch = build_step_batch(entries, ctx_lens, slots, tables, slot_maps, static=static, token_map=token_map, **args)
             self._feed(batch.tokens, batch.token_map, device_tokens, token_map)
-            self.model.forward(batch, self.storage)            # warm-up: allocations, plans, lazy set-up
+            first = self.model.forward(batch, self.storage)    # this step itself, run eagerly: allocations, plans, lazy set-up
             torch.cuda.synchronize()
             from ..kernels import library
             before = library.launches[0]
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
+            with torch.cuda.graph(graph):                      # recorded, not run
                 logits = self.model.forward(batch, self.storage)
-            g = self._graphs[R] = dict(graph=graph, static=static, logits=logits, tokens=batch.tokens,
-                                       token_map=batch.token_map, launches=library.launches[0] - before)
+            self._graphs[R] = dict(graph=graph, static=static, logits=logits, tokens=batch.tokens,
+                                   token_map=batch.token_map, launches=library.launches[0] - before)
+            # the step has run once already: replaying the graph now would run it a second time, which a mixer
+            # with state of its own (its state advances with every run) must not see
+            return first
         else:
             build_step_batch(entries, ctx_lens, slots, tables, slot_maps, static=g["static"], token_map=token_map, **args)
             self._feed(g["tokens"], g["token_map"], device_tokens, token_map)

@@ -19,8 +19,6 @@ PLAIN_ONLY = os.environ.get("HIPINFER_B200_PLAIN", "0") == "1"
 _p, _i, _l, _f = C.c_void_p, C.c_int, C.c_long, C.c_float
 _SIGS = {
     "hb_gemm_tc": [_p, _l, _p, _l, _p, _l, _i, _i, _i, _i, _i, _p, _p],
-    "hb_gemm_skinny": [_p, _l, _p, _l, _p, _l, _i, _i, _i, _i, _p, _l, _p, _i, _p],
-    "hb_gemm_skinny_plan": [_i, _i, _p, _p, _p, _p],
     "hb_gemm_stream": [_p, _l, _p, _l, _p, _l, _i, _i, _i, _i, _p, _l, _p, _i, _p, _p],
     "hb_gemm_stream_plan": [_i, _i, _p, _p, _p, _p],
     "hb_gemm_stream_finish": [_p, _p, _l, _i, _i, _i, _i, _p],
@@ -36,7 +34,7 @@ _SIGS = {
     "hb_wait_selftest": [_p, _i, _p, _p],
 }
 _fns = {}
-_LAUNCHES = {"hb_gemm_tc_rope_kv": 1, "hb_gemm_stream_finish": 1, "hb_add_rmsnorm_slices": 1, "hb_rope_kv_slices": 1, "hb_gemm_tc": 1, "hb_gemm_skinny": 1, "hb_gemm_stream": 1, "hb_attn_decode": 1, "hb_flash_prefill": 1, "hb_flash_prefill_tc": 1}
+_LAUNCHES = {"hb_gemm_tc_rope_kv": 1, "hb_gemm_stream_finish": 1, "hb_add_rmsnorm_slices": 1, "hb_rope_kv_slices": 1, "hb_gemm_tc": 1, "hb_gemm_stream": 1, "hb_attn_decode": 1, "hb_flash_prefill": 1, "hb_flash_prefill_tc": 1}
 _status = None
 
 EPI_F32, EPI_BF16, EPI_ADD_F32, EPI_SWIGLU_BF16, EPI_SLICES = 0, 1, 2, 3, 4
@@ -108,23 +106,13 @@ def gemm_tc(a, w, out, epi, tile_n=0):
     return out
 
 
-SKINNY_MAX_ROWS = 64      # rows up to which the weight-streaming kernel is used instead of the tcgen05 kernel
+STREAM_MAX_ROWS = 64      # rows up to which the weight-streaming kernel is used instead of the tcgen05 kernel
 _scratch = {}
 _retired = []
 _plans = {}
 
 
-def skinny_plan(N, K):
-    """(kslice, ksplit, workspace floats per padded token row, column blocks) for an [N, K] weight."""
-    key = (N, K)
-    if key not in _plans:
-        ks, sp, nb, per = C.c_int(), C.c_int(), C.c_int(), C.c_long()
-        _call("hb_gemm_skinny_plan", N, K, C.byref(ks), C.byref(sp), C.byref(per), C.byref(nb))
-        _plans[key] = (ks.value, sp.value, per.value, nb.value)
-    return _plans[key]
-
-
-def _skinny_scratch(device, ws_floats, n_counters):
+def _stream_scratch(device, ws_floats, n_counters):
     """Workspace and zeroed counters shared by all small-batch products of this device and stream
     order; they grow on demand (kernels that share them run one after the other)."""
     sc = _scratch.get(device)
@@ -138,19 +126,6 @@ def _skinny_scratch(device, ws_floats, n_counters):
 
 
 _scratch_gen = [0]       # counts the products that wrote the shared scratch: slices left there are valid until the next one
-
-
-def gemm_skinny(a, w, out, epi):
-    """The weight-streaming kernel itself (M <= 64): out per `epi` (see csrc/gemm_skinny.cu)."""
-    M, K = a.shape
-    N = w.shape[0]
-    _scratch_gen[0] += 1
-    _, _, per_row, n_blocks = skinny_plan(N, K)
-    mp = 8 if M <= 8 else 16 if M <= 16 else 32 if M <= 32 else 64
-    ws, cnt = _skinny_scratch(a.device, per_row * mp, n_blocks)
-    _call("hb_gemm_skinny", a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0), M, N, K,
-          epi, ws.data_ptr(), ws.numel(), cnt.data_ptr(), cnt.numel(), _stream())
-    return out
 
 
 def stream_plan(N, K):
@@ -169,7 +144,7 @@ def gemm_stream(a, w, out, epi):
     N = w.shape[0]
     _, _, per_token, n_blocks = stream_plan(N, K)
     nt = 16 if M <= 16 else 32 if M <= 32 else 64
-    ws, cnt = _skinny_scratch(a.device, per_token * nt, n_blocks)
+    ws, cnt = _stream_scratch(a.device, per_token * nt, n_blocks)
     _scratch_gen[0] += 1
     if stream_plan(N, K)[1] > 1 and M >= 8:
         library.launches[0] += 1     # the slices are added by a kernel of its own (counted here, launched by the call below)
@@ -195,7 +170,7 @@ def gemm_stream_slices(a, w) -> Slices:
     N = w.shape[0]
     _, ksplit, per_token, n_blocks = stream_plan(N, K)
     nt = 16 if M <= 16 else 32 if M <= 32 else 64
-    ws, cnt = _skinny_scratch(a.device, per_token * nt, n_blocks)
+    ws, cnt = _stream_scratch(a.device, per_token * nt, n_blocks)
     _scratch_gen[0] += 1
     _call("hb_gemm_stream", a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), None, 0, M, N, K, EPI_SLICES,
           ws.data_ptr(), ws.numel(), cnt.data_ptr(), cnt.numel(), status_word().data_ptr(), _stream())
@@ -241,18 +216,16 @@ def rope_kv_slices(sl: Slices, positions, slot_map, table, q_out, k_cache, v_cac
 
 def linear_slices(a, w):
     """a @ w.T as slices when the small-product kernel applies (a few bf16 rows), else None."""
-    if a.shape[0] > SKINNY_MAX_ROWS or SMALL_IMPL != "stream" or DEFER_OFF or not _tc_ok(a, w.t):
+    if a.shape[0] > STREAM_MAX_ROWS or not _tc_ok(a, w.t):
         return None
     return gemm_stream_slices(a, w.t)
 
 
-SMALL_IMPL = os.environ.get("HIPINFER_B200_SMALL_GEMM", "stream")   # "stream" (tcgen05) or "skinny" (mma.sync)
-DEFER_OFF = os.environ.get("HIPINFER_B200_DEFER", "1") == "0"        # "0": every product adds its own slices
 
 
 def _gemm(a, w, out, epi):
-    if a.shape[0] <= SKINNY_MAX_ROWS:
-        return gemm_stream(a, w, out, epi) if SMALL_IMPL == "stream" else gemm_skinny(a, w, out, epi)
+    if a.shape[0] <= STREAM_MAX_ROWS:
+        return gemm_stream(a, w, out, epi)
     return gemm_tc(a, w, out, epi)
 
 
@@ -269,14 +242,13 @@ def linear(a, w, out, accumulate) -> bool:
     return True
 
 
-ROPE_FUSED_OFF = os.environ.get("HIPINFER_B200_ROPE_FUSED", "1") == "0"   # "0": the projection and the rotation as two kernels
 
 
 def linear_rope_kv(a, w, positions, slot_map, table, q_out, k_cache, v_cache, n_heads, n_kv_heads, head_dim, rotary_dim,
                    page_size) -> bool:
     """The q/k/v projection of more than a few rows with the rotation and the cache write in its epilogue
     (csrc/gemm_tc.cu, EPI_ROPE_KV); False where no kernel takes these sizes (heads of 64, rotated whole)."""
-    if (ROPE_FUSED_OFF or a.shape[0] <= SKINNY_MAX_ROWS or head_dim != 64 or rotary_dim != 64 or not _tc_ok(a, w.t)
+    if (a.shape[0] <= STREAM_MAX_ROWS or head_dim != 64 or rotary_dim != 64 or not _tc_ok(a, w.t)
             or w.shape[0] != (n_heads + 2 * n_kv_heads) * 64 or q_out.dtype != torch.bfloat16 or not q_out.is_contiguous()
             or table.dtype != torch.float32 or not table.is_contiguous()):
         return False
@@ -299,7 +271,7 @@ def linear_swiglu(a, w, act_out, group) -> bool:
 
 
 DECODE_CHUNK = 256      # keys per split of the decode attention kernel (absolute positions)
-DECODE_CHUNK_64 = int(os.environ.get("HIPINFER_B200_DECODE_CHUNK_64", "512"))
+DECODE_CHUNK_64 = 512   # at head_dim 64 without a window: a warp walks 128 keys in two passes
 
 
 def decode_chunk(head_dim: int, window: int = 0) -> int:
@@ -363,7 +335,6 @@ def flash_prefill(q, k_cache, v_cache, block_table, q_start, q_len, ctx_len, out
     return out
 
 
-FLASH_IMPL = os.environ.get("HIPINFER_B200_FLASH", "tc")      # "tc": tcgen05 where it applies; "mma": warp MMAs only
 
 
 def flash_prefill_tc_supported(n_heads, n_kv_heads, head_dim, page_size) -> bool:
@@ -390,7 +361,7 @@ def attention(q, k_cache, v_cache, batch, group, out, n_heads, n_kv_heads, head_
     need_rows = not use_flash or min(batch.h_q_len) < FLASH_MIN_ROWS
     bt = batch.block_tables[group]
     if use_flash:
-        tc = FLASH_IMPL == "tc" and flash_prefill_tc_supported(n_heads, n_kv_heads, head_dim, page_size)
+        tc = flash_prefill_tc_supported(n_heads, n_kv_heads, head_dim, page_size)    # else: warp MMAs (other page sizes)
         (flash_prefill_tc if tc else flash_prefill)(q, k_cache, v_cache, bt, batch.req_q_start, batch.req_q_len,
                                                     batch.req_ctx_len, out, batch.max_q_len, n_heads, n_kv_heads,
                                                     head_dim, page_size, window, scale, FLASH_MIN_ROWS)

@@ -45,7 +45,7 @@ def timeit(fn, iters, flush):
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
-    ap.add_argument("kernel", choices=["gemm_tc", "gemm_stream", "gemm_skinny", "attn_decode", "flash_prefill", "flash_prefill_tc", "rmsnorm"])
+    ap.add_argument("kernel", choices=["gemm_tc", "gemm_stream", "attn_decode", "flash_prefill", "flash_prefill_tc", "rmsnorm"])
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=16384)
     ap.add_argument("--k", type=int, default=2048)
@@ -74,10 +74,8 @@ def main(argv=None) -> int:
         c = torch.zeros(M, N // 2 if epi == 3 else N, device=dev, dtype=torch.bfloat16 if epi in (1, 3) else torch.float32)
         if a.kernel == "gemm_tc":
             fn = lambda: fast.gemm_tc(x, w, c, epi, a.tile_n)
-        elif a.kernel == "gemm_stream":
-            fn = lambda: fast.gemm_stream(x, w, c, epi)
         else:
-            fn = lambda: fast.gemm_skinny(x, w, c, epi)
+            fn = lambda: fast.gemm_stream(x, w, c, epi)
         ms = timeit(fn, a.iters, a.flush)
         nbytes = N * K * 2 + M * K * 2 + c.numel() * c.element_size()
         out.update(M=M, N=N, K=K, epi=a.epi, ms=ms, tflops=2.0 * M * N * K / ms / 1e9, gbs=nbytes / ms / 1e6)

@@ -14,9 +14,7 @@ def llama_spec(c: LlamaConfig) -> ModelSpec:
                                      scaling=c.rope_scaling.to_dict() if c.rope_scaling else None, pairing="half"))
     layers = []
     for l in range(c.num_hidden_layers):
-        layers.append(LayerSpec(
-            prefix=f"model.layers.{l}.",
-            block="pre_norm",
+        layers.append(LayerSpec(prefix=f"model.layers.{l}.", block="pre_norm", parts=dict(
             mixer=PartSpec("attention", dict(hidden_size=c.hidden_size, n_heads=c.num_attention_heads,
                                              n_kv_heads=c.num_key_value_heads, head_dim=c.head_dim, window=0,
                                              position=position)),
@@ -24,7 +22,7 @@ def llama_spec(c: LlamaConfig) -> ModelSpec:
             feed_forward=PartSpec("swiglu", dict(hidden_size=c.hidden_size, intermediate_size=c.intermediate_size)),
             feed_forward_norm=PartSpec("rmsnorm", dict(name="post_attention_layernorm.weight", size=c.hidden_size,
                                                        eps=c.rms_norm_eps)),
-        ))
+        )))
     embed_name = "model.embed_tokens.weight"
     head = dict(vocab_size=c.vocab_size, hidden_size=c.hidden_size)
     head.update(dict(tied_to=embed_name) if c.tie_word_embeddings else dict(name="lm_head.weight"))

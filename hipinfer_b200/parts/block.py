@@ -1,22 +1,38 @@
 """Arrangements of a layer's parts. "pre_norm": x += mixer(norm(x)); x += feed_forward(norm(x)),
-the order of the reference's attn_rows and mlp_rows (src/api.cu:1673, 1712)."""
+the order of the reference's attn_rows and mlp_rows (src/api.cu:1673, 1712).
+
+A block kind declares its slots (`SLOTS`: slot name -> registry role) and builds the parts the
+`LayerSpec` gives under those names; a layer that gives other names, or lacks one, is refused
+with a message. Every block has an attribute `mixer`: the part whose `cache_need()` and
+`state_need()` the cache manager serves."""
 from __future__ import annotations
 
 from ..kernels import ops
 from .registry import Part, build_part, register_part
 
 
+def build_slots(block: Part, layer, slots, ctx, prefix) -> list:
+    """Builds the parts of `layer` (a LayerSpec) for the slots {name: role} of a block kind, sets each as the
+    attribute of its slot name on `block`, and returns them in the slots' order."""
+    extra = sorted(set(layer.parts) - set(slots))
+    if extra:
+        raise ValueError(f"layer {layer.prefix!r}: block {layer.block!r} has no part {extra}; its parts are {sorted(slots)}")
+    built = []
+    for name, role in slots.items():
+        part = build_part(role, layer.part(name), ctx, prefix)
+        setattr(block, name, part)
+        built.append(part)
+    return built
+
+
 class PreNormBlock(Part):
     """params: layer (the LayerSpec)."""
 
+    SLOTS = {"mixer_norm": "norm", "mixer": "mixer", "feed_forward_norm": "norm", "feed_forward": "feed_forward"}
+
     def __init__(self, params, ctx, prefix=""):
         super().__init__(params, ctx, prefix)
-        ls = params["layer"]
-        self.mixer_norm = build_part("norm", ls.mixer_norm, ctx, prefix)
-        self.mixer = build_part("mixer", ls.mixer, ctx, prefix)
-        self.feed_forward_norm = build_part("norm", ls.feed_forward_norm, ctx, prefix)
-        self.feed_forward = build_part("feed_forward", ls.feed_forward, ctx, prefix)
-        self.parts = [self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward]
+        self.parts = build_slots(self, params["layer"], self.SLOTS, ctx, prefix)
 
     def param_specs(self):
         return [s for p in self.parts for s in p.param_specs()]

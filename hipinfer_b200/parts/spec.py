@@ -4,8 +4,11 @@ and in which order the layers run. An architecture is a function from its config
 and knows nothing else about the architecture.
 
 - A `PartSpec` names a registered kind and carries every size and constant the part needs.
-- A `LayerSpec` names the arrangement of a block (for instance "pre_norm"), its mixer, its
-  feed-forward and their norms, chosen layer by layer: layers of one model may differ.
+- A `LayerSpec` names the arrangement of a block (for instance "pre_norm") and gives the block's
+  parts as a mapping from slot name to `PartSpec`. Which slots there are is the block kind's
+  business ("pre_norm": mixer_norm, mixer, feed_forward_norm, feed_forward; a block with norms
+  after its mixer and feed-forward as well, or one norm shared by both, is another block kind
+  with other slots and needs no change here). Chosen layer by layer: layers of one model may differ.
 - `order` is the list of steps in which layers run. A step may name a layer that an earlier
   step named (its weights are used again, with a cache of its own), or say that its mixer
   reads the cache of an earlier step instead of keeping one.
@@ -15,7 +18,7 @@ The reference has one hard-wired graph (src/api.cu:1728-1765, 1891-1952).
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any, Dict, List, Optional, Tuple
+from typing import Any, Dict, List, Mapping, Optional, Tuple
 
 
 @dataclass(frozen=True)
@@ -26,12 +29,16 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    prefix: str            # tensor-name prefix of the layer, e.g. "model.layers.3."
-    block: str             # arrangement kind
-    mixer: PartSpec
-    mixer_norm: PartSpec
-    feed_forward: PartSpec
-    feed_forward_norm: PartSpec
+    prefix: str                       # tensor-name prefix of the layer, e.g. "model.layers.3."
+    block: str                        # arrangement kind
+    parts: Mapping[str, PartSpec]     # slot name -> part; the block kind says which slots it has
+
+    def part(self, slot: str) -> PartSpec:
+        try:
+            return self.parts[slot]
+        except KeyError:
+            raise KeyError(f"layer {self.prefix!r}: block {self.block!r} asks for a part {slot!r}; the layer gives "
+                           f"{sorted(self.parts)}") from None
 
 
 @dataclass(frozen=True)

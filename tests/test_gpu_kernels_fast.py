@@ -139,7 +139,7 @@ def test_gemm_tc_strided_views():
 # ------------------------------------------------------------------------------------------
 # the weight-streaming kernel for small batches
 # ------------------------------------------------------------------------------------------
-IMPLS = ["skinny", "stream"]
+IMPLS = ["stream"]
 
 
 def small(impl):

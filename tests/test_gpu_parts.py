@@ -175,14 +175,22 @@ def _register_toy():
             return {"h": ((self.hidden,), torch.float32)}
 
         def forward(self, xn, x, batch, cache, state):
+            """Indexed with the batch's DEVICE arrays only (row -> request, first row, rows and state slot of a
+            request), with no loop over requests on the host: the same code is recorded into the CUDA graph of
+            decode-only steps and replayed with other requests in the rows."""
             assert cache is None
-            for r in range(batch.n_requests):
-                s, n, slot = batch.h_q_start[r], batch.h_q_len[r], batch.h_state_slot[r]
-                h = state["h"][slot].clone()
-                for i in range(n):
-                    h = self.a * h + xn[s + i].float()
-                    x[s + i] += h @ self.w.T
-                state["h"][slot] = h
+            T = xn.shape[0]
+            req = batch.row_request.long()
+            t = torch.arange(T, device=xn.device)
+            j = t - batch.req_q_start.long()[req]                       # a row's place within its request's rows
+            slots = batch.req_state_slot.long()
+            same = req[:, None] == req[None, :]
+            lag = (t[:, None] - t[None, :]).clamp(min=0).float()
+            mix = torch.where(same & (t[:, None] >= t[None, :]), self.a ** lag, torch.zeros((), device=xn.device))
+            h = mix @ xn.float() + (self.a ** (j + 1).float())[:, None] * state["h"][slots[req]]
+            x += h @ self.w.T
+            last = batch.req_q_start.long() + batch.req_q_len.long() - 1
+            state["h"][slots] = h[last]
 
     @dataclass(frozen=True)
     class ToyConfig(ModelConfig):
@@ -213,8 +221,9 @@ def _register_toy():
         att = lambda window: PartSpec("attention", dict(hidden_size=H, n_heads=c.n_heads, n_kv_heads=c.n_kv_heads,
                                                         head_dim=c.head_dim, window=window, position=pos))
         mixers = [att(0), PartSpec("toy_decay", dict(hidden_size=H, decay=c.decay)), att(c.window)]
-        layers = tuple(LayerSpec(f"toy.layers.{i}.", "pre_norm", m, norm("input_layernorm.weight"), ffn,
-                                 norm("post_attention_layernorm.weight")) for i, m in enumerate(mixers))
+        layers = tuple(LayerSpec(f"toy.layers.{i}.", "pre_norm", dict(
+            mixer=m, mixer_norm=norm("input_layernorm.weight"), feed_forward=ffn,
+            feed_forward_norm=norm("post_attention_layernorm.weight"))) for i, m in enumerate(mixers))
         order = (RunStep(0), RunStep(1), RunStep(2), RunStep(1), RunStep(0, reads_cache_of=0))
         return ModelSpec(c.architecture, H, c.vocab_size, 256,
                          PartSpec("token", dict(name="toy.embed.weight", vocab_size=c.vocab_size, hidden_size=H)), layers, order,
@@ -283,7 +292,7 @@ def test_toy_architecture_registered_from_the_test(dtype):
     tensors = random_weights(spec_param_specs(spec), seed=9, std=0.08, norm_std=0.1, dtype=torch.bfloat16)
     assert "toy.layers.1.decay.weight" in tensors and "toy.layers.1.self_attn.q_proj.weight" not in tensors
     runner = ModelRunner(cfg, {k: v.to(DEV) for k, v in tensors.items()}, dtype=dtype, num_pages=40, max_model_len=256,
-                         max_num_seqs=4, cuda_graphs=False)   # the toy mixer reads host mirrors of the batch
+                         max_num_seqs=4)      # CUDA graphs on: decode-only steps are replayed, the mixer's state with them
     m = runner.model
     assert [(g.kind, g.n_layers, g.window) for g in m.cache_groups] == [("full", 1, 0), ("window", 1, 40)]
     assert [p and (p.group, p.slot, p.write) for p in m.cache_plan] == [(0, 0, True), None, (1, 0, True), None, (0, 0, False)]
@@ -293,12 +302,13 @@ def test_toy_architecture_registered_from_the_test(dtype):
     ref = {rid: toy_plain(TOY, w, toks) for rid, toks in requests.items()}
     st = tiny.RunnerStepper(runner)
     for name, plan in (("whole", tiny.plan_whole(requests)), ("portions", tiny.plan_portions(requests)),
-                       ("mixed", tiny.plan_mixed(requests, 3))):
+                       ("tail", tiny.plan_tail_decode(requests, 12)), ("mixed", tiny.plan_mixed(requests, 3))):
         got = tiny.run_plan(st, requests, plan)
         for rid in requests:
-            tiny.assert_logits_close(got[rid], ref[rid], dtype, f"toy {name} {rid}")
+            tiny.assert_logits_close(got[rid], ref[rid], dtype, f"toy {name} {rid}", group=("toy architecture", name))
         runner.cache.check()
         assert runner.cache.free_pages() == [40, 40] and runner.cache.slots.free_count == 4
+    assert runner._graphs, "no decode-only step went through a CUDA graph"
     # the window group gives pages back while a long request is still running; the full group does not
     from hipinfer_b200.engine import StepEntry
     runner.step([StepEntry("long", requests["t0"], [])])
@@ -311,12 +321,48 @@ def test_toy_architecture_registered_from_the_test(dtype):
 # A second toy architecture: a position encoding and a feed-forward of its own kind.
 #   layer 0: attention with "toy_decay_position" (no rotation: q_t is scaled by e^(+l t), k_s by e^(-l s), so a
 #            score carries the factor e^(l (t - s))) + "toy_top1_experts" (a router picks one of E small experts)
-#   layer 1: attention with rope + SwiGLU
+#   layer 1: attention with rope + SwiGLU in a block kind of its own, "toy_sandwich", which has six parts: a norm
+#            before AND after the mixer, and before and after the feed-forward
 # ------------------------------------------------------------------------------------------
 def _register_toy2():
     from hipinfer_b200.config import ModelConfig, register_architecture, take
     from hipinfer_b200.parts import LayerSpec, ModelSpec, Part, PartSpec, RunStep, register_part
+    from hipinfer_b200.parts.block import build_slots
     from hipinfer_b200.weights import ParamSpec
+
+    class SandwichBlock(Part):
+        """x += post_norm(mixer(pre_norm(x))); x += post_norm(feed_forward(pre_norm(x))). Mixers and feed-forwards add
+        into the rows they are given, so each gets rows of zeros, whose norm is then added into x."""
+
+        SLOTS = {"mixer_norm": "norm", "mixer": "mixer", "mixer_post_norm": "norm", "feed_forward_norm": "norm",
+                 "feed_forward": "feed_forward", "feed_forward_post_norm": "norm"}
+
+        def __init__(self, params, ctx, prefix=""):
+            super().__init__(params, ctx, prefix)
+            self.parts = build_slots(self, params["layer"], self.SLOTS, ctx, prefix)
+
+        def param_specs(self):
+            return [s for p in self.parts for s in p.param_specs()]
+
+        def load(self, tensors):
+            for p in self.parts:
+                p.load(tensors)
+
+        def weight_bytes(self):
+            return sum(p.weight_bytes() for p in self.parts)
+
+        @staticmethod
+        def _done(left):
+            if left is not None and hasattr(left, "finish"):
+                left.finish()
+
+        def forward(self, x, batch, cache, state):
+            y = torch.zeros_like(x)
+            self._done(self.mixer.forward(self.mixer_norm.forward(x), y, batch, cache, state))
+            x += self.mixer_post_norm.forward(y).float()
+            y = torch.zeros_like(x)
+            self._done(self.feed_forward.forward(self.feed_forward_norm.forward(x), y, batch))
+            x += self.feed_forward_post_norm.forward(y).float()
 
     class DecayPosition(Part):
         """params: head_dim, rate. It has no `pending` argument: the mixer finishes its product first."""
@@ -392,13 +438,19 @@ def _register_toy2():
                   att(PartSpec("rope", dict(head_dim=c.head_dim, theta=10000.0, scaling=None)))]
         ffns = [PartSpec("toy_top1_experts", dict(hidden_size=H, inner_size=c.intermediate_size, n_experts=c.n_experts)),
                 PartSpec("swiglu", dict(hidden_size=H, intermediate_size=c.intermediate_size))]
-        layers = tuple(LayerSpec(f"toy2.layers.{i}.", "pre_norm", mixers[i], norm("input_layernorm.weight"), ffns[i],
-                                 norm("post_attention_layernorm.weight")) for i in range(2))
+        layers = (LayerSpec("toy2.layers.0.", "pre_norm", dict(
+                      mixer=mixers[0], mixer_norm=norm("input_layernorm.weight"), feed_forward=ffns[0],
+                      feed_forward_norm=norm("post_attention_layernorm.weight"))),
+                  LayerSpec("toy2.layers.1.", "toy_sandwich", dict(
+                      mixer=mixers[1], mixer_norm=norm("input_layernorm.weight"), mixer_post_norm=norm("post_mixer_norm.weight"),
+                      feed_forward=ffns[1], feed_forward_norm=norm("post_attention_layernorm.weight"),
+                      feed_forward_post_norm=norm("post_feed_forward_norm.weight"))))
         return ModelSpec(c.architecture, H, c.vocab_size, 256,
                          PartSpec("token", dict(name="toy2.embed.weight", vocab_size=c.vocab_size, hidden_size=H)), layers,
                          (RunStep(0), RunStep(1)), norm("toy2.norm.weight"),
                          PartSpec("linear", dict(tied_to="toy2.embed.weight", vocab_size=c.vocab_size, hidden_size=H)))
 
+    register_part("block", "toy_sandwich", SandwichBlock)
     register_part("position", "toy_decay_position", DecayPosition)
     register_part("feed_forward", "toy_top1_experts", Top1Experts)
     register_architecture("Toy2ForCausalLM", Toy2Config, toy2_spec)
@@ -428,12 +480,14 @@ def toy2_plain(c, w, tokens):
     for i in range(T):
         e = int(p[i].argmax())
         x[i] = x[i] + p[i, e] * (w2[e] @ torch.relu(w1[e] @ xn[i]))
-    # layer 1: the architecture's own parts
+    # layer 1: the architecture's own parts, each between two norms
     inv = plain.rope_inv_freq(D, 10000.0)
-    x = x + plain.attention_block(plain.rmsnorm(x, w[p1 + "input_layernorm.weight"], c["eps"]),
-                                  *(w[p1 + f"self_attn.{n}_proj.weight"] for n in "qkvo"), pos, Hq, Hkv, D, inv)
-    x = x + plain.swiglu_mlp(plain.rmsnorm(x, w[p1 + "post_attention_layernorm.weight"], c["eps"]),
-                             *(w[p1 + f"mlp.{n}_proj.weight"] for n in ("gate", "up", "down")))
+    y = plain.attention_block(plain.rmsnorm(x, w[p1 + "input_layernorm.weight"], c["eps"]),
+                              *(w[p1 + f"self_attn.{n}_proj.weight"] for n in "qkvo"), pos, Hq, Hkv, D, inv)
+    x = x + plain.rmsnorm(y, w[p1 + "post_mixer_norm.weight"], c["eps"])
+    y = plain.swiglu_mlp(plain.rmsnorm(x, w[p1 + "post_attention_layernorm.weight"], c["eps"]),
+                         *(w[p1 + f"mlp.{n}_proj.weight"] for n in ("gate", "up", "down")))
+    x = x + plain.rmsnorm(y, w[p1 + "post_feed_forward_norm.weight"], c["eps"])
     return plain.lm_head(x, w["toy2.norm.weight"], w["toy2.embed.weight"], c["eps"])
 
 
@@ -450,6 +504,7 @@ def test_toy_position_encoding_and_routed_feed_forward():
     spec = get_architecture("Toy2ForCausalLM").build_spec(cfg)
     tensors = random_weights(spec_param_specs(spec), seed=11, std=0.08, norm_std=0.1, dtype=torch.float32)
     assert "toy2.layers.0.moe.router.weight" in tensors and "toy2.layers.0.mlp.gate_proj.weight" not in tensors
+    assert "toy2.layers.1.post_mixer_norm.weight" in tensors and "toy2.layers.0.post_mixer_norm.weight" not in tensors
     runner = ModelRunner(cfg, {k: v.to(DEV) for k, v in tensors.items()}, dtype="float32", num_pages=30, max_model_len=256,
                          max_num_seqs=4, cuda_graphs=False)
     w = {k: v.float() for k, v in tensors.items()}
@@ -460,7 +515,7 @@ def test_toy_position_encoding_and_routed_feed_forward():
                        ("mixed", tiny.plan_mixed(requests, 3))):
         got = tiny.run_plan(st, requests, plan)
         for rid in requests:
-            tiny.assert_logits_close(got[rid], ref[rid], "float32", f"toy2 {name} {rid}")
+            tiny.assert_logits_close(got[rid], ref[rid], "float32", f"toy2 {name} {rid}", group=("toy architecture 2", name))
         runner.cache.check()
         assert runner.cache.free_pages() == [30] and runner.cache.slots.free_count == 4
 

@@ -5,8 +5,11 @@ lives in arrays inside the library instead of a workspace from the caller.
 
 The test calls it through its exported C symbol, twice in a row, and compares with the
 ordinary entry point (hb_gemm_stream with a caller-allocated workspace) on the same inputs.
-Everything the call touches is allocated before it; the call itself must not allocate. It also
-checks that a product beyond the arrays' size is refused with a message. This file is collected
+Everything the call touches is allocated before it; the call itself must not allocate: the
+driver's count of free device memory (cudaMemGetInfo, which sees every allocation on the GPU,
+the library's own included) is the same after the calls as before them. It also checks that a
+product beyond the arrays' size, a bad epilogue code and a missing status word are refused with
+a message before anything is queued. This file is collected
 last so that a run that stops at the first failure has already run every other test.
 """
 import ctypes as C
@@ -44,16 +47,20 @@ def test_static_scratch_matches_the_ordinary_entry_point(M, N, K, epi):
     status = fast.status_word()
     stream = torch.cuda.current_stream().cuda_stream
     outs = [base.clone(), base.clone()]                     # allocated before the calls
+    warm = base.clone()                                     # a first call has looked up the arrays' addresses and loaded the kernel
+    assert fn(a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), warm.data_ptr(), warm.stride(0), M, N, K, epi,
+              status.data_ptr(), stream) == 0, lib.hb_last_error().decode()
     torch.cuda.synchronize()
-    before = torch.cuda.memory_allocated()
+    before, before_torch = torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated()
     for out in outs:                                        # two calls in a row share the arrays
         rc = fn(a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0), M, N, K, epi,
                 status.data_ptr(), stream)
         assert rc == 0, lib.hb_last_error().decode()
     torch.cuda.synchronize()
     fast.check_status()
-    assert torch.cuda.memory_allocated() == before
-    for out in outs:
+    assert torch.cuda.mem_get_info()[0] == before, "free device memory changed: something allocated"
+    assert torch.cuda.memory_allocated() == before_torch
+    for out in outs + [warm]:
         assert torch.equal(out, want)
     if epi == 0:                                            # and the ordinary entry point itself is right
         assert float((want - ref).abs().max()) < 2e-5 * float(ref.abs().max()) * K ** 0.5
@@ -70,5 +77,11 @@ def test_sizes_beyond_the_static_arrays_are_refused():
     assert rc != 0
     msg = lib.hb_last_error().decode()
     assert "static array holds" in msg and "need" in msg
+    small_a, small_w = a[:8], w[:256]
+    for epi, status_ptr, frag in ((4, fast.status_word().data_ptr(), "epilogue"), (7, fast.status_word().data_ptr(), "epilogue"),
+                                  (0, None, "status")):
+        rc = fn(small_a.data_ptr(), K, small_w.data_ptr(), K, out.data_ptr(), N, 8, 256, K, epi, status_ptr,
+                torch.cuda.current_stream().cuda_stream)
+        assert rc != 0 and frag in lib.hb_last_error().decode()
     torch.cuda.synchronize()
     assert bool((out == 7.0).all()), "a refused call must not launch anything"
