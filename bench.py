@@ -11,8 +11,8 @@ prompts, so the steps run at contexts 2,048 + W .. 2,048 + W + K. `e2e` is the s
 `Engine.step()` (scheduler, host tokens in and out). `prefill` is one 2,048-token prompt in one
 step. `roofline` divides the bytes a decode step has to read (every weight it uses once, and the
 cache of the live requests) by its time. Peaks come from MEASURED_PEAKS.json beside this file,
-else from the fallback figures. The batch-1 and batch-64 points are the faster of two runs of 64
-steps each. The reference measures the same quantities in
+else from the fallback figures. The batch-1 and batch-64 points are the median of three runs of
+64 steps each. The reference measures the same quantities in
 scripts/bench.py:384-449 (decode over many replayed steps, floor = weight + cache bytes / peak).
 """
 from __future__ import annotations
@@ -29,7 +29,7 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# BASELINE configs[2]: Llama-3.2-1B shape
+# the default run: Llama-3.2-1B shape
 MODEL = dict(architectures=["LlamaForCausalLM"], vocab_size=128256, hidden_size=2048, intermediate_size=8192,
              num_hidden_layers=16, num_attention_heads=32, num_key_value_heads=8, head_dim=64,
              max_position_embeddings=131072, rms_norm_eps=1e-5, rope_theta=500000.0,
@@ -37,7 +37,7 @@ MODEL = dict(architectures=["LlamaForCausalLM"], vocab_size=128256, hidden_size=
                                original_max_position_embeddings=8192),
              tie_word_embeddings=True, hidden_act="silu")
 CONTEXT_LEN, PROMPT_LEN, PREFILL_TOKENS, PAGE = 4096, 2048, 2048, 16
-# further layer shapes of the same architecture (BASELINE configs[3] and [4]) for --shape; the default stays configs[2]
+# further layer shapes of the same architecture for --shape (Llama-3.2-3B and Llama-3.1-8B sizes)
 SHAPES = {
     "1b": dict(name="Llama-3.2-1B shape"),
     "3b": dict(name="Llama-3.2-3B shape", hidden_size=3072, intermediate_size=8192, num_hidden_layers=28,
@@ -239,6 +239,84 @@ def prefill_device(eng, warmup: int, reps: int):
     return statistics.median(times)
 
 
+def mixed_workload(a) -> int:
+    """The scheduler's own workload: `--requests` requests with
+    uniform-random prompt lengths in [64, 2048] (seeded), prompts cut into portions under a budget of
+    `--max-prefill` tokens a step beside the decode rows of the others, `--new` tokens each, through
+    Engine.add_request / Engine.step. One JSON line: generated and processed tokens a second over the whole
+    run (wall clock around synchronised ends, host tokens in and out), the device time of the same region
+    (CUDA events), steps split into those that carry prompt portions and decode-only ones, preemptions."""
+    import torch
+
+    from hipinfer_b200 import Engine
+
+    layers = a.layers or MODEL["num_hidden_layers"]
+    g = torch.Generator().manual_seed(7)
+    lens = torch.randint(64, 2049, (a.requests,), generator=g).tolist()
+    ps = [torch.randint(0, MODEL["vocab_size"], (n,), generator=g).tolist() for n in lens]
+    max_seq = 2048 + a.new + 64
+    pages = a.requests * -(-(2048 + a.new) // PAGE) + 8
+    if a.pool_fraction < 1.0:
+        pages = max(int(pages * a.pool_fraction), -(-(2048 + a.new) // PAGE) + 8)
+    eng = Engine(config=dict(MODEL, num_hidden_layers=layers), random_weights=0, std=0.02, dtype="bfloat16",
+                 max_batch=a.requests, max_seq=max_seq, max_prefill=a.max_prefill, page_size=PAGE, num_pages=pages)
+
+    def run_once(timed):
+        for p in ps:
+            eng.add_request(p, a.new)
+        kinds = {"prefill": [0, 0.0, 0], "decode": [0, 0.0, 0]}
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        t0 = time.perf_counter()
+        n_done, host = 0, 0.0
+        while eng.scheduler.has_work() or eng._pending is not None or eng._unreported:
+            h0 = time.perf_counter()
+            n_done += len(eng.step())
+            dt = time.perf_counter() - h0
+            host += dt
+            if eng.last_step is not None:
+                k = kinds["prefill" if eng.last_step[2] else "decode"]
+                k[0] += 1
+                k[1] += dt
+                k[2] += eng.last_step[0]
+        stop.record()
+        stop.synchronize()
+        wall = time.perf_counter() - t0
+        assert n_done == a.requests
+        return wall, start.elapsed_time(stop) / 1e3, kinds
+
+    run_once(False)                       # warm-up: compiles nothing new afterwards, graphs of the decode sizes captured
+    pre0 = eng.scheduler.n_preemptions
+    clocks = ClockSampler().start()
+    with clocks:
+        wall, dev, kinds = run_once(True)
+    from hipinfer_b200.kernels import ops
+    ops.check_device_status()
+    gen = a.requests * a.new
+    total = sum(lens) + gen - a.requests
+    steps = kinds["prefill"][0] + kinds["decode"][0]
+    out = {
+        "metric": f"mixed workload, generated tok/s ({SHAPE_NAME}: {a.requests} requests, prompts U[64, 2048], "
+                  f"{a.max_prefill}-token budget, {a.new} new tokens each)",
+        "value": round(gen / wall, 1), "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": 1,
+        "ms_per_step": round(wall / steps * 1e3, 4), "higher_is_better": True, "dtype": "bf16", "impl": "ours",
+        "data": "synthetic: uniform-random token ids and prompt lengths (seed 7), random N(0, 0.02) bf16 weights",
+        "config": dict(bench_config(a.requests, layers, "inputs larger than L2"), max_prefill=a.max_prefill, new_tokens=a.new,
+                       prompt_tokens=sum(lens), pool_pages=pages),
+        "processed_tok_s": round(total / wall, 1), "wall_s": round(wall, 4), "device_s": round(dev, 4),
+        "e2e_over_device": round(wall / dev, 4),
+        "steps_with_prompt_portions": {"steps": kinds["prefill"][0], "rows": kinds["prefill"][2],
+                                       "host_ms_per_step": round(kinds["prefill"][1] / max(1, kinds["prefill"][0]) * 1e3, 4)},
+        "decode_only_steps": {"steps": kinds["decode"][0], "rows": kinds["decode"][2],
+                              "host_ms_per_step": round(kinds["decode"][1] / max(1, kinds["decode"][0]) * 1e3, 4)},
+        "preemptions": eng.scheduler.n_preemptions - pre0, "clocks": clocks.summary(),
+    }
+    eng.close()
+    print(json.dumps(out))
+    return 0
+
+
 def prefill_flops(layers: int) -> float:
     m, T = MODEL, PREFILL_TOKENS
     H, I, D, Hq, Hkv, V = (m["hidden_size"], m["intermediate_size"], m["head_dim"], m["num_attention_heads"],
@@ -396,6 +474,12 @@ def main() -> int:
     ap.add_argument("--prompt", type=int, default=PROMPT_LEN, help="tokens of each prompt behind the decode steps")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="tokens of the timed prefill step")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "mixed"],
+                    help="decode: the default run; mixed: requests of random lengths through the scheduler (see mixed_workload)")
+    ap.add_argument("--requests", type=int, default=32, help="mixed: number of requests")
+    ap.add_argument("--new", type=int, default=128, help="mixed: tokens generated per request")
+    ap.add_argument("--max-prefill", type=int, default=512, help="mixed: token budget of a step")
+    ap.add_argument("--pool-fraction", type=float, default=1.0, help="mixed: fraction of the pages all requests would need (< 1: preemptions)")
     ap.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 decode points")
     ap.add_argument("--breakdown", action="store_true", help="print per-kernel times of a decode step and exit")
     ap.add_argument("--prefill", action="store_true", help="with --breakdown: the prefill step instead of a decode step")
@@ -413,6 +497,8 @@ def main() -> int:
         a.layers = MODEL["num_hidden_layers"]
     if a.breakdown:
         return breakdown(a.layers, a.batch, a.prefill)
+    if a.workload == "mixed":
+        return mixed_workload(a)
     import torch
 
     pk = peaks()
@@ -425,8 +511,8 @@ def main() -> int:
     step_bytes = eng.weight_bytes + a.batch * mean_ctx * eng.kv_bytes_per_token
     achieved = step_bytes / ms / 1e6
     points = {f"decode_b{a.batch}": round(value, 1)}
-    for b in point_batches:      # the faster of two short runs: a point is one figure, and the GPU's other tenants are not ours
-        pms = min(decode_device(eng, b, min(a.steps, 64), a.warmup)[0] for _ in range(2))
+    for b in point_batches:      # the median of three short runs
+        pms = statistics.median(decode_device(eng, b, min(a.steps, 64), a.warmup)[0] for _ in range(3))
         points[f"decode_b{b}"] = round(b / pms * 1e3, 1)
     pre_ms = prefill_device(eng, 3, 5)
     pre_frac = prefill_flops(a.layers) / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12)

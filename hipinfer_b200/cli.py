@@ -6,6 +6,7 @@ are kept, with --model for a folder of config.json and model.safetensors.
                                      [--temperature T --seed S] [--max-batch --max-seq --max-prefill]
     python -m hipinfer_b200 random-model --config config.json --out DIR --seed 0 [--std 0.02] [--dtype bfloat16]
     python -m hipinfer_b200 replay --model DIR --dtype bfloat16 --out DIR --max-tokens N   (steps on stdin)
+    python -m hipinfer_b200 bench [bench.py's options]        (the measurement program beside the package)
 """
 from __future__ import annotations
 
@@ -35,12 +36,27 @@ def main(argv=None) -> int:
     r.add_argument("--norm-std", type=float, default=0.0)
     r.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     sub.add_parser("replay", help="trace replay; same options as bin/trace_run", add_help=False)
+    sub.add_parser("bench", help="the measurement program (bench.py beside the package); same options", add_help=False)
     if argv is None:
         argv = sys.argv[1:]
     if argv and argv[0] == "replay":
         from .engine.replay import main as replay_main
 
         return replay_main(argv[1:])
+    if argv and argv[0] == "bench":
+        import os
+        import runpy
+
+        script = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "bench.py")
+        if not os.path.isfile(script):
+            print(f"hipinfer_b200 bench: {script} is not there (the measurement program lives beside the package)", file=sys.stderr)
+            return 2
+        sys.argv = [script] + list(argv[1:])
+        try:
+            runpy.run_path(script, run_name="__main__")
+        except SystemExit as e:
+            return int(e.code or 0)
+        return 0
     a = ap.parse_args(argv)
     if a.cmd == "generate":
         from .engine.api import Engine

@@ -63,6 +63,7 @@ class Engine:
         # back, so the host prepares step i + 1 while the device runs step i (see step())
         self.pipeline = bool(pipeline)
         self._pending = None
+        self.last_step = None      # (rows, requests, rows of prompt portions) of the step launched last
         self._unreported: List[Request] = []
         self._ids = itertools.count()
         self._slots: Dict[int, dict] = {}
@@ -129,6 +130,7 @@ class Engine:
             entries.append(StepEntry(s.request.request_id, part, [s.n - 1] if s.samples else []))
             token_map += tm
             row += s.n
+        self.last_step = (row, len(sched), sum(s.n for s in sched if s.n > 1))
         feed = older is not None and any(t >= 0 for t in token_map)
         logits = self.runner.step(entries, device_tokens=older["tokens_dev"] if feed else None,
                                   token_map=token_map if feed else None)
@@ -180,6 +182,7 @@ class Engine:
             return []
         entries = [StepEntry(s.request.request_id, s.request.tokens[s.start:s.start + s.n], [s.n - 1] if s.samples else [])
                    for s in sched]
+        self.last_step = (sum(s.n for s in sched), len(sched), sum(s.n for s in sched if s.n > 1))
         logits = self.runner.step(entries)
         samplers = [s for s in sched if s.samples]
         toks = self.sampler.sample(logits, [s.request.params for s in samplers],

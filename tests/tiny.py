@@ -238,8 +238,13 @@ def run_plan(stepper, requests, plan):
 
 # Tolerances, as a fraction of the largest |logit| of the request. 32-bit: rounding of sums in
 # another order. bfloat16: activations, q, k, v and the attention output are rounded to 8 bits
-# of mantissa a few times per layer.
-TOL = {"float32": 2e-5, "bfloat16": 3e-2}
+# of mantissa a few times per layer. The bounds stand about a factor of two above what the
+# engine measures (printed at the end of every run): 32-bit 2.5e-7 (tiny A) to 4.2e-6 (1B layer
+# sizes, 2 layers); bfloat16 2.1e-3 (tiny A) to 8.8e-3 (tiny B and the 1B layer sizes). They are
+# meant for these models of two and three layers: the error grows with depth. That the same
+# step function holds 4e-6 in 32-bit under every cutting is what rules out a fault of the cache
+# or the batch hiding below the bfloat16 bound.
+TOL = {"float32": 1e-5, "bfloat16": 1.5e-2}
 MEASURED = []      # ((configuration, plan), dtype, largest |difference| / largest |logit|) of every comparison: printed at the end of a run
 
 
