@@ -32,9 +32,13 @@ _SIGS = {
     "hb_gemm_tc_rope_kv": [_p, _l, _p, _l, _i, _i, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p, _p],
     "hb_attn_decode_supported": [_i, _i, _i],
     "hb_wait_selftest": [_p, _i, _p, _p],
+    "hb_rows_norm_qkv_rope": [_p, _l, _p, _f, _p, _l, _i, _i, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p, _p],
+    "hb_rows_add": [_p, _l, _p, _l, _p, _l, _i, _i, _i, _p, _p],
+    "hb_rows_norm_swiglu": [_p, _l, _p, _f, _p, _l, _p, _l, _i, _i, _i, _p, _p],
+    "hb_rows_norm_supported": [_i, _i],
 }
 _fns = {}
-_LAUNCHES = {"hb_gemm_tc_rope_kv": 1, "hb_gemm_stream_finish": 1, "hb_add_rmsnorm_slices": 1, "hb_rope_kv_slices": 1, "hb_gemm_tc": 1, "hb_gemm_stream": 1, "hb_attn_decode": 1, "hb_flash_prefill": 1, "hb_flash_prefill_tc": 1}
+_LAUNCHES = {"hb_rows_norm_qkv_rope": 1, "hb_rows_add": 1, "hb_rows_norm_swiglu": 1, "hb_gemm_tc_rope_kv": 1, "hb_gemm_stream_finish": 1, "hb_add_rmsnorm_slices": 1, "hb_rope_kv_slices": 1, "hb_gemm_tc": 1, "hb_gemm_stream": 1, "hb_attn_decode": 1, "hb_flash_prefill": 1, "hb_flash_prefill_tc": 1}
 _status = None
 
 EPI_F32, EPI_BF16, EPI_ADD_F32, EPI_SWIGLU_BF16, EPI_SLICES = 0, 1, 2, 3, 4
@@ -267,6 +271,65 @@ def linear_swiglu(a, w, act_out, group) -> bool:
     if group != 16 or act_out.dtype != torch.bfloat16 or not _tc_ok(a, w.t) or w.shape[0] % 32:
         return False
     _gemm(a, w.t, act_out, EPI_SWIGLU_BF16)
+    return True
+
+
+# ------------------------------------------------------------------------------------------
+# a few token rows (csrc/gemm_rows.cu): whole-K output stripes, norm in the prologue, the layer's
+# own arithmetic in the epilogue; a decoder layer of a small decode step is five kernels
+# ------------------------------------------------------------------------------------------
+ROWS_MAX = 16           # token rows up to which the rows kernels are used
+
+
+def _rows_w_ok(w) -> bool:
+    return (not PLAIN_ONLY and w.dtype == torch.bfloat16 and w.is_contiguous() and w.shape[1] % 32 == 0
+            and w.data_ptr() % 16 == 0)
+
+
+def _rows_norm_ok(x, norm_w, w) -> bool:
+    M, K = x.shape
+    return (M <= ROWS_MAX and x.is_cuda and x.dtype == torch.float32 and x.stride(1) == 1 and x.stride(0) % 4 == 0
+            and x.data_ptr() % 16 == 0 and norm_w.dtype == torch.bfloat16 and norm_w.is_contiguous() and norm_w.numel() == K
+            and _rows_w_ok(w) and w.shape[1] == K and bool(_fn("hb_rows_norm_supported")(M, K)))
+
+
+def rows_norm_qkv_rope(x, norm_w, eps, w, positions, slot_map, table, q_out, k_cache, v_cache, n_heads, n_kv_heads, head_dim,
+                       rotary_dim, page_size) -> bool:
+    """q, k (rotated) and v of RMSNorm(x) times the fused [q; k; v] weight for a few rows, q into q_out, k and v into their
+    page slots: one kernel. False: nothing done (sizes or types it does not take)."""
+    if (not _rows_norm_ok(x, norm_w, w) or head_dim % 16 or rotary_dim != head_dim
+            or w.shape[0] != (n_heads + 2 * n_kv_heads) * head_dim or q_out.dtype != torch.bfloat16 or not q_out.is_contiguous()
+            or table.dtype != torch.float32 or not table.is_contiguous()):
+        return False
+    if slot_map is not None and not (k_cache.dtype == torch.bfloat16 and v_cache.dtype == torch.bfloat16
+                                     and k_cache.is_contiguous() and v_cache.is_contiguous()):
+        return False
+    p = lambda t: None if t is None else t.data_ptr()
+    _call("hb_rows_norm_qkv_rope", x.data_ptr(), x.stride(0), norm_w.data_ptr(), float(eps), w.data_ptr(), w.stride(0),
+          x.shape[0], x.shape[1], positions.data_ptr(), p(slot_map), table.data_ptr(), q_out.data_ptr(),
+          p(k_cache) if slot_map is not None else None, p(v_cache) if slot_map is not None else None, n_heads, n_kv_heads,
+          head_dim, page_size, status_word().data_ptr(), _stream())
+    return True
+
+
+def rows_add(act, w, out) -> bool:
+    """out (fp32) += act @ w.T for a few bf16 rows, finished in one kernel (no slices). False: nothing done."""
+    M, K = act.shape
+    if (M > ROWS_MAX or not act.is_cuda or act.dtype != torch.bfloat16 or act.stride(1) != 1 or act.stride(0) % 8
+            or act.data_ptr() % 16 or not _rows_w_ok(w) or w.shape[1] != K or out.dtype != torch.float32 or out.stride(1) != 1):
+        return False
+    _call("hb_rows_add", act.data_ptr(), act.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0), M, w.shape[0],
+          K, status_word().data_ptr(), _stream())
+    return True
+
+
+def rows_norm_swiglu(x, norm_w, eps, w, act_out, group) -> bool:
+    """act_out (bf16) = silu(gate) * up of RMSNorm(x) times a gate/up weight interleaved in groups of 16 rows. False: nothing done."""
+    if (group != 16 or not _rows_norm_ok(x, norm_w, w) or w.shape[0] % 32 or act_out.dtype != torch.bfloat16
+            or act_out.stride(1) != 1):
+        return False
+    _call("hb_rows_norm_swiglu", x.data_ptr(), x.stride(0), norm_w.data_ptr(), float(eps), w.data_ptr(), w.stride(0),
+          act_out.data_ptr(), act_out.stride(0), x.shape[0], w.shape[0], x.shape[1], status_word().data_ptr(), _stream())
     return True
 
 

@@ -30,7 +30,7 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", 
 # library name -> sources (relative to csrc/); headers every library depends on
 LIBRARIES: Dict[str, List[str]] = {
     "core": ["core.cu"],
-    "fast": ["fast_entry.cu", "gemm_tc.cu", "gemm_stream.cu", "gemm_stream_consumers.cu", "attention_fast.cu", "attention_prefill.cu", "attention_prefill_tc.cu", "wait_selftest.cu"],
+    "fast": ["fast_entry.cu", "gemm_tc.cu", "gemm_stream.cu", "gemm_stream_consumers.cu", "gemm_rows.cu", "attention_fast.cu", "attention_prefill.cu", "attention_prefill_tc.cu", "wait_selftest.cu"],
 }
 HEADERS = ["common.cuh", "tc_common.cuh", "gemm_stream_static.h"]
 

@@ -45,7 +45,7 @@ def timeit(fn, iters, flush):
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
-    ap.add_argument("kernel", choices=["gemm_tc", "gemm_stream", "attn_decode", "flash_prefill", "flash_prefill_tc", "rmsnorm"])
+    ap.add_argument("kernel", choices=["gemm_tc", "gemm_stream", "rows_add", "rows_swiglu", "rows_qkv", "attn_decode", "flash_prefill", "flash_prefill_tc", "rmsnorm"])
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=16384)
     ap.add_argument("--k", type=int, default=2048)
@@ -68,7 +68,31 @@ def main(argv=None) -> int:
     g = torch.Generator(device=dev).manual_seed(0)
     rnd = lambda *s: torch.randn(*s, generator=g, device=dev)
     out = {"kernel": a.kernel}
-    if a.kernel.startswith("gemm"):
+    if a.kernel.startswith("rows"):
+        M, N, K = a.m, a.n, a.k
+        w = (rnd(N, K) * 0.02).bfloat16()
+        nw = torch.ones(K, device=dev, dtype=torch.bfloat16)
+        if a.kernel == "rows_add":
+            act, acc = rnd(M, K).bfloat16(), torch.zeros(M, N, device=dev)
+            fn = lambda: fast.rows_add(act, w, acc)
+        elif a.kernel == "rows_swiglu":
+            x, act = rnd(M, K), torch.empty(M, N // 2, device=dev, dtype=torch.bfloat16)
+            fn = lambda: fast.rows_norm_swiglu(x, nw, 1e-5, w, act, 16)
+        else:
+            Hq, Hkv, D = a.heads, a.kv_heads, a.head_dim
+            N = (Hq + 2 * Hkv) * D
+            w = (rnd(N, K) * 0.02).bfloat16()
+            x, q = rnd(M, K), torch.empty(M, Hq * D, device=dev, dtype=torch.bfloat16)
+            table = ops.rope_table((10000.0 ** (-torch.arange(0, D, 2, dtype=torch.float64) / D)).float().to(dev), 4096)
+            pos = torch.arange(M, dtype=torch.int32, device=dev) + 2048
+            kc = torch.zeros(M + 4, Hkv, a.page_size, D, device=dev, dtype=torch.bfloat16)
+            vc = torch.zeros_like(kc)
+            slots = (torch.arange(M, dtype=torch.int32, device=dev) * a.page_size)
+            fn = lambda: fast.rows_norm_qkv_rope(x, nw, 1e-5, w, pos, slots, table, q, kc, vc, Hq, Hkv, D, D, a.page_size)
+        assert fn(), "the rows kernel does not take these sizes"
+        ms = timeit(fn, a.iters, a.flush)
+        out.update(M=M, N=N, K=K, ms=ms, gbs=N * K * 2 / ms / 1e6)
+    elif a.kernel.startswith("gemm"):
         M, N, K, epi = a.m, a.n, a.k, EPI[a.epi]
         x, w = rnd(M, K).bfloat16(), (rnd(N, K) * 0.02).bfloat16()
         c = torch.zeros(M, N // 2 if epi == 3 else N, device=dev, dtype=torch.bfloat16 if epi in (1, 3) else torch.float32)

@@ -344,6 +344,59 @@ def linear_swiglu(a: torch.Tensor, w_gate_up: Weight, act_out: torch.Tensor, gro
     return swiglu(gu, act_out, group)
 
 
+class LazyNorm:
+    """The RMSNorm of residual rows that has not been computed yet: (x fp32 [T, H], weight, eps). A part that can
+    fold the norm into its own first kernel (a few rows: the product's prologue) takes it as it is; any other
+    calls materialize(), which runs the norm kernel. A part says that it understands one with `takes_lazy_norm`."""
+    __slots__ = ("x", "weight", "eps", "dtype")
+
+    def __init__(self, x, weight, eps, dtype):
+        self.x, self.weight, self.eps, self.dtype = x, weight, eps, dtype
+
+    @property
+    def shape(self):
+        return self.x.shape
+
+    @property
+    def device(self):
+        return self.x.device
+
+    def materialize(self) -> torch.Tensor:
+        out = torch.empty(self.x.shape, dtype=self.dtype, device=self.x.device)
+        return rmsnorm(self.x, self.weight, self.eps, out)
+
+
+def lazy_norm_applies(x: torch.Tensor, weight: torch.Tensor, dtype) -> bool:
+    """Whether a consumer could fold this norm into its product: a few bf16-path rows on the device."""
+    from . import fast
+
+    return (x.is_cuda and dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.dtype == torch.float32
+            and x.shape[0] <= fast.ROWS_MAX and not fast.PLAIN_ONLY)
+
+
+def norm_linear_rope_kv_write(xn: "LazyNorm", w: "Weight", positions, slot_map, table, q_out, k_cache, v_cache, n_heads,
+                              n_kv_heads, head_dim, rotary_dim, page_size) -> bool:
+    """rope_kv_write of RMSNorm(x) @ w.T in one kernel for a few rows; False: nothing was done."""
+    from . import fast
+
+    return fast.rows_norm_qkv_rope(xn.x, xn.weight, xn.eps, w.t, positions, slot_map, table, q_out, k_cache, v_cache, n_heads,
+                                   n_kv_heads, head_dim, rotary_dim, page_size)
+
+
+def norm_linear_swiglu(xn: "LazyNorm", w_gate_up: "Weight", act_out: torch.Tensor, group: int) -> bool:
+    """act_out = swiglu(RMSNorm(x) @ w_gate_up.T) in one kernel for a few rows; False: nothing was done."""
+    from . import fast
+
+    return fast.rows_norm_swiglu(xn.x, xn.weight, xn.eps, w_gate_up.t, act_out, group)
+
+
+def linear_add_rows(a: torch.Tensor, w: "Weight", out: torch.Tensor) -> bool:
+    """out += a @ w.T finished in one kernel for a few rows (whole-K stripes, nothing left to add); False: nothing was done."""
+    from . import fast
+
+    return a.is_cuda and fast.rows_add(a, w.t, out)
+
+
 class Pending:
     """A product whose K slices have yet to be added: into `out` (accumulate) or as `out` itself.
     The kernel that reads the result next can add them on its way (rmsnorm and rope_kv_write take

@@ -55,11 +55,18 @@ class AttentionMixer(Mixer):
     def cache_need(self):
         return CacheNeed("window" if self.window else "full", self.n_kv_heads, self.head_dim, self.window)
 
+    takes_lazy_norm = True
+
     def forward(self, xn, x, batch, cache, state):
         T = xn.shape[0]
         Hq, Hkv, D = self.n_heads, self.n_kv_heads, self.head_dim
         q = torch.empty(T, Hq * D, dtype=self.ctx.dtype, device=xn.device)
         slot_map = batch.slot_maps[cache.group] if cache.write else None
+        if isinstance(xn, ops.LazyNorm):     # a few rows: norm, projection, rotation and cache write as one kernel
+            folded = getattr(self.position, "norm_project_rotate_and_store", None)
+            if folded is not None and folded(xn, self.wqkv, batch.positions, slot_map, q, cache.k, cache.v, Hq, Hkv):
+                return self._attend_and_project(q, x, batch, cache)
+            xn = xn.materialize()
         fused = getattr(self.position, "project_rotate_and_store", None)    # many rows: the rotation in the product's epilogue
         if fused is not None and fused(xn, self.wqkv, batch.positions, slot_map, q, cache.k, cache.v, Hq, Hkv):
             return self._attend_and_project(q, x, batch, cache)
@@ -80,6 +87,8 @@ class AttentionMixer(Mixer):
         att = torch.empty(T, Hq * D, dtype=self.ctx.dtype, device=q.device)
         ops.attention(q, cache.k, cache.v, batch, cache.group, att, Hq, Hkv, D, self.ctx.page_size, self.window,
                       self.scale)
+        if ops.linear_add_rows(att, self.wo, x):                       # a few rows: added in the product's epilogue
+            return None
         return ops.linear_deferred(att, self.wo, x, accumulate=True)   # the next norm may add it
 
 

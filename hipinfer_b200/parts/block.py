@@ -47,8 +47,13 @@ class PreNormBlock(Part):
     takes_pending = True
 
     @staticmethod
-    def _normed(norm, x, pending):
+    def _normed(norm, x, pending, consumer):
         if pending is None:
+            # a few rows: a consumer that says so gets the norm unevaluated and folds it into its first product
+            if getattr(consumer, "takes_lazy_norm", False) and hasattr(norm, "lazy"):
+                lazy = norm.lazy(x)
+                if lazy is not None:
+                    return lazy
             return norm.forward(x)
         if norm.takes_pending:
             return norm.forward(x, pending=pending)
@@ -58,9 +63,9 @@ class PreNormBlock(Part):
     def forward(self, x, batch, cache, state, pending=None):
         """pending: a sum the layer before has yet to add into x. Returns what this layer leaves
         to be added (None when x is complete)."""
-        left = self.mixer.forward(self._normed(self.mixer_norm, x, pending), x, batch, cache, state)
+        left = self.mixer.forward(self._normed(self.mixer_norm, x, pending, self.mixer), x, batch, cache, state)
         pending = left if isinstance(left, ops.Pending) else None
-        left = self.feed_forward.forward(self._normed(self.feed_forward_norm, x, pending), x, batch)
+        left = self.feed_forward.forward(self._normed(self.feed_forward_norm, x, pending, self.feed_forward), x, batch)
         return left if isinstance(left, ops.Pending) else None
 
 

@@ -45,9 +45,17 @@ class SwiGLU(Part):
     def weight_bytes(self):
         return self.wgu.nbytes + self.wdown.nbytes
 
+    takes_lazy_norm = True
+
     def forward(self, xn, x, batch):
         act = torch.empty(xn.shape[0], self.inter, dtype=self.ctx.dtype, device=xn.device)
-        ops.linear_swiglu(xn, self.wgu, act, GROUP)
+        if isinstance(xn, ops.LazyNorm):     # a few rows: the norm in the gate/up product's prologue
+            if not ops.norm_linear_swiglu(xn, self.wgu, act, GROUP):
+                ops.linear_swiglu(xn.materialize(), self.wgu, act, GROUP)
+        else:
+            ops.linear_swiglu(xn, self.wgu, act, GROUP)
+        if ops.linear_add_rows(act, self.wdown, x):                       # a few rows: added in the product's epilogue
+            return None
         return ops.linear_deferred(act, self.wdown, x, accumulate=True)   # the next norm may add it
 
 

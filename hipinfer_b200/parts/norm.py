@@ -30,6 +30,12 @@ class RMSNorm(Part):
 
     takes_pending = True
 
+    def lazy(self, x):
+        """The norm of x left to its consumer (kernels.ops.LazyNorm) where a consumer could fold it into its product, else None."""
+        if self.weight is None or not ops.lazy_norm_applies(x, self.weight, self.ctx.dtype):
+            return None
+        return ops.LazyNorm(x, self.weight, self.eps, self.ctx.dtype)
+
     def forward(self, x, rows=None, out=None, pending=None):
         """pending: a sum that has yet to be added into x (it is added before the norm)."""
         M = x.shape[0] if rows is None else rows.numel()

@@ -79,4 +79,15 @@ class RotaryEmbedding(Part):
                                         n_kv_heads, self.head_dim, self.rotary_dim, self.ctx.page_size)
 
 
+    def norm_project_rotate_and_store(self, lazy_norm, weight, positions, slot_map, q_out, k_cache, v_cache, n_heads,
+                                      n_kv_heads) -> bool:
+        """rotate_and_store of RMSNorm(x) @ weight.T for a few rows as one kernel (the norm in the product's prologue,
+        the rotation in its epilogue); `lazy_norm` is a kernels.ops.LazyNorm. False: nothing was done. Optional, like
+        project_rotate_and_store."""
+        if not self.rotary_dim:
+            return False
+        return ops.norm_linear_rope_kv_write(lazy_norm, weight, positions, slot_map, self.table, q_out, k_cache, v_cache,
+                                             n_heads, n_kv_heads, self.head_dim, self.rotary_dim, self.ctx.page_size)
+
+
 register_part("position", "rope", RotaryEmbedding)

@@ -504,3 +504,142 @@ def test_slices_added_by_the_rotation(M, Hq, Hkv, D, K):
     ops.rope_kv_write(qkv, pos, None, table, q, kc2, kc2, Hq, Hkv, D, D, ps, pending=ops.linear_deferred(xn, w, qkv))
     torch.cuda.synchronize()
     assert bool((kc2 == 9.0).all()) and torch.equal(q, q_ref)
+
+
+# ------------------------------------------------------------------------------------------
+# the kernels for a few token rows: whole-K stripes, the norm in the prologue, the layer's arithmetic in the epilogue
+# ------------------------------------------------------------------------------------------
+def _rms(x, w, eps):
+    """RMSNorm in float64 from float32 rows, rounded once to bfloat16 (what the product then reads)."""
+    xd = x.double()
+    return (w.double() * (xd * torch.rsqrt((xd * xd).mean(-1, keepdim=True) + eps))).float().bfloat16()
+
+
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("N,K", [(128, 128), (96, 96), (300, 224), (2048, 8192), (704, 2048), (40, 1056)])
+def test_rows_add(M, N, K):
+    """out += act W^T finished in one kernel, twice in a row, nothing written beyond the last row or column."""
+    a, w = rnd(M, K, seed=71), rnd(N, K, seed=72, scale=0.1)
+    ref = a.float().double() @ w.float().double().T
+    tol = 2e-5 * max(1.0, float(ref.abs().max())) * (K ** 0.5)
+    for _ in range(2):
+        base = rnd(M + 1, N + 3, seed=73, dtype=torch.float32)
+        out = base.clone()
+        assert fast().rows_add(a, w, out[:M, :N])
+        sync_check()
+        assert float((out[:M, :N].double() - (base[:M, :N].double() + ref)).abs().max()) < tol
+        assert torch.equal(out[M], base[M]) and torch.equal(out[:, N:], base[:, N:])
+
+
+@pytest.mark.parametrize("M,I,K", [(1, 16, 64), (5, 176, 96), (8, 320, 160), (16, 1024, 2048), (7, 8192, 3072), (12, 48, 4096)])
+def test_rows_norm_swiglu(M, I, K):
+    x = rnd(M, K, seed=74, dtype=torch.float32, scale=3.0)
+    nw = (1 + 0.2 * torch.randn(K, generator=torch.Generator().manual_seed(75))).bfloat16().to(DEV)
+    g, u = rnd(I, K, seed=76, scale=0.2), rnd(I, K, seed=77, scale=0.2)
+    gu = torch.stack([g.reshape(I // 16, 16, K), u.reshape(I // 16, 16, K)], 1).reshape(2 * I, K).contiguous()
+    xn = _rms(x, nw, 1e-5).float()
+    gg, uu = xn @ g.float().T, xn @ u.float().T
+    ref = gg / (1 + torch.exp(-gg)) * uu
+    out = torch.full((M + 1, I), 7.0, dtype=torch.bfloat16, device=DEV)
+    assert fast().rows_norm_swiglu(x, nw, 1e-5, gu, out[:M], 16)
+    sync_check()
+    assert float((out[:M].float() - ref).abs().max()) < 1.5e-2 * max(1.0, float(ref.abs().max()))
+    assert bool((out[M] == 7.0).all())
+
+
+@pytest.mark.parametrize("M,Hq,Hkv,D,K,ps,write", [(1, 32, 8, 64, 2048, 16, True), (8, 32, 8, 64, 2048, 16, True), (16, 8, 2, 64, 256, 8, True),
+                                                   (5, 4, 2, 128, 512, 16, True), (3, 3, 1, 32, 96, 16, True), (9, 4, 2, 16, 64, 16, True),
+                                                   (6, 24, 8, 128, 3072, 16, True), (4, 4, 4, 64, 128, 32, False)])
+def test_rows_norm_qkv_rope(M, Hq, Hkv, D, K, ps, write):
+    """Norm, projection, rotation and page writes as one kernel against the same steps in float32/float64: q and
+    the pages within bfloat16 rounding of the plain result, pages of other tokens and of rows that are not stored untouched."""
+    from hipinfer_b200.kernels import ops
+
+    N = (Hq + 2 * Hkv) * D
+    x = rnd(M, K, seed=81, dtype=torch.float32, scale=2.0)
+    nw = (1 + 0.2 * torch.randn(K, generator=torch.Generator().manual_seed(82))).bfloat16().to(DEV)
+    w = rnd(N, K, seed=83, scale=0.1)
+    g = torch.Generator().manual_seed(84)
+    n_pos = 4096
+    inv_freq = (10000.0 ** (-torch.arange(0, D, 2, dtype=torch.float64) / D)).float().to(DEV)
+    table = ops.rope_table(inv_freq, n_pos)
+    positions = torch.randint(0, n_pos, (M,), generator=g, dtype=torch.int32).to(DEV)
+    n_pages = -(-M // ps) + 4
+    slots = torch.randperm(n_pages * ps, generator=g)[:M].to(torch.int32)
+    if M > 2:
+        slots[2] = -1                                           # a row whose key and value are not stored
+    slot_map = slots.to(DEV) if write else None
+    kc = torch.full((n_pages, Hkv, ps, D), 3.0, dtype=torch.bfloat16, device=DEV)
+    vc = kc.clone()
+    q = torch.full((M + 1, Hq * D), 7.0, dtype=torch.bfloat16, device=DEV)
+    assert fast().rows_norm_qkv_rope(x, nw, 1e-5, w, positions, slot_map, table, q[:M], kc, vc, Hq, Hkv, D, D, ps)
+    sync_check()
+    # plain: norm (rounded once), product in float64, rotation of the pairs (j, j + D/2)
+    qkv = (_rms(x, nw, 1e-5).double() @ w.double().T)
+    cs = table[positions.long()].double()                       # [M, D/2, 2]
+    cos, sin = cs[..., 0][:, None, :], cs[..., 1][:, None, :]
+
+    def rot(t):
+        t1, t2 = t[..., :D // 2], t[..., D // 2:]
+        return torch.cat([t1 * cos - t2 * sin, t2 * cos + t1 * sin], -1)
+
+    q_ref = rot(qkv[:, :Hq * D].reshape(M, Hq, D)).reshape(M, Hq * D)
+    k_ref = rot(qkv[:, Hq * D:(Hq + Hkv) * D].reshape(M, Hkv, D))
+    v_ref = qkv[:, (Hq + Hkv) * D:].reshape(M, Hkv, D)
+    tol = 1.2e-2 * max(1.0, float(qkv.abs().max()))
+    assert float((q[:M].double() - q_ref).abs().max()) < tol
+    assert bool((q[M] == 7.0).all())
+    kc_ref = torch.full_like(kc, 3.0).double()
+    vc_ref = kc_ref.clone()
+    if write:
+        for m in range(M):
+            s = int(slots[m])
+            if s >= 0:
+                kc_ref[s // ps, :, s % ps] = k_ref[m]
+                vc_ref[s // ps, :, s % ps] = v_ref[m]
+    untouched = kc_ref == 3.0
+    assert float((kc.double() - kc_ref).abs().max()) < tol and float((vc.double() - vc_ref).abs().max()) < tol
+    assert bool((kc[untouched] == 3.0).all()) and bool((vc[vc_ref == 3.0] == 3.0).all())
+
+
+def test_rows_kernels_do_not_depend_on_the_batch():
+    """A token's result is bit-identical alone, among 8 and among 16 rows (its column of the MMA is its own)."""
+    from hipinfer_b200.kernels import ops
+
+    K, I, Hq, Hkv, D, ps = 2048, 512, 8, 2, 64, 16
+    x = rnd(16, K, seed=91, dtype=torch.float32, scale=2.0)
+    nw = torch.ones(K, dtype=torch.bfloat16, device=DEV)
+    gu, wo, wqkv = rnd(2 * I, K, seed=92, scale=0.1), rnd(384, K, seed=93, scale=0.1), rnd((Hq + 2 * Hkv) * D, K, seed=94, scale=0.1)
+    act = rnd(16, K, seed=95)
+    table = ops.rope_table((10000.0 ** (-torch.arange(0, D, 2, dtype=torch.float64) / D)).float().to(DEV), 512)
+    pos = torch.arange(100, 116, dtype=torch.int32, device=DEV)
+
+    def run(rows):
+        r = torch.tensor(rows, device=DEV)
+        n = len(rows)
+        o1 = torch.empty(n, I, dtype=torch.bfloat16, device=DEV)
+        assert fast().rows_norm_swiglu(x[r].contiguous(), nw, 1e-5, gu, o1, 16)
+        o2 = torch.zeros(n, 384, dtype=torch.float32, device=DEV)
+        assert fast().rows_add(act[r].contiguous(), wo, o2)
+        q = torch.empty(n, Hq * D, dtype=torch.bfloat16, device=DEV)
+        assert fast().rows_norm_qkv_rope(x[r].contiguous(), nw, 1e-5, wqkv, pos[r].contiguous(), None, table, q, None, None,
+                                         Hq, Hkv, D, D, ps)
+        sync_check()
+        return o1, o2, q
+
+    full = run(list(range(16)))
+    for rows in ([0], [5, 15], list(range(3, 11)), list(range(2, 14))):
+        for got, want in zip(run(rows), full):
+            assert torch.equal(got, want[rows])
+
+
+def test_rows_kernels_refuse_what_they_do_not_take():
+    x = rnd(17, 256, seed=96, dtype=torch.float32)
+    nw = torch.ones(256, dtype=torch.bfloat16, device=DEV)
+    w = rnd(64, 256, seed=97)
+    out = torch.zeros(17, 32, dtype=torch.bfloat16, device=DEV)
+    assert not fast().rows_norm_swiglu(x, nw, 1e-5, w, out, 16)                    # 17 rows
+    assert not fast().rows_norm_swiglu(x[:4], nw, 1e-5, w.float(), out[:4], 16)    # weights stored in 32-bit
+    assert not fast().rows_add(rnd(4, 200, seed=98), rnd(64, 200, seed=99), torch.zeros(4, 64, device=DEV))   # K no multiple of 32
+    assert not fast().rows_norm_swiglu(rnd(4, 65536, seed=1, dtype=torch.float32), torch.ones(65536, dtype=torch.bfloat16, device=DEV),
+                                       1e-5, rnd(32, 65536, seed=2), out[:4, :16], 16)   # rows too wide for shared memory
