@@ -17,6 +17,9 @@ HB_TL_DEFINE(attn)
 #define HB_AD_THREADS 128
 #endif
 constexpr int AD_THREADS = HB_AD_THREADS, AD_WARPS = AD_THREADS / 32;
+static int g_ad_cluster_rows = 8;    // rows of a step up to which a row's chunk blocks run as one cluster (see CL below); measured:
+                                     // 4 % faster steps at 1 and 8 rows, 2 % slower at 16, 12 % slower at 32 (clusters are placed as gangs)
+HB_EXPORT void hb_attn_decode_set_cluster_rows(int rows) { g_ad_cluster_rows = rows; }
 
 // Byte offset of 16-byte chunk c of key row `row` in a [keys][D] bf16 tile (D = 64 or 128): the
 // swizzle that makes ldmatrix of eight consecutive rows free of bank conflicts.
@@ -88,7 +91,12 @@ __device__ __forceinline__ void ad_load_rows(const __nv_bfloat16* __restrict__ k
 // SR (TMA only): rows of shared memory a warp has: RW (it asks for the keys of a pass when it is done with the pass
 // before) or KW (all its keys are asked for at the start: 128 KB a block, for launches of so few blocks that every one
 // has an SM of its own; the passes and their arithmetic are the same).
-template <int D, int G, bool TMA, int RW, int KW, int SR>
+// CL (TMA only): the chunk blocks of a (row, kv head) are one thread-block cluster (the grid's x extent, at most 8). A
+// block leaves its partial result in its own shared memory, the cluster meets at a barrier, and the block of the
+// row's first chunk adds the partials through distributed shared memory, in the same order and with the same
+// arithmetic as the merge through memory below: fence, counter and the partials' round trip through L2 (4 of a
+// layer's 11 us at 8 requests) become two cluster barriers. Blocks without keys only pass the barriers.
+template <int D, int G, bool TMA, int RW, int KW, int SR, bool CL>
 __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
     const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, int* __restrict__ status,
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc,
@@ -110,6 +118,8 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
   __shared__ int is_last;
   __shared__ __align__(8) uint64_t bars[AD_WARPS];
   __shared__ int abort_flag;
+  __shared__ __align__(16) float cl_acc[CL ? G * D : 1];     // CL: this block's partial result, read by the merging block
+  __shared__ __align__(8) float cl_ml[CL ? G * 2 : 2];
   hb_pdl_launch();
   HB_TL_MARK(0, 0);
   const int t = blockIdx.z, h = blockIdx.y, s = blockIdx.x;
@@ -121,6 +131,7 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
   const int s_lo = lo / chunk, s_hi = p / chunk;
   if ((q_len && q_len[rq] >= row_limit) || s < s_lo || s > s_hi) {  // a long portion (the flash kernel's), or no keys here
     if ((blockIdx.x | blockIdx.y | blockIdx.z) == 0) hb_pdl_wait();  // the grid never ends before the one ahead of it
+    if constexpr (CL) { hb_cluster_sync(); hb_cluster_sync(); }      // the cluster's two barriers, as every block of it
     return;
   }
   const int k0 = max(s * chunk, lo), k1 = min((s + 1) * chunk, p + 1), nk = k1 - k0;
@@ -324,6 +335,9 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
     const size_t head = (size_t)t * Hq + (size_t)h * G + gg;
     if (whole) {
       out[head * D + d] = __float2bfloat16_rn(a / l);
+    } else if constexpr (CL) {
+      cl_acc[i] = a;
+      if (d == 0) { cl_ml[gg * 2] = m * 0.6931471805599453f; cl_ml[gg * 2 + 1] = l; }
     } else {
       part_acc[(head * S + s) * D + d] = a;
       if (d == 0) {
@@ -333,6 +347,41 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
     }
   }
   HB_TL_MARK(1, 3);   // slot 1: the end of the chunk work; slot 0: the end of the merge
+  if constexpr (CL) {
+    hb_cluster_sync();                                     // every block's partial is in its shared memory, visible cluster-wide
+    if (!whole && s == s_lo) {
+      const int nc = s_hi - s_lo + 1;
+      const uint32_t acc_l = hb_smem_u32(cl_acc), ml_l = hb_smem_u32(cl_ml);
+      for (int i = tid; i < G * D; i += AD_THREADS) {
+        const int gg = i / D;
+        float mv[8], lv[8], av[8];                         // a cluster has at most 8 blocks
+#pragma unroll
+        for (int c = 0; c < 8; c++)
+          if (c < nc) {
+            uint32_t ra, rm;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(acc_l + (uint32_t)i * 4), "r"((uint32_t)(s_lo + c)));
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(rm) : "r"(ml_l + (uint32_t)gg * 8), "r"((uint32_t)(s_lo + c)));
+            asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(av[c]) : "r"(ra) : "memory");
+            asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(mv[c]), "=f"(lv[c]) : "r"(rm) : "memory");
+          }
+        float m = -INFINITY, a = 0.f, l = 0.f;
+#pragma unroll
+        for (int c = 0; c < 8; c++)
+          if (c < nc) m = fmaxf(m, mv[c]);
+#pragma unroll
+        for (int c = 0; c < 8; c++)
+          if (c < nc) {
+            const float f = expf(mv[c] - m);
+            l += lv[c] * f;
+            a += av[c] * f;
+          }
+        out[((size_t)t * Hq + (size_t)h * G + gg) * D + (i - gg * D)] = __float2bfloat16_rn(a / l);
+      }
+    }
+    hb_cluster_sync();                                     // no block leaves while its partial may still be read
+    HB_TL_MARK(0, 3);
+    return;
+  }
   if (whole) return;
   // the block of this (row, kv head) that ends last adds the chunks, lowest first
   __threadfence();
@@ -403,7 +452,7 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(
   HB_TL_MARK(0, 3);
 }
 
-template <int D, bool TMA, int RW, int KW, int SR>
+template <int D, bool TMA, int RW, int KW, int SR, bool CL = false>
 static int launch_decode(int G, dim3 grid, size_t smem, cudaStream_t st, const CUtensorMap& mk, const CUtensorMap& mv,
                          int* status, const __nv_bfloat16* q, const __nv_bfloat16* kc, const __nv_bfloat16* vc,
                          const int* bt, int bt_stride, const int* row_req, const int* pos, __nv_bfloat16* out, float* pa,
@@ -414,13 +463,18 @@ static int launch_decode(int G, dim3 grid, size_t smem, cudaStream_t st, const C
     {                                                                                                               \
       static bool configured = false;                                                                               \
       if (!configured) {                                                                                            \
-        cudaFuncSetAttribute(attn_decode_kernel<D, GG, TMA, RW, KW, SR>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
+        cudaFuncSetAttribute(attn_decode_kernel<D, GG, TMA, RW, KW, SR, CL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
         configured = true;                                                                                          \
       }                                                                                                             \
     }                                                                                                               \
-    hb_launch(attn_decode_kernel<D, GG, TMA, RW, KW, SR>, grid, AD_THREADS, smem, st, mk, mv, status, q, kc, vc, bt, bt_stride,  \
-              row_req, pos, out, pa, pm, Hq, Hkv, page_size, window, scale, chunk, S, q_len, row_limit, ctx_len,    \
-              counters);                                                                                            \
+    if (CL)                                                                                                         \
+      hb_launch_cluster(attn_decode_kernel<D, GG, TMA, RW, KW, SR, CL>, grid, AD_THREADS, smem, st, dim3(grid.x, 1, 1), mk, mv, status, \
+                        q, kc, vc, bt, bt_stride, row_req, pos, out, pa, pm, Hq, Hkv, page_size, window, scale, chunk, S,    \
+                        q_len, row_limit, ctx_len, counters);                                                       \
+    else                                                                                                            \
+      hb_launch(attn_decode_kernel<D, GG, TMA, RW, KW, SR, CL>, grid, AD_THREADS, smem, st, mk, mv, status, q, kc, vc, bt, bt_stride, \
+                row_req, pos, out, pa, pm, Hq, Hkv, page_size, window, scale, chunk, S, q_len, row_limit, ctx_len,  \
+                counters);                                                                                          \
     return 0;
   switch (G) {
     HB_AD_CASE(1) HB_AD_CASE(2) HB_AD_CASE(3) HB_AD_CASE(4) HB_AD_CASE(5) HB_AD_CASE(6) HB_AD_CASE(7) HB_AD_CASE(8)
@@ -489,7 +543,12 @@ HB_EXPORT int hb_attn_decode(const void* q, const void* kc, const void* vc, long
   int r = 1;
 #define HB_AD_ARGS G, grid, smem, st, mk, mv, status, qq, kk, vv, bt, bt_stride, row_req, pos, (__nv_bfloat16*)out, pa, pm, Hq, Hkv, \
                    page_size, window, sl2, chunk, S, q_len, row_limit, ctx_len, counters
-  if (D == 64 && resident) r = launch_decode<64, true, 64, 128, 128>(HB_AD_ARGS);
+  // a step of few rows whose chunks fit one cluster: the chunks' partial results meet in distributed shared memory
+  const bool cl = tma && S >= 2 && S <= 8 && T <= g_ad_cluster_rows;
+  if (D == 64 && resident && cl) r = launch_decode<64, true, 64, 128, 128, true>(HB_AD_ARGS);
+  else if (D == 64 && wide && cl) r = launch_decode<64, true, 64, 128, 64, true>(HB_AD_ARGS);
+  else if (halves && cl) r = launch_decode<128, true, 32, 64, 32, true>(HB_AD_ARGS);
+  else if (D == 64 && resident) r = launch_decode<64, true, 64, 128, 128>(HB_AD_ARGS);
   else if (D == 64 && wide) r = launch_decode<64, true, 64, 128, 64>(HB_AD_ARGS);
   else if (D == 64) r = tma ? launch_decode<64, true, 64, 64, 64>(HB_AD_ARGS) : launch_decode<64, false, 64, 64, 64>(HB_AD_ARGS);
   else if (halves) r = launch_decode<128, true, 32, 64, 32>(HB_AD_ARGS);

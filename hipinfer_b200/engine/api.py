@@ -63,6 +63,7 @@ class Engine:
         # back, so the host prepares step i + 1 while the device runs step i (see step())
         self.pipeline = bool(pipeline)
         self._pending = None
+        self._copy_stream = torch.cuda.Stream(device=r.device)
         self.last_step = None      # (rows, requests, rows of prompt portions) of the step launched last
         self._unreported: List[Request] = []
         self._ids = itertools.count()
@@ -139,10 +140,17 @@ class Engine:
         if samplers:
             tokens_dev = self.sampler.sample_device(logits, [s.request.params for s in samplers],
                                                     [s.start + s.n for s in samplers])
+            # the tokens go to the host on a stream of their own: a copy in the compute stream would stand between this
+            # step's last kernel and the next step's first (the copy engine's turn-around, some 10 us a step)
             host = torch.empty(len(samplers), dtype=torch.int32, pin_memory=True)
-            host.copy_(tokens_dev, non_blocking=True)
+            sampled = torch.cuda.Event()
+            sampled.record()
             event = torch.cuda.Event()
-            event.record()
+            with torch.cuda.stream(self._copy_stream):
+                self._copy_stream.wait_event(sampled)
+                host.copy_(tokens_dev, non_blocking=True)
+                event.record(self._copy_stream)
+            tokens_dev.record_stream(self._copy_stream)
             pending.update(tokens_dev=tokens_dev, host=host, event=event)
         self.scheduler.update(sched, [self.PLACEHOLDER] * len(samplers))
         pending["slots"] = [(s.request, len(s.request.output) - 1) for s in samplers]

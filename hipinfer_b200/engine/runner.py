@@ -58,7 +58,7 @@ class ModelRunner:
         # decode-only steps (one token per request, every row wanted) are replayed from a CUDA
         # graph captured per number of requests: same kernels, one launch
         self.cuda_graphs = bool(cuda_graphs)
-        self._graphs: Dict[int, dict] = {}
+        self._graphs: Dict[tuple, dict] = {}
         self._table_widths = [pages_per_seq] * len(groups)
         self._np_tables: Dict[object, list] = {}
 
@@ -194,14 +194,21 @@ class ModelRunner:
             from ..kernels import ops
             ops.feed_tokens(tokens, device_tokens, map_dev)
 
+    GRAPH_LENGTH_QUANTUM = 512     # tokens by which the length class of a decode graph grows
+    MAX_GRAPHS = 24                # captured graphs kept (each holds its batch buffer and its logits)
+
     def _graph_step(self, entries, ctx_lens, slots, tables, slot_maps, device_tokens=None, token_map=None) -> torch.Tensor:
-        """A decode-only step through the CUDA graph for this many requests (captured at first use).
-        The graph's batch lives in one static device buffer that each step overwrites; launch
-        geometry is made for the longest sequence, so blocks beyond a row's keys return at once.
-        The logits tensor is the graph's own and is overwritten by the next such step."""
+        """A decode-only step through the CUDA graph for this many requests and this length class (captured at
+        first use). The graph's batch lives in one static device buffer that each step overwrites; launch
+        geometry is made for the longest position of the class (the step's longest request rounded up to
+        GRAPH_LENGTH_QUANTUM tokens), so few blocks lie beyond a row's keys and those return at once; a new
+        graph is captured when the longest request crosses into the next class. The logits tensor is the
+        graph's own and is overwritten by the next such step."""
         R, G = len(entries), len(self.cache.groups)
-        g = self._graphs.get(R)
-        args = dict(n_groups=G, device=self.device, table_widths=self._table_widths, max_pos=self.max_model_len - 1)
+        bound = min(self.max_model_len, (max(ctx_lens) // self.GRAPH_LENGTH_QUANTUM + 1) * self.GRAPH_LENGTH_QUANTUM)
+        key = (R, bound)
+        g = self._graphs.get(key)
+        args = dict(n_groups=G, device=self.device, table_widths=self._table_widths, max_pos=bound - 1)
         if g is None:
             n_int = 4 * R + 4 * R + R + sum(R * w for w in self._table_widths) + G * R
             static = torch.zeros(n_int, dtype=torch.int32, device=self.device)
@@ -214,7 +221,9 @@ class ModelRunner:
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):                      # recorded, not run
                 logits = self.model.forward(batch, self.storage)
-            self._graphs[R] = dict(graph=graph, static=static, logits=logits, tokens=batch.tokens,
+            while len(self._graphs) >= self.MAX_GRAPHS:          # the oldest class goes (requests only grow)
+                self._graphs.pop(next(iter(self._graphs)))
+            self._graphs[key] = dict(graph=graph, static=static, logits=logits, tokens=batch.tokens,
                                    token_map=batch.token_map, launches=library.launches[0] - before)
             # the step has run once already: replaying the graph now would run it a second time, which a mixer
             # with state of its own (its state advances with every run) must not see

@@ -278,7 +278,12 @@ def linear_swiglu(a, w, act_out, group) -> bool:
 # a few token rows (csrc/gemm_rows.cu): whole-K output stripes, norm in the prologue, the layer's
 # own arithmetic in the epilogue; a decoder layer of a small decode step is five kernels
 # ------------------------------------------------------------------------------------------
-ROWS_MAX = 16           # token rows up to which the rows kernels are used
+ROWS_MAX = 8            # token rows up to which the rows kernels are used (they take up to 16; measured at the 1B shape,
+                        # steps of 9 to 16 rows are 9 to 13 % faster through the split-K kernels below: two rows a warp
+                        # in the norm prologue and twice the rows from L2 for every block)
+
+
+ROWS_LIMIT = 16         # what the kernels themselves take (the functions below; the engine's choice is ROWS_MAX)
 
 
 def _rows_w_ok(w) -> bool:
@@ -288,7 +293,7 @@ def _rows_w_ok(w) -> bool:
 
 def _rows_norm_ok(x, norm_w, w) -> bool:
     M, K = x.shape
-    return (M <= ROWS_MAX and x.is_cuda and x.dtype == torch.float32 and x.stride(1) == 1 and x.stride(0) % 4 == 0
+    return (M <= ROWS_LIMIT and x.is_cuda and x.dtype == torch.float32 and x.stride(1) == 1 and x.stride(0) % 4 == 0
             and x.data_ptr() % 16 == 0 and norm_w.dtype == torch.bfloat16 and norm_w.is_contiguous() and norm_w.numel() == K
             and _rows_w_ok(w) and w.shape[1] == K and bool(_fn("hb_rows_norm_supported")(M, K)))
 
@@ -315,7 +320,7 @@ def rows_norm_qkv_rope(x, norm_w, eps, w, positions, slot_map, table, q_out, k_c
 def rows_add(act, w, out) -> bool:
     """out (fp32) += act @ w.T for a few bf16 rows, finished in one kernel (no slices). False: nothing done."""
     M, K = act.shape
-    if (M > ROWS_MAX or not act.is_cuda or act.dtype != torch.bfloat16 or act.stride(1) != 1 or act.stride(0) % 8
+    if (M > ROWS_LIMIT or not act.is_cuda or act.dtype != torch.bfloat16 or act.stride(1) != 1 or act.stride(0) % 8
             or act.data_ptr() % 16 or not _rows_w_ok(w) or w.shape[1] != K or out.dtype != torch.float32 or out.stride(1) != 1):
         return False
     _call("hb_rows_add", act.data_ptr(), act.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0), M, w.shape[0],

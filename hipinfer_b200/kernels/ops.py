@@ -394,7 +394,7 @@ def linear_add_rows(a: torch.Tensor, w: "Weight", out: torch.Tensor) -> bool:
     """out += a @ w.T finished in one kernel for a few rows (whole-K stripes, nothing left to add); False: nothing was done."""
     from . import fast
 
-    return a.is_cuda and fast.rows_add(a, w.t, out)
+    return a.is_cuda and a.shape[0] <= fast.ROWS_MAX and fast.rows_add(a, w.t, out)
 
 
 class Pending:
