@@ -408,13 +408,16 @@ static int rows_launch(RowsArgs a, cudaStream_t s) {
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const size_t fixed = rows_fixed_bytes<MT, A_MODE>(a.K);
-  const size_t budget = (size_t)g_rows_budget_kb[EPI == RW_ADD && a.K > 2 * RW_KC ? 3 : EPI] * 1024;
+  a.n_tiles = (a.N + R - 1) / R;
+  // a deep ring of one block per SM, unless there are more tiles than SMs and fewer than two rounds of them: then
+  // two smaller blocks share an SM, so that every tile streams from the start (a second round would double the time)
+  const bool deep = a.n_tiles <= sms || a.n_tiles >= 2 * sms;
+  const size_t budget = (size_t)g_rows_budget_kb[EPI == RW_ADD ? (a.K > 2 * RW_KC && deep ? 3 : 1) : EPI == RW_SWIGLU && !deep ? 1 : EPI] * 1024;
   if (fixed + 2 * (STAGE + 16) > RW_SMEM_MAX) HB_FAIL("hb_rows: K = %d with %d token rows does not fit shared memory", a.K, MT);
   int stages = fixed + 2 * (STAGE + 16) > budget ? 2 : (int)((budget - fixed) / (STAGE + 16));
   if (stages > 12) stages = 12;
   a.stages = stages;
   const size_t smem = fixed + (size_t)stages * (STAGE + 16);
-  a.n_tiles = (a.N + R - 1) / R;
   auto kern = rows_product_kernel<MT, A_MODE, EPI>;
   static bool configured[64] = {};      // the attribute belongs to a device: set once on each
   if (dev < 0 || dev >= 64 || !configured[dev]) {
