@@ -41,7 +41,7 @@
 
 HB_TL_DEFINE(rows)
 
-enum { RW_A_BF16 = 0, RW_A_NORM = 1 };
+enum { RW_A_BF16 = 0, RW_A_NORM = 1, RW_A_SCALED = 2 };
 enum { RW_ROPE_KV = 0, RW_ADD = 1, RW_SWIGLU = 2 };
 constexpr int RW_R = 16;                         // weight rows of a tile: one m16 MMA tile
 constexpr int RW_KC = 1024;                      // K elements of a stage: a copy brings 2 KB of one row
@@ -59,6 +59,11 @@ struct RowsArgs {
   __nv_bfloat16 *q_out, *kc, *vc;
   int Hq, Hkv, D, page_size;
   int* status;
+  // ADD, optional: what the NEXT norm's consumer wants, made while the new residual values are in registers:
+  // xb [M, N] bf16 = x_new * next_w (not yet divided by the row's RMS), ssq_part [N / 16][16] = each tile's share of sum(x_new^2)
+  const __nv_bfloat16* next_w; __nv_bfloat16* xb; long ldxb; float* ssq_part;
+  // A_SCALED: A is such an xb; the row's 1 / RMS comes from ssq_part (n_parts tiles) and is applied in the epilogue
+  int n_parts;
 };
 
 __device__ __forceinline__ void rw_bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
@@ -93,17 +98,21 @@ __device__ __forceinline__ long rw_row(const RowsArgs& a, int t, int r) {
 template <int MT, int A_MODE, int EPI>
 __global__ void __launch_bounds__(RW_THREADS, 2) rows_product_kernel(const RowsArgs a) {
   constexpr int NTILES = MT / 8;
-  constexpr int W_STAGE = RW_R * RW_ROWB, A_STAGE = A_MODE == RW_A_BF16 ? MT * RW_ROWB : 0, STAGE = W_STAGE + A_STAGE;
+  constexpr bool STREAM_A = A_MODE == RW_A_BF16;     // the token rows come through the ring; else they lie in shared memory (xs)
+  constexpr int W_STAGE = RW_R * RW_ROWB, A_STAGE = STREAM_A ? MT * RW_ROWB : 0, STAGE = W_STAGE + A_STAGE;
   extern __shared__ __align__(128) uint8_t smem[];
   const int stages = a.stages;
   uint8_t* ring = smem;
   float* red = (float*)(smem + (size_t)stages * STAGE);                        // [consumers][16][MT]
-  uint8_t* xs = (uint8_t*)(red + RW_CONSUMERS * RW_R * MT);                    // A_NORM: [MT][K * 2 + 64]
+  uint8_t* xs = (uint8_t*)(red + RW_CONSUMERS * RW_R * MT);                    // A_NORM, A_SCALED: [MT][K * 2 + 64]
   const int xs_rowb = a.K * 2 + RW_PAD;
-  uint8_t* wsm = xs + (A_MODE == RW_A_NORM ? (size_t)MT * xs_rowb : 0);       // A_NORM: the norm's weight, [K] bf16
+  uint8_t* wsm = xs + (!STREAM_A ? (size_t)MT * xs_rowb : 0);                 // A_NORM: the norm's weight, [K] bf16
   uint64_t* full = (uint64_t*)(wsm + (A_MODE == RW_A_NORM ? (size_t)a.K * 2 : 0));
   uint64_t* empty = full + stages;
+  uint64_t* xbar = empty + stages;                                            // A_SCALED: the token rows have arrived in xs
+  uint64_t* rbar = xbar + 1;                                                  // A_SCALED: rs is written
   __shared__ int abort_word;
+  __shared__ float rs[16];               // A_SCALED: 1 / RMS of the token rows
   volatile int* abort_flag = &abort_word;
 
   hb_pdl_launch();
@@ -116,11 +125,13 @@ __global__ void __launch_bounds__(RW_THREADS, 2) rows_product_kernel(const RowsA
   // Lane r < 16 of the producer warp brings weight row r of every unit, lane 16 + m activation row m (A_BF16). A copy is
   // one instruction of one lane with everything it needs in registers: a thread that loops over a stage's copies, or
   // divides to find its addresses, hands the copy engine far less than the memory can deliver (measured: 2 to 3 TB/s).
-  constexpr int ARRIVALS = A_MODE == RW_A_BF16 ? 32 : 16;
-  const bool w_lane = lane < RW_R, a_lane = A_MODE == RW_A_BF16 && lane >= 16 && lane - 16 < a.M;
+  constexpr int ARRIVALS = STREAM_A ? 32 : 16;
+  const bool w_lane = lane < RW_R, a_lane = STREAM_A && lane >= 16 && lane - 16 < a.M;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; s++) { hb_mbar_init(&full[s], ARRIVALS); hb_mbar_init(&empty[s], RW_CONSUMERS); }
+    hb_mbar_init(xbar, 1);
+    hb_mbar_init(rbar, RW_WARPS - RW_CONSUMERS - 1);
     *abort_flag = 0;
     hb_fence_barrier_init();
   }
@@ -172,12 +183,38 @@ __global__ void __launch_bounds__(RW_THREADS, 2) rows_product_kernel(const RowsA
   hb_pdl_wait();
   HB_TL_MARK(EPI * 3 + 0, 1);
   if (producer && !w_lane) {
-    if (A_MODE == RW_A_BF16)
+    if (STREAM_A)
       for (int u = 0; u < pre; u++) p_issue(true, true);
     else
       for (int u = 0; u < pre; u++) p_issue(false, false);      // (idle lanes keep the same counters)
   }
 
+  if constexpr (A_MODE == RW_A_SCALED) {
+    // the token rows (already times the norm's weight, bf16) come into xs by bulk copy, a lane of the producer warp per row
+    if (producer && lane == 0) hb_mbar_expect_tx(xbar, (uint32_t)(a.M * a.K * 2));
+    __syncwarp();
+    if (producer && lane < a.M)
+      rw_bulk_load(xs + (size_t)lane * xs_rowb, (const __nv_bfloat16*)a.A + (long)lane * a.lda, (uint32_t)(a.K * 2), xbar);
+    // the rows' sums of squares were left in pieces, one per tile of the product that wrote the residual: the three warps
+    // that neither multiply nor copy add them, a row at a time in a fixed order, while the others go on; the epilogue
+    // waits for them (rbar). Eight loads of a lane are in flight at once.
+    if (warp > RW_CONSUMERS) {
+      for (int m = warp - RW_CONSUMERS - 1; m < a.M; m += RW_WARPS - RW_CONSUMERS - 1) {
+        float ss = 0.f;
+        for (int p0 = lane; p0 < a.n_parts; p0 += 32 * 8) {
+          float v[8];
+#pragma unroll
+          for (int j = 0; j < 8; j++) v[j] = p0 + 32 * j < a.n_parts ? __ldcg(a.ssq_part + (size_t)(p0 + 32 * j) * 16 + m) : 0.f;
+#pragma unroll
+          for (int j = 0; j < 8; j++) ss += v[j];
+        }
+        ss = hb_warp_sum(ss);
+        if (lane == 0) rs[m] = rsqrtf(ss / (float)a.K + a.eps);
+      }
+      __syncwarp();
+      if (lane == 0) hb_mbar_arrive(rbar);
+    }
+  }
   if constexpr (A_MODE == RW_A_NORM) {
     // RMSNorm of the token rows into shared memory, a warp per row (all eight warps): x * rsqrt(mean(x^2) + eps) * w,
     // in fp32, rounded once
@@ -246,7 +283,7 @@ __global__ void __launch_bounds__(RW_THREADS, 2) rows_product_kernel(const RowsA
 
   if (warp >= RW_CONSUMERS) {
     // ---------------- producer warp: refill a stage as soon as the consumers are done with it
-    if (producer && (w_lane || A_MODE == RW_A_BF16))
+    if (producer && (w_lane || STREAM_A))
       while (p_u < total) {
         if (!hb_mbar_wait(&empty[p_s], (uint32_t)p_par ^ 1, abort_flag)) break;
         p_issue(true, true);
@@ -256,11 +293,37 @@ __global__ void __launch_bounds__(RW_THREADS, 2) rows_product_kernel(const RowsA
     const int g = lane >> 2, tq = lane & 3;
     int s = 0, par = 0;
     bool ok = true;      // false once a wait of this warp gave up; the warp still passes every barrier of the block
+    if constexpr (A_MODE == RW_A_SCALED) ok = hb_mbar_wait(xbar, 0, abort_flag);
     for (int ti = 0; ti < my_tiles; ti++) {
       const int t = blockIdx.x + ti * gridDim.x;
       // The steps of a tile go to SETS independent accumulators in turn (added up at the end): the MMAs of a round do
       // not wait for one another. The same number for 8 and 16 token rows, so that a row's sum has one order.
       constexpr int SETS = 4;
+      // What the epilogue reads from memory does not depend on the product: it is asked for now and has come by then.
+      // ADD: a thread's (at most two) old residual values and next-norm weights; ROPE_KV: its row's (cos, sin) and slot.
+      constexpr int EPI_ITEMS = (EPI == RW_ADD ? RW_R : 8) * MT, EPI_PER = (EPI_ITEMS + RW_CONSUMERS * 32 - 1) / (RW_CONSUMERS * 32);
+      float pre_x[EPI_PER], pre_w[EPI_PER];
+      float2 pre_cs[EPI_PER];
+      int pre_slot[EPI_PER];
+#pragma unroll
+      for (int e = 0; e < EPI_PER; e++) {
+        const int i = (int)threadIdx.x + e * RW_CONSUMERS * 32;
+        pre_x[e] = 0.f; pre_w[e] = 0.f; pre_cs[e] = make_float2(1.f, 0.f); pre_slot[e] = -1;
+        if constexpr (EPI == RW_ADD) {
+          const int m = i >> 4, r = i & 15;
+          const long n = (long)t * RW_R + r;
+          if (i < EPI_ITEMS && m < a.M && n < a.N) {
+            pre_x[e] = __ldcg((const float*)a.out + (long)m * a.ldo + n);
+            if (a.next_w) pre_w[e] = __bfloat162float(a.next_w[n]);
+          }
+        } else if constexpr (EPI == RW_ROPE_KV) {
+          const int m = i >> 3, j = i & 7, per_head = a.D >> 4, hh = t / per_head, d = (t - hh * per_head) * 8 + j;
+          if (i < EPI_ITEMS && m < a.M) {
+            if (hh < a.Hq + a.Hkv) pre_cs[e] = a.table[(size_t)a.pos[m] * (a.D >> 1) + d];
+            if (hh >= a.Hq && a.slot_map) pre_slot[e] = a.slot_map[m];
+          }
+        }
+      }
       float acc[SETS][NTILES][4];
 #pragma unroll
       for (int e = 0; e < SETS; e++)
@@ -284,9 +347,9 @@ __global__ void __launch_bounds__(RW_THREADS, 2) rows_product_kernel(const RowsA
         // with k = 8 tq + {0, 1, 2, 3} in the first step and 8 tq + {4, 5, 6, 7} in the second: a sum over k does not
         // care in which slot a k sits, and three 16-byte loads feed two MMAs instead of twelve 4-byte ones.
         const uint8_t* a_base = ws + g * RW_ROWB + tq * 16;
-        const uint8_t* b_base = A_MODE == RW_A_NORM ? xs + (size_t)g * xs_rowb + (size_t)k0 * 2 + tq * 16
+        const uint8_t* b_base = !STREAM_A ? xs + (size_t)g * xs_rowb + (size_t)k0 * 2 + tq * 16
                                                     : ws + W_STAGE + g * RW_ROWB + tq * 16;
-        const size_t b_rows8 = A_MODE == RW_A_NORM ? (size_t)8 * xs_rowb : (size_t)8 * RW_ROWB;
+        const size_t b_rows8 = !STREAM_A ? (size_t)8 * xs_rowb : (size_t)8 * RW_ROWB;
         const int blocks32 = steps >> 1;
         auto round = [&](int kb, int e0) {       // 32 of K: three 16-byte loads a token tile, two MMAs
           const uint4 lo = *(const uint4*)(a_base + kb * 64), hi = *(const uint4*)(a_base + 8 * RW_ROWB + kb * 64);
@@ -324,6 +387,8 @@ __global__ void __launch_bounds__(RW_THREADS, 2) rows_product_kernel(const RowsA
         *(float2*)(mine + g * MT + col) = make_float2(v[0], v[1]);
         *(float2*)(mine + (g + 8) * MT + col) = make_float2(v[2], v[3]);
       }
+      if constexpr (A_MODE == RW_A_SCALED)
+        if (ti == 0 && !hb_mbar_wait(rbar, 0, abort_flag)) ok = false;
       rw_consumer_sync();
       const int tid = *abort_flag ? RW_THREADS : (int)threadIdx.x;      // a block that gave up stores nothing
       auto total_of = [&](int r, int m) {
@@ -332,30 +397,50 @@ __global__ void __launch_bounds__(RW_THREADS, 2) rows_product_kernel(const RowsA
         for (int w = 0; w < RW_CONSUMERS; w++) v += red[(w * RW_R + r) * MT + m];
         return v;
       };
+      auto scale_of = [&](int m) { return A_MODE == RW_A_SCALED ? rs[m] : 1.f; };
       if constexpr (EPI == RW_ADD) {
-        for (int i = tid; i < RW_R * MT; i += RW_CONSUMERS * 32) {
+#pragma unroll
+        for (int e = 0; e < EPI_PER; e++) {
+          const int i = tid + e * RW_CONSUMERS * 32;
+          if (i >= RW_R * MT) break;
           const int m = i >> 4, r = i & 15;
           const long n = (long)t * RW_R + r;
-          if (m < a.M && n < a.N) ((float*)a.out)[(long)m * a.ldo + n] += total_of(r, m);
+          float xn = 0.f;
+          if (m < a.M && n < a.N) {
+            xn = pre_x[e] + total_of(r, m);
+            ((float*)a.out)[(long)m * a.ldo + n] = xn;
+            if (a.next_w) a.xb[(long)m * a.ldxb + n] = __float2bfloat16_rn(xn * pre_w[e]);
+          }
+          if (a.next_w) {               // the 16 lanes that hold a row's 16 columns add their squares, in a fixed order
+            float sq = xn * xn;
+            sq += __shfl_xor_sync(0xffffffffu, sq, 8);
+            sq += __shfl_xor_sync(0xffffffffu, sq, 4);
+            sq += __shfl_xor_sync(0xffffffffu, sq, 2);
+            sq += __shfl_xor_sync(0xffffffffu, sq, 1);
+            if (r == 0 && m < a.M) a.ssq_part[(size_t)t * 16 + m] = sq;
+          }
         }
       } else if constexpr (EPI == RW_SWIGLU) {
         for (int i = tid; i < 8 * MT; i += RW_CONSUMERS * 32) {
           const int m = i >> 3, j = i & 7;
           if (m < a.M && rw_row<EPI>(a, t, 8 + j) < a.N) {
-            const float gt = total_of(j, m), up = total_of(8 + j, m);
+            const float gt = total_of(j, m) * scale_of(m), up = total_of(8 + j, m) * scale_of(m);
             ((__nv_bfloat16*)a.out)[(long)m * a.ldo + (long)t * 8 + j] = __float2bfloat16_rn(gt / (1.f + __expf(-gt)) * up);
           }
         }
       } else {
         const int half = a.D >> 1, per_head = a.D >> 4;
         const int hh = t / per_head, d0 = (t - hh * per_head) * 8;
-        for (int i = tid; i < 8 * MT; i += RW_CONSUMERS * 32) {
+#pragma unroll
+        for (int e = 0; e < EPI_PER; e++) {
+          const int i = tid + e * RW_CONSUMERS * 32;
+          if (i >= 8 * MT) break;
           const int m = i >> 3, j = i & 7, d = d0 + j;
           if (m >= a.M) continue;
-          const float x1 = total_of(j, m), x2 = total_of(8 + j, m);
+          const float x1 = total_of(j, m) * scale_of(m), x2 = total_of(8 + j, m) * scale_of(m);
           float y1 = x1, y2 = x2;
           if (hh < a.Hq + a.Hkv) {
-            const float2 cs = a.table[(size_t)a.pos[m] * half + d];
+            const float2 cs = pre_cs[e];
             y1 = __fsub_rn(__fmul_rn(x1, cs.x), __fmul_rn(x2, cs.y));
             y2 = __fadd_rn(__fmul_rn(x2, cs.x), __fmul_rn(x1, cs.y));
           }
@@ -363,7 +448,7 @@ __global__ void __launch_bounds__(RW_THREADS, 2) rows_product_kernel(const RowsA
           if (hh < a.Hq) {
             dst = a.q_out + ((long)m * a.Hq + hh) * a.D + d;
           } else {
-            const int slot = a.slot_map ? a.slot_map[m] : -1;
+            const int slot = pre_slot[e];
             if (slot < 0) continue;
             const long page = slot / a.page_size, off = slot % a.page_size;
             const bool is_k = hh < a.Hq + a.Hkv;
@@ -397,7 +482,8 @@ HB_EXPORT void hb_rows_set_budget(int epi, int kb) {
 constexpr size_t RW_SMEM_MAX = 220 * 1024;
 
 template <int MT, int A_MODE> static size_t rows_fixed_bytes(int K) {
-  return (size_t)RW_CONSUMERS * RW_R * MT * 4 + (A_MODE == RW_A_NORM ? (size_t)MT * (K * 2 + RW_PAD) + (size_t)K * 2 : 0) + 256;
+  return (size_t)RW_CONSUMERS * RW_R * MT * 4 + (A_MODE != RW_A_BF16 ? (size_t)MT * (K * 2 + RW_PAD) : 0) +
+         (A_MODE == RW_A_NORM ? (size_t)K * 2 : 0) + 256;
 }
 
 template <int MT, int A_MODE, int EPI>
@@ -462,15 +548,50 @@ HB_EXPORT int hb_rows_norm_qkv_rope(const float* x, long ldx, const void* norm_w
   return M <= 8 ? rows_launch<8, RW_A_NORM, RW_ROPE_KV>(a, s) : rows_launch<16, RW_A_NORM, RW_ROPE_KV>(a, s);
 }
 
-// out fp32 [M, N] (row stride ldo) += act [M, K] (bf16) W[N, K]^T.
+// out fp32 [M, N] (row stride ldo) += act [M, K] (bf16) W[N, K]^T. With next_w (bf16 [N], the weight of the norm that reads
+// `out` next): also xb [M, N] bf16 (row stride ldxb) = out * next_w, and ssq_part [ceil(N / 16)][16] floats = each 16-column
+// tile's share of the rows' sums of squares; hb_rows_scaled_* take those in place of the residual rows.
 HB_EXPORT int hb_rows_add(const void* act, long lda, const void* W, long ldw, float* out, long ldo, int M, int N, int K,
-                          int* status, cudaStream_t s) {
+                          const void* next_w, void* xb, long ldxb, float* ssq_part, int* status, cudaStream_t s) {
   RowsArgs a = {};
   a.A = act; a.lda = lda; a.W = (const __nv_bfloat16*)W; a.ldw = ldw; a.M = M; a.N = N; a.K = K; a.out = out; a.ldo = ldo;
-  a.status = status;
+  a.status = status; a.next_w = (const __nv_bfloat16*)next_w; a.xb = (__nv_bfloat16*)xb; a.ldxb = ldxb; a.ssq_part = ssq_part;
   if (M <= 0 || N <= 0) return 0;
   if (rows_check("hb_rows_add", a, false)) return -1;
+  if (next_w && (!xb || !ssq_part)) HB_FAIL("hb_rows_add: next_w without xb and ssq_part");
   return M <= 8 ? rows_launch<8, RW_A_BF16, RW_ADD>(a, s) : rows_launch<16, RW_A_BF16, RW_ADD>(a, s);
+}
+
+// hb_rows_norm_qkv_rope with the normalisation prepared by the product that wrote the residual (hb_rows_add with next_w):
+// xb [M, K] bf16 = x * norm_w and ssq_part [n_parts][16] in place of x and norm_w; 1 / RMS is applied in the epilogue.
+HB_EXPORT int hb_rows_scaled_qkv_rope(const void* xb, long ldxb, const float* ssq_part, int n_parts, float eps, const void* W,
+                                      long ldw, int M, int K, const int* pos, const int* slot_map, const void* table,
+                                      void* q_out, void* kc, void* vc, int Hq, int Hkv, int D, int page_size, int* status,
+                                      cudaStream_t s) {
+  RowsArgs a = {};
+  a.A = xb; a.lda = ldxb; a.ssq_part = (float*)ssq_part; a.n_parts = n_parts; a.eps = eps; a.W = (const __nv_bfloat16*)W; a.ldw = ldw;
+  a.M = M; a.N = (Hq + 2 * Hkv) * D; a.K = K; a.pos = pos; a.slot_map = slot_map; a.table = (const float2*)table;
+  a.q_out = (__nv_bfloat16*)q_out; a.kc = (__nv_bfloat16*)kc; a.vc = (__nv_bfloat16*)vc;
+  a.Hq = Hq; a.Hkv = Hkv; a.D = D; a.page_size = page_size; a.status = status;
+  if (M <= 0) return 0;
+  if (rows_check("hb_rows_scaled_qkv_rope", a, false)) return -1;
+  if (D < 16 || (D & 15)) HB_FAIL("hb_rows_scaled_qkv_rope: head_dim %d must be a multiple of 16", D);
+  if (!ssq_part || n_parts * 16 != K) HB_FAIL("hb_rows_scaled_qkv_rope: %d pieces of the sums of squares for a width of %d", n_parts, K);
+  if (!pos || !table || !q_out || (slot_map && (!kc || !vc))) HB_FAIL("hb_rows_scaled_qkv_rope: a null argument");
+  return M <= 8 ? rows_launch<8, RW_A_SCALED, RW_ROPE_KV>(a, s) : rows_launch<16, RW_A_SCALED, RW_ROPE_KV>(a, s);
+}
+
+// hb_rows_norm_swiglu with the normalisation prepared the same way.
+HB_EXPORT int hb_rows_scaled_swiglu(const void* xb, long ldxb, const float* ssq_part, int n_parts, float eps, const void* W,
+                                    long ldw, void* out, long ldo, int M, int N, int K, int* status, cudaStream_t s) {
+  RowsArgs a = {};
+  a.A = xb; a.lda = ldxb; a.ssq_part = (float*)ssq_part; a.n_parts = n_parts; a.eps = eps; a.W = (const __nv_bfloat16*)W; a.ldw = ldw;
+  a.M = M; a.N = N; a.K = K; a.out = out; a.ldo = ldo; a.status = status;
+  if (M <= 0 || N <= 0) return 0;
+  if (rows_check("hb_rows_scaled_swiglu", a, false)) return -1;
+  if (N & 31) HB_FAIL("hb_rows_scaled_swiglu: N = %d must be a multiple of 32 (gate and up rows in groups of 16)", N);
+  if (!ssq_part || n_parts * 16 != K) HB_FAIL("hb_rows_scaled_swiglu: %d pieces of the sums of squares for a width of %d", n_parts, K);
+  return M <= 8 ? rows_launch<8, RW_A_SCALED, RW_SWIGLU>(a, s) : rows_launch<16, RW_A_SCALED, RW_SWIGLU>(a, s);
 }
 
 // out bf16 [M, N / 2] = silu(gate) * up of x's RMSNorm times W [N, K], whose rows alternate 16 gate rows and their 16 up rows.

@@ -157,7 +157,7 @@ HB_EXPORT int hb_rope_kv_slices(const float* ws, int ksplit, long slice_stride, 
     HB_FAIL("hb_rope_kv_slices: pointers and strides must be multiples of 16 bytes");
   if (ksplit < 1) HB_FAIL("hb_rope_kv_slices: %d slices", ksplit);
   const int items = (Hq + Hkv) * (D >> 3) + Hkv * (D >> 2);
-  const int ny = T >= 32 ? 1 : (items + 255) / 256;
+  const int ny = T > 128 ? 1 : (items + 255) / 256;     // few rows: a row's heads are shared among several blocks
   hb_launch(rope_kv_slices_kernel, dim3(T, ny), 256, 0, s, ws, ksplit, slice_stride, row_stride, pos, slot_map,
             (const float2*)table, (__nv_bfloat16*)q_out, (__nv_bfloat16*)kc, (__nv_bfloat16*)vc, Hq, Hkv, D, page_size);
   HB_CHECK_LAUNCH("hb_rope_kv_slices");

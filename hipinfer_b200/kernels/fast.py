@@ -33,12 +33,14 @@ _SIGS = {
     "hb_attn_decode_supported": [_i, _i, _i],
     "hb_wait_selftest": [_p, _i, _p, _p],
     "hb_rows_norm_qkv_rope": [_p, _l, _p, _f, _p, _l, _i, _i, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p, _p],
-    "hb_rows_add": [_p, _l, _p, _l, _p, _l, _i, _i, _i, _p, _p],
+    "hb_rows_add": [_p, _l, _p, _l, _p, _l, _i, _i, _i, _p, _p, _l, _p, _p, _p],
+    "hb_rows_scaled_qkv_rope": [_p, _l, _p, _i, _f, _p, _l, _i, _i, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p, _p],
+    "hb_rows_scaled_swiglu": [_p, _l, _p, _i, _f, _p, _l, _p, _l, _i, _i, _i, _p, _p],
     "hb_rows_norm_swiglu": [_p, _l, _p, _f, _p, _l, _p, _l, _i, _i, _i, _p, _p],
     "hb_rows_norm_supported": [_i, _i],
 }
 _fns = {}
-_LAUNCHES = {"hb_rows_norm_qkv_rope": 1, "hb_rows_add": 1, "hb_rows_norm_swiglu": 1, "hb_gemm_tc_rope_kv": 1, "hb_gemm_stream_finish": 1, "hb_add_rmsnorm_slices": 1, "hb_rope_kv_slices": 1, "hb_gemm_tc": 1, "hb_gemm_stream": 1, "hb_attn_decode": 1, "hb_flash_prefill": 1, "hb_flash_prefill_tc": 1}
+_LAUNCHES = {"hb_rows_scaled_qkv_rope": 1, "hb_rows_scaled_swiglu": 1, "hb_rows_norm_qkv_rope": 1, "hb_rows_add": 1, "hb_rows_norm_swiglu": 1, "hb_gemm_tc_rope_kv": 1, "hb_gemm_stream_finish": 1, "hb_add_rmsnorm_slices": 1, "hb_rope_kv_slices": 1, "hb_gemm_tc": 1, "hb_gemm_stream": 1, "hb_attn_decode": 1, "hb_flash_prefill": 1, "hb_flash_prefill_tc": 1}
 _status = None
 
 EPI_F32, EPI_BF16, EPI_ADD_F32, EPI_SWIGLU_BF16, EPI_SLICES = 0, 1, 2, 3, 4
@@ -317,14 +319,75 @@ def rows_norm_qkv_rope(x, norm_w, eps, w, positions, slot_map, table, q_out, k_c
     return True
 
 
-def rows_add(act, w, out) -> bool:
-    """out (fp32) += act @ w.T for a few bf16 rows, finished in one kernel (no slices). False: nothing done."""
+class NormFeed:
+    """What the product that writes the residual rows leaves for the norm that reads them next (csrc/gemm_rows.cu):
+    xb [M, H] bf16 = x * norm weight (not yet divided by the row's RMS) and ssq [H / 16, 16] fp32, each 16-column
+    tile's share of the rows' sums of squares. The next product takes them in place of the residual rows and applies
+    1 / RMS in its epilogue: it has no norm prologue left. `filled` says whether a product has written them."""
+    __slots__ = ("weight", "eps", "xb", "ssq", "filled")
+
+    def __init__(self, weight, eps, rows):
+        H = weight.numel()
+        self.weight, self.eps, self.filled = weight, float(eps), False
+        self.xb = torch.empty(rows, H, dtype=torch.bfloat16, device=weight.device)
+        self.ssq = torch.empty(-(-H // 16), 16, dtype=torch.float32, device=weight.device)
+
+
+def norm_feed_applies(weight, rows) -> bool:
+    return (not PLAIN_ONLY and weight.is_cuda and weight.dtype == torch.bfloat16 and weight.is_contiguous()
+            and rows <= ROWS_MAX and weight.numel() % 32 == 0)
+
+
+def rows_add(act, w, out, feed: "NormFeed" = None) -> bool:
+    """out (fp32) += act @ w.T for a few bf16 rows, finished in one kernel (no slices). With feed (a NormFeed for the
+    norm of width N that reads `out` next) the kernel fills it as well. False: nothing done."""
     M, K = act.shape
     if (M > ROWS_LIMIT or not act.is_cuda or act.dtype != torch.bfloat16 or act.stride(1) != 1 or act.stride(0) % 8
             or act.data_ptr() % 16 or not _rows_w_ok(w) or w.shape[1] != K or out.dtype != torch.float32 or out.stride(1) != 1):
         return False
+    if feed is not None and (feed.weight.numel() != w.shape[0] or feed.xb.shape[0] < M):
+        feed = None
     _call("hb_rows_add", act.data_ptr(), act.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0), M, w.shape[0],
-          K, status_word().data_ptr(), _stream())
+          K, None if feed is None else feed.weight.data_ptr(), None if feed is None else feed.xb.data_ptr(),
+          0 if feed is None else feed.xb.stride(0), None if feed is None else feed.ssq.data_ptr(),
+          status_word().data_ptr(), _stream())
+    if feed is not None:
+        feed.filled = True
+    return True
+
+
+def _rows_feed_ok(feed, M, w) -> bool:
+    K = feed.weight.numel()
+    return (feed.filled and M <= ROWS_LIMIT and _rows_w_ok(w) and w.shape[1] == K
+            and bool(_fn("hb_rows_norm_supported")(M, K)))
+
+
+def rows_scaled_qkv_rope(feed, M, w, positions, slot_map, table, q_out, k_cache, v_cache, n_heads, n_kv_heads, head_dim,
+                         rotary_dim, page_size) -> bool:
+    """rows_norm_qkv_rope from a filled NormFeed in place of the residual rows (no norm prologue). False: nothing done."""
+    if (not _rows_feed_ok(feed, M, w) or head_dim % 16 or rotary_dim != head_dim
+            or w.shape[0] != (n_heads + 2 * n_kv_heads) * head_dim or q_out.dtype != torch.bfloat16 or not q_out.is_contiguous()
+            or table.dtype != torch.float32 or not table.is_contiguous()):
+        return False
+    if slot_map is not None and not (k_cache.dtype == torch.bfloat16 and v_cache.dtype == torch.bfloat16
+                                     and k_cache.is_contiguous() and v_cache.is_contiguous()):
+        return False
+    p = lambda t: None if t is None else t.data_ptr()
+    _call("hb_rows_scaled_qkv_rope", feed.xb.data_ptr(), feed.xb.stride(0), feed.ssq.data_ptr(), feed.ssq.shape[0], feed.eps,
+          w.data_ptr(), w.stride(0), M, w.shape[1], positions.data_ptr(), p(slot_map), table.data_ptr(), q_out.data_ptr(),
+          p(k_cache) if slot_map is not None else None, p(v_cache) if slot_map is not None else None, n_heads, n_kv_heads,
+          head_dim, page_size, status_word().data_ptr(), _stream())
+    return True
+
+
+def rows_scaled_swiglu(feed, M, w, act_out, group) -> bool:
+    """rows_norm_swiglu from a filled NormFeed in place of the residual rows. False: nothing done."""
+    if (group != 16 or not _rows_feed_ok(feed, M, w) or w.shape[0] % 32 or act_out.dtype != torch.bfloat16
+            or act_out.stride(1) != 1):
+        return False
+    _call("hb_rows_scaled_swiglu", feed.xb.data_ptr(), feed.xb.stride(0), feed.ssq.data_ptr(), feed.ssq.shape[0], feed.eps,
+          w.data_ptr(), w.stride(0), act_out.data_ptr(), act_out.stride(0), M, w.shape[0], w.shape[1],
+          status_word().data_ptr(), _stream())
     return True
 
 

@@ -348,10 +348,11 @@ class LazyNorm:
     """The RMSNorm of residual rows that has not been computed yet: (x fp32 [T, H], weight, eps). A part that can
     fold the norm into its own first kernel (a few rows: the product's prologue) takes it as it is; any other
     calls materialize(), which runs the norm kernel. A part says that it understands one with `takes_lazy_norm`."""
-    __slots__ = ("x", "weight", "eps", "dtype")
+    __slots__ = ("x", "weight", "eps", "dtype", "feed")
 
-    def __init__(self, x, weight, eps, dtype):
+    def __init__(self, x, weight, eps, dtype, feed=None):
         self.x, self.weight, self.eps, self.dtype = x, weight, eps, dtype
+        self.feed = feed       # a filled fast.NormFeed of this norm, left by the product that wrote x (or None)
 
     @property
     def shape(self):
@@ -379,6 +380,9 @@ def norm_linear_rope_kv_write(xn: "LazyNorm", w: "Weight", positions, slot_map, 
     """rope_kv_write of RMSNorm(x) @ w.T in one kernel for a few rows; False: nothing was done."""
     from . import fast
 
+    if xn.feed is not None and fast.rows_scaled_qkv_rope(xn.feed, xn.x.shape[0], w.t, positions, slot_map, table, q_out, k_cache,
+                                                         v_cache, n_heads, n_kv_heads, head_dim, rotary_dim, page_size):
+        return True
     return fast.rows_norm_qkv_rope(xn.x, xn.weight, xn.eps, w.t, positions, slot_map, table, q_out, k_cache, v_cache, n_heads,
                                    n_kv_heads, head_dim, rotary_dim, page_size)
 
@@ -387,14 +391,24 @@ def norm_linear_swiglu(xn: "LazyNorm", w_gate_up: "Weight", act_out: torch.Tenso
     """act_out = swiglu(RMSNorm(x) @ w_gate_up.T) in one kernel for a few rows; False: nothing was done."""
     from . import fast
 
+    if xn.feed is not None and fast.rows_scaled_swiglu(xn.feed, xn.x.shape[0], w_gate_up.t, act_out, group):
+        return True
     return fast.rows_norm_swiglu(xn.x, xn.weight, xn.eps, w_gate_up.t, act_out, group)
 
 
-def linear_add_rows(a: torch.Tensor, w: "Weight", out: torch.Tensor) -> bool:
-    """out += a @ w.T finished in one kernel for a few rows (whole-K stripes, nothing left to add); False: nothing was done."""
+def linear_add_rows(a: torch.Tensor, w: "Weight", out: torch.Tensor, norm_feed=None) -> bool:
+    """out += a @ w.T finished in one kernel for a few rows (whole-K stripes, nothing left to add); False: nothing was done.
+    norm_feed (a fast.NormFeed of the norm that reads `out` next, or None): the kernel prepares that norm on its way."""
     from . import fast
 
-    return a.is_cuda and a.shape[0] <= fast.ROWS_MAX and fast.rows_add(a, w.t, out)
+    return a.is_cuda and a.shape[0] <= fast.ROWS_MAX and fast.rows_add(a, w.t, out, norm_feed)
+
+
+def make_norm_feed(weight: torch.Tensor, eps: float, rows: int):
+    """A NormFeed for the norm (weight, eps) over `rows` residual rows, where the rows kernels apply; else None."""
+    from . import fast
+
+    return fast.NormFeed(weight, eps, rows) if fast.norm_feed_applies(weight, rows) else None
 
 
 class Pending:

@@ -94,15 +94,25 @@ class DecoderModel:
     def forward(self, batch, storage) -> torch.Tensor:
         """Run the batch's tokens from the cache; logits float32 [len(batch.want_rows), vocab]."""
         x = self.embedding.forward(batch.tokens)
-        pending = None      # what a layer has left to be added into x (kernels.ops.Pending): the next norm adds it
-        for i, st in enumerate(self.spec.order):
+        # what a layer leaves for the next reader of x: a sum not yet added (kernels.ops.Pending: the next norm adds
+        # it), or that next norm already prepared by the layer's last product (kernels.fast.NormFeed); else None
+        carry = None
+        order = self.spec.order
+        for i, st in enumerate(order):
             layer = self.layers[st.layer]
             cache, state = storage.layer_cache(self.cache_plan[i]), storage.layer_state(i)
-            if pending is not None and not layer.takes_pending:
-                pending.finish()
-                pending = None
-            left = layer.forward(x, batch, cache, state, pending) if pending is not None else layer.forward(x, batch, cache, state)
-            pending = left if isinstance(left, ops.Pending) else None
+            if carry is not None and not layer.takes_pending:
+                if isinstance(carry, ops.Pending):
+                    carry.finish()
+                carry = None
+            kw = {}
+            if carry is not None:
+                kw["pending"] = carry
+            if getattr(layer, "takes_next_norm", False) and i + 1 < len(order):
+                kw["next_norm"] = getattr(self.layers[order[i + 1].layer], "mixer_norm", None)
+            left = layer.forward(x, batch, cache, state, **kw)
+            carry = left if left is not None and not isinstance(left, torch.Tensor) else None
+        pending = carry if isinstance(carry, ops.Pending) else None
         if batch.n_want == 0:
             if pending is not None:
                 pending.finish()

@@ -56,8 +56,9 @@ class AttentionMixer(Mixer):
         return CacheNeed("window" if self.window else "full", self.n_kv_heads, self.head_dim, self.window)
 
     takes_lazy_norm = True
+    takes_norm_feed = True     # forward() accepts norm_feed=: buffers of the norm that reads x next (see parts/block.py)
 
-    def forward(self, xn, x, batch, cache, state):
+    def forward(self, xn, x, batch, cache, state, norm_feed=None):
         T = xn.shape[0]
         Hq, Hkv, D = self.n_heads, self.n_kv_heads, self.head_dim
         q = torch.empty(T, Hq * D, dtype=self.ctx.dtype, device=xn.device)
@@ -65,11 +66,11 @@ class AttentionMixer(Mixer):
         if isinstance(xn, ops.LazyNorm):     # a few rows: norm, projection, rotation and cache write as one kernel
             folded = getattr(self.position, "norm_project_rotate_and_store", None)
             if folded is not None and folded(xn, self.wqkv, batch.positions, slot_map, q, cache.k, cache.v, Hq, Hkv):
-                return self._attend_and_project(q, x, batch, cache)
+                return self._attend_and_project(q, x, batch, cache, norm_feed)
             xn = xn.materialize()
         fused = getattr(self.position, "project_rotate_and_store", None)    # many rows: the rotation in the product's epilogue
         if fused is not None and fused(xn, self.wqkv, batch.positions, slot_map, q, cache.k, cache.v, Hq, Hkv):
-            return self._attend_and_project(q, x, batch, cache)
+            return self._attend_and_project(q, x, batch, cache, norm_feed)
         qkv = torch.empty(T, (Hq + 2 * Hkv) * D, dtype=torch.float32, device=xn.device)
         pending = ops.linear_deferred(xn, self.wqkv, qkv)      # a few rows: the rotation adds the product's slices
         if pending is not None and not self.position.takes_pending:
@@ -79,15 +80,15 @@ class AttentionMixer(Mixer):
             self.position.rotate_and_store(qkv, batch.positions, slot_map, q, cache.k, cache.v, Hq, Hkv)
         else:
             self.position.rotate_and_store(qkv, batch.positions, slot_map, q, cache.k, cache.v, Hq, Hkv, pending=pending)
-        return self._attend_and_project(q, x, batch, cache)
+        return self._attend_and_project(q, x, batch, cache, norm_feed)
 
-    def _attend_and_project(self, q, x, batch, cache):
+    def _attend_and_project(self, q, x, batch, cache, norm_feed=None):
         T = q.shape[0]
         Hq, Hkv, D = self.n_heads, self.n_kv_heads, self.head_dim
         att = torch.empty(T, Hq * D, dtype=self.ctx.dtype, device=q.device)
         ops.attention(q, cache.k, cache.v, batch, cache.group, att, Hq, Hkv, D, self.ctx.page_size, self.window,
                       self.scale)
-        if ops.linear_add_rows(att, self.wo, x):                       # a few rows: added in the product's epilogue
+        if ops.linear_add_rows(att, self.wo, x, norm_feed):            # a few rows: added in the product's epilogue
             return None
         return ops.linear_deferred(att, self.wo, x, accumulate=True)   # the next norm may add it
 

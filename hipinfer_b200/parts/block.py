@@ -45,13 +45,14 @@ class PreNormBlock(Part):
         return sum(p.weight_bytes() for p in self.parts)
 
     takes_pending = True
+    takes_next_norm = True      # forward() accepts next_norm=: the norm that reads x after this layer (the next layer's first)
 
     @staticmethod
-    def _normed(norm, x, pending, consumer):
+    def _normed(norm, x, pending, consumer, feed=None):
         if pending is None:
             # a few rows: a consumer that says so gets the norm unevaluated and folds it into its first product
             if getattr(consumer, "takes_lazy_norm", False) and hasattr(norm, "lazy"):
-                lazy = norm.lazy(x)
+                lazy = norm.lazy(x, feed) if feed is not None else norm.lazy(x)
                 if lazy is not None:
                     return lazy
             return norm.forward(x)
@@ -60,13 +61,33 @@ class PreNormBlock(Part):
         pending.finish()
         return norm.forward(x)
 
-    def forward(self, x, batch, cache, state, pending=None):
-        """pending: a sum the layer before has yet to add into x. Returns what this layer leaves
-        to be added (None when x is complete)."""
-        left = self.mixer.forward(self._normed(self.mixer_norm, x, pending, self.mixer), x, batch, cache, state)
+    @staticmethod
+    def _feed_of(norm, producer, rows):
+        """Buffers for `norm` that `producer` (the part whose last product writes the norm's input) may fill, or None."""
+        if norm is None or not getattr(producer, "takes_norm_feed", False) or not hasattr(norm, "feed"):
+            return None
+        return norm.feed(rows)
+
+    def forward(self, x, batch, cache, state, pending=None, next_norm=None):
+        """pending: what the layer before left: a sum it has yet to add into x (kernels.ops.Pending), or the first
+        norm of this layer prepared by its last product (kernels.fast.NormFeed). Returns what this layer leaves in
+        the same way (None when x is complete and nothing is prepared)."""
+        feed_in = None
+        if pending is not None and not isinstance(pending, ops.Pending):
+            feed_in, pending = pending, None
+        rows = x.shape[0]
+        xn = self._normed(self.mixer_norm, x, pending, self.mixer, feed_in)
+        feed = self._feed_of(self.feed_forward_norm, self.mixer, rows)
+        left = (self.mixer.forward(xn, x, batch, cache, state, norm_feed=feed) if feed is not None
+                else self.mixer.forward(xn, x, batch, cache, state))
         pending = left if isinstance(left, ops.Pending) else None
-        left = self.feed_forward.forward(self._normed(self.feed_forward_norm, x, pending, self.feed_forward), x, batch)
-        return left if isinstance(left, ops.Pending) else None
+        xn = self._normed(self.feed_forward_norm, x, pending, self.feed_forward, feed)
+        feed = self._feed_of(next_norm, self.feed_forward, rows)
+        left = (self.feed_forward.forward(xn, x, batch, norm_feed=feed) if feed is not None
+                else self.feed_forward.forward(xn, x, batch))
+        if isinstance(left, ops.Pending):
+            return left
+        return feed if feed is not None and feed.filled else None
 
 
 register_part("block", "pre_norm", PreNormBlock)

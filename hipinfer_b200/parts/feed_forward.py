@@ -46,15 +46,16 @@ class SwiGLU(Part):
         return self.wgu.nbytes + self.wdown.nbytes
 
     takes_lazy_norm = True
+    takes_norm_feed = True     # forward() accepts norm_feed=: buffers of the norm that reads x next (see parts/block.py)
 
-    def forward(self, xn, x, batch):
+    def forward(self, xn, x, batch, norm_feed=None):
         act = torch.empty(xn.shape[0], self.inter, dtype=self.ctx.dtype, device=xn.device)
         if isinstance(xn, ops.LazyNorm):     # a few rows: the norm in the gate/up product's prologue
             if not ops.norm_linear_swiglu(xn, self.wgu, act, GROUP):
                 ops.linear_swiglu(xn.materialize(), self.wgu, act, GROUP)
         else:
             ops.linear_swiglu(xn, self.wgu, act, GROUP)
-        if ops.linear_add_rows(act, self.wdown, x):                       # a few rows: added in the product's epilogue
+        if ops.linear_add_rows(act, self.wdown, x, norm_feed):            # a few rows: added in the product's epilogue
             return None
         return ops.linear_deferred(act, self.wdown, x, accumulate=True)   # the next norm may add it
 

@@ -30,11 +30,20 @@ class RMSNorm(Part):
 
     takes_pending = True
 
-    def lazy(self, x):
-        """The norm of x left to its consumer (kernels.ops.LazyNorm) where a consumer could fold it into its product, else None."""
+    def lazy(self, x, feed=None):
+        """The norm of x left to its consumer (kernels.ops.LazyNorm) where a consumer could fold it into its product, else
+        None. feed: what `feed()` gave and the product that wrote x has filled; the consumer then needs no prologue."""
         if self.weight is None or not ops.lazy_norm_applies(x, self.weight, self.ctx.dtype):
             return None
-        return ops.LazyNorm(x, self.weight, self.eps, self.ctx.dtype)
+        ok = feed is not None and feed.filled and feed.weight is self.weight
+        return ops.LazyNorm(x, self.weight, self.eps, self.ctx.dtype, feed if ok else None)
+
+    def feed(self, rows):
+        """Buffers that the product which writes this norm's input rows may fill on its way (x times this norm's weight in
+        bf16, and the pieces of the rows' sums of squares), for steps of a few rows; else None. See kernels.fast.NormFeed."""
+        if self.weight is None or self.ctx.dtype != torch.bfloat16:
+            return None
+        return ops.make_norm_feed(self.weight, self.eps, rows)
 
     def forward(self, x, rows=None, out=None, pending=None):
         """pending: a sum that has yet to be added into x (it is added before the norm)."""

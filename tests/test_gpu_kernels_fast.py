@@ -643,3 +643,51 @@ def test_rows_kernels_refuse_what_they_do_not_take():
     assert not fast().rows_add(rnd(4, 200, seed=98), rnd(64, 200, seed=99), torch.zeros(4, 64, device=DEV))   # K no multiple of 32
     assert not fast().rows_norm_swiglu(rnd(4, 65536, seed=1, dtype=torch.float32), torch.ones(65536, dtype=torch.bfloat16, device=DEV),
                                        1e-5, rnd(32, 65536, seed=2), out[:4, :16], 16)   # rows too wide for shared memory
+
+
+@pytest.mark.parametrize("M,H,I,Hq,Hkv,D", [(8, 2048, 1024, 8, 2, 64), (1, 256, 96, 4, 2, 32), (5, 3072, 512, 6, 2, 128), (13, 512, 160, 4, 4, 16)])
+def test_rows_add_prepares_the_next_norm(M, H, I, Hq, Hkv, D):
+    """The residual add that also leaves x * (next norm's weight) in bf16 and the pieces of the rows' sums of squares,
+    and the two products that take those in place of the residual rows (1 / RMS in their epilogue): against the plain
+    statement (norm rounded once, products in float64), and x itself the same bits as without the preparation."""
+    from hipinfer_b200.kernels import ops
+
+    act, wd = rnd(M, I, seed=101), rnd(H, I, seed=102, scale=0.1)
+    x0 = rnd(M, H, seed=103, dtype=torch.float32, scale=2.0)
+    nw = (1 + 0.2 * torch.randn(H, generator=torch.Generator().manual_seed(104))).bfloat16().to(DEV)
+    feed = fast().NormFeed(nw, 1e-5, M)
+    x1, x2 = x0.clone(), x0.clone()
+    assert fast().rows_add(act, wd, x1, feed) and feed.filled
+    assert fast().rows_add(act, wd, x2)
+    sync_check()
+    assert torch.equal(x1, x2)
+    assert float((feed.xb.float() - x1 * nw.float()).abs().max()) <= 2 ** -8 * float((x1 * nw.float()).abs().max())
+    ssq = feed.ssq.sum(0)[:M].double()
+    assert float((ssq - (x1.double() ** 2).sum(-1)).abs().max()) < 1e-4 * float(ssq.max())
+    xn = _rms(x1, nw, 1e-5).double()
+    # gate/up from the feed
+    g, u = rnd(I, H, seed=105, scale=0.2), rnd(I, H, seed=106, scale=0.2)
+    gu = torch.stack([g.reshape(I // 16, 16, H), u.reshape(I // 16, 16, H)], 1).reshape(2 * I, H).contiguous()
+    gg, uu = xn @ g.double().T, xn @ u.double().T
+    ref = gg / (1 + torch.exp(-gg)) * uu
+    out = torch.full((M + 1, I), 7.0, dtype=torch.bfloat16, device=DEV)
+    assert fast().rows_scaled_swiglu(feed, M, gu, out[:M], 16)
+    sync_check()
+    assert float((out[:M].double() - ref).abs().max()) < 1.5e-2 * max(1.0, float(ref.abs().max()))
+    assert bool((out[M] == 7.0).all())
+    # q/k/v with rotation from the feed, against the kernel that normalises itself
+    N = (Hq + 2 * Hkv) * D
+    w = rnd(N, H, seed=107, scale=0.1)
+    table = ops.rope_table((10000.0 ** (-torch.arange(0, D, 2, dtype=torch.float64) / D)).float().to(DEV), 512)
+    pos = torch.arange(M, dtype=torch.int32, device=DEV) * 7 + 3
+    slots = torch.arange(M, dtype=torch.int32, device=DEV) * 3 + 1
+    mk = lambda: torch.full((M * 3 // 16 + 2, Hkv, 16, D), 3.0, dtype=torch.bfloat16, device=DEV)
+    kc1, vc1, kc2, vc2 = mk(), mk(), mk(), mk()
+    q1 = torch.empty(M, Hq * D, dtype=torch.bfloat16, device=DEV)
+    q2 = torch.empty_like(q1)
+    assert fast().rows_scaled_qkv_rope(feed, M, w, pos, slots, table, q1, kc1, vc1, Hq, Hkv, D, D, 16)
+    assert fast().rows_norm_qkv_rope(x1, nw, 1e-5, w, pos, slots, table, q2, kc2, vc2, Hq, Hkv, D, D, 16)
+    sync_check()
+    scale = max(1.0, float(q2.float().abs().max()))
+    for a, b in ((q1, q2), (kc1, kc2), (vc1, vc2)):      # the two round the activations at different places: bf16 rounding apart
+        assert float((a.float() - b.float()).abs().max()) < 2e-2 * scale
