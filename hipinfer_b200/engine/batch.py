@@ -49,6 +49,8 @@ class StepBatch:
     max_pos: int = 0              # largest position among the rows
     max_q_len: int = 0
     extra: dict = field(default_factory=dict)  # what a kernel dispatcher derived for this batch (cached per step)
+    dump: Optional[dict] = None   # debug: planes of the step are recorded here, keyed (order index, name) (parts/planes.py)
+    dump_step: int = -1           # the order index the decoder is at
 
 
 def build_step_batch(entries: Sequence[StepEntry], ctx_lens: Sequence[int], state_slots: Sequence[int],

@@ -10,6 +10,9 @@ All entries of a step are one batch. For a step in which something is wanted the
 the wanted places (in the order of the entries and of `want`) go to `<out>/<step>.f32` as
 little-endian float32 [wanted, vocab]. After every step a line `done <step>` is printed and
 flushed. `end` names requests that are finished after the step; their pages are given back.
+With --planes every step also leaves its layers' named planes (parts/planes.py) beside the logits, so
+that the first (layer, sub-step) at which two runs part ways can be read off; the reference's
+scripts/layer_diff.py does that for its own graph.
 
 The reference's nearest things: `RefEngine.forward` keeps its cache between calls
 (scripts/ref_engine.py:218-232) and `hi_prefill(slot, tokens, T, p0)` continues a slot at p0
@@ -34,6 +37,9 @@ def main(argv=None) -> int:
                     help="most tokens live requests hold at any time (each rounded up to 64); sizes the cache pool")
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--max-requests", type=int, default=4, help="most requests live at a time")
+    ap.add_argument("--planes", action="store_true",
+                    help="also write <step>.planes.safetensors: every layer's named planes of the step's rows "
+                         "(parts/planes.py), named <order index>.<plane>; such steps run eagerly")
     a = ap.parse_args(argv)
 
     from .runner import ModelRunner
@@ -55,7 +61,13 @@ def main(argv=None) -> int:
         rec = json.loads(line)
         step = rec["step"]
         entries = [StepEntry(e["id"], e["tokens"], e.get("want", [])) for e in rec.get("entries", [])]
-        logits = runner.step(entries)
+        dump = {} if a.planes else None
+        logits = runner.step(entries, dump=dump)
+        if dump:
+            from safetensors.torch import save_file
+
+            save_file({f"{i}.{name}": t.cpu().contiguous() for (i, name), t in dump.items()},
+                      os.path.join(a.out, f"{step}.planes.safetensors"))
         if logits.shape[0]:
             arr = logits.detach().to("cpu").numpy().astype("<f4", copy=False)
             arr.tofile(os.path.join(a.out, f"{step}.f32"))

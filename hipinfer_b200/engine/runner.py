@@ -116,14 +116,15 @@ class ModelRunner:
         return arrays
 
     def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None,
-             token_map: Optional[Sequence[int]] = None) -> torch.Tensor:
+             token_map: Optional[Sequence[int]] = None, dump: Optional[dict] = None) -> torch.Tensor:
         """Run one batch; float32 logits [number of wanted places, vocab] on the device.
         Raises OutOfPages (nothing changed) when the cache cannot hold the new tokens.
         `device_tokens` (int32 [rows], on the device) replaces the entries' token values, which
         are then placeholders: tokens sampled on the device feed the next step without a trip to
         the host (the reference keeps token and position on the device for the same reason,
         README.md:510-512). With `token_map` (one int per row) only rows with an entry >= 0 take
-        their token from device_tokens[entry]; the others keep the value the entry gives."""
+        their token from device_tokens[entry]; the others keep the value the entry gives.
+        `dump` (a dict): the step runs eagerly and leaves named planes of every layer in it (parts/planes.py)."""
         entries = list(entries)
         token_arrays = self.check_entries(entries)
         if not entries:
@@ -152,12 +153,13 @@ class ModelRunner:
             slots.append(rc.state_slot)
             slot_maps.append(self.cache.append(e.request_id, len(e.tokens), as_arrays=True))
             tables.append(self._table_rows(rc))
-        if self.cuda_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
+        if dump is None and self.cuda_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
             logits = self._graph_step(entries, ctx_lens, slots, tables, slot_maps, device_tokens, token_map)
         else:
             batch = build_step_batch(entries, ctx_lens, slots, tables, slot_maps, len(self.cache.groups), self.device,
                                      token_map=token_map, token_arrays=token_arrays)
             self._feed(batch.tokens, batch.token_map, device_tokens, token_map)
+            batch.dump = dump
             logits = self.model.forward(batch, self.storage)
         for e in entries:
             if self.cache.release_behind_window(e.request_id):

@@ -14,6 +14,7 @@ import torch
 
 from ..cache import CacheGroupSpec
 from ..kernels import ops
+from ..parts import planes
 from ..parts.registry import BuildContext, build_part
 from ..parts.spec import ModelSpec, PartSpec
 
@@ -94,6 +95,7 @@ class DecoderModel:
     def forward(self, batch, storage) -> torch.Tensor:
         """Run the batch's tokens from the cache; logits float32 [len(batch.want_rows), vocab]."""
         x = self.embedding.forward(batch.tokens)
+        planes.record(batch, "embedding", x)
         # what a layer leaves for the next reader of x: a sum not yet added (kernels.ops.Pending: the next norm adds
         # it), or that next norm already prepared by the layer's last product (kernels.fast.NormFeed); else None
         carry = None
@@ -110,8 +112,15 @@ class DecoderModel:
                 kw["pending"] = carry
             if getattr(layer, "takes_next_norm", False) and i + 1 < len(order):
                 kw["next_norm"] = getattr(self.layers[order[i + 1].layer], "mixer_norm", None)
+            batch.dump_step = i
             left = layer.forward(x, batch, cache, state, **kw)
             carry = left if left is not None and not isinstance(left, torch.Tensor) else None
+            if planes.dumping(batch):          # a dumped step leaves nothing pending: x is whole where a plane is taken
+                if isinstance(carry, ops.Pending):
+                    carry.finish()
+                carry = None
+                if (i, "after_feed_forward") not in batch.dump:
+                    planes.record(batch, "after_feed_forward", x)
         pending = carry if isinstance(carry, ops.Pending) else None
         if batch.n_want == 0:
             if pending is not None:

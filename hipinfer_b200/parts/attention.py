@@ -21,6 +21,7 @@ import torch
 
 from ..kernels import ops
 from ..weights import ParamSpec
+from . import planes
 from .registry import CacheNeed, Mixer, build_part, register_part, to_compute
 
 
@@ -88,6 +89,8 @@ class AttentionMixer(Mixer):
         att = torch.empty(T, Hq * D, dtype=self.ctx.dtype, device=q.device)
         ops.attention(q, cache.k, cache.v, batch, cache.group, att, Hq, Hkv, D, self.ctx.page_size, self.window,
                       self.scale)
+        planes.record(batch, "q", q)
+        planes.record(batch, "attention", att)
         if ops.linear_add_rows(att, self.wo, x, norm_feed):            # a few rows: added in the product's epilogue
             return None
         return ops.linear_deferred(att, self.wo, x, accumulate=True)   # the next norm may add it

@@ -8,6 +8,7 @@ with a message. Every block has an attribute `mixer`: the part whose `cache_need
 from __future__ import annotations
 
 from ..kernels import ops
+from . import planes
 from .registry import Part, build_part, register_part
 
 
@@ -72,6 +73,8 @@ class PreNormBlock(Part):
         """pending: what the layer before left: a sum it has yet to add into x (kernels.ops.Pending), or the first
         norm of this layer prepared by its last product (kernels.fast.NormFeed). Returns what this layer leaves in
         the same way (None when x is complete and nothing is prepared)."""
+        if planes.dumping(batch):
+            return self._forward_dumped(x, batch, cache, state, pending)
         feed_in = None
         if pending is not None and not isinstance(pending, ops.Pending):
             feed_in, pending = pending, None
@@ -88,6 +91,24 @@ class PreNormBlock(Part):
         if isinstance(left, ops.Pending):
             return left
         return feed if feed is not None and feed.filled else None
+
+    def _forward_dumped(self, x, batch, cache, state, pending):
+        """The same layer with every sum finished and every norm evaluated where a plane is recorded (parts/planes.py)."""
+        if isinstance(pending, ops.Pending):
+            pending.finish()
+        xn = self.mixer_norm.forward(x)
+        planes.record(batch, "mixer_norm", xn)
+        left = self.mixer.forward(xn, x, batch, cache, state)
+        if isinstance(left, ops.Pending):
+            left.finish()
+        planes.record(batch, "after_mixer", x)
+        xn = self.feed_forward_norm.forward(x)
+        planes.record(batch, "feed_forward_norm", xn)
+        left = self.feed_forward.forward(xn, x, batch)
+        if isinstance(left, ops.Pending):
+            left.finish()
+        planes.record(batch, "after_feed_forward", x)
+        return None
 
 
 register_part("block", "pre_norm", PreNormBlock)

@@ -14,6 +14,7 @@ import torch
 
 from ..kernels import ops
 from ..weights import ParamSpec
+from . import planes
 from .registry import Part, register_part, to_compute
 
 GROUP = 16
@@ -55,6 +56,7 @@ class SwiGLU(Part):
                 ops.linear_swiglu(xn.materialize(), self.wgu, act, GROUP)
         else:
             ops.linear_swiglu(xn, self.wgu, act, GROUP)
+        planes.record(batch, "activation", act)
         if ops.linear_add_rows(act, self.wdown, x, norm_feed):            # a few rows: added in the product's epilogue
             return None
         return ops.linear_deferred(act, self.wdown, x, accumulate=True)   # the next norm may add it
