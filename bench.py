@@ -239,6 +239,28 @@ def prefill_device(eng, warmup: int, reps: int):
     return statistics.median(times)
 
 
+def self_check(eng, tail: int = 8):
+    """What the timed steps compute, checked at the benchmark's own sizes: the logits of the last `tail` positions of a
+    short request, once from decode steps over the cache (graph replay, the timed path) and once from a single step
+    over the whole request (the prefill path, which the tests compare with the plain implementation at these layer
+    sizes). Returns (all finite, largest |difference| / largest |logit|)."""
+    import torch
+
+    from hipinfer_b200.engine import StepEntry
+
+    runner = eng.runner
+    n = 160
+    toks = prompts(1, 5, n)[0]
+    whole = runner.step([StepEntry("check-whole", toks, list(range(n - tail, n)))]).float()
+    runner.end("check-whole")
+    runner.step([StepEntry("check-steps", toks[:n - tail], [])])
+    rows = [runner.step([StepEntry("check-steps", [t], [0])]).float().clone() for t in toks[n - tail:]]
+    runner.end("check-steps")
+    steps = torch.cat(rows)
+    finite = bool(torch.isfinite(whole).all()) and bool(torch.isfinite(steps).all()) and float(whole.abs().max()) > 0
+    return finite, float((whole - steps).abs().max()) / max(float(whole.abs().max()), 1e-30)
+
+
 def mixed_workload(a) -> int:
     """The scheduler's own workload: `--requests` requests with
     uniform-random prompt lengths in [64, 2048] (seeded), prompts cut into portions under a budget of
@@ -517,6 +539,13 @@ def main() -> int:
     pre_ms = prefill_device(eng, 3, 5)
     pre_frac = prefill_flops(a.layers) / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12)
     e2e_ms, h2d, d2h = decode_e2e(eng, a.batch, min(a.steps, 64), a.warmup)
+    finite, drift = self_check(eng)
+    # two bfloat16 paths, each held to 1.5e-2 of the largest logit against the 32-bit plain implementation by the
+    # tests, may lie 3e-2 apart; this guards against a timed path that computes something else, not against rounding
+    if not finite or drift > 3e-2:
+        print(f"bench.py: the timed path's logits are wrong (finite: {finite}; decode steps against a whole prompt: "
+              f"{drift:.3e} of the largest logit)", file=sys.stderr)
+        return 1
     out = {
         "metric": f"decode tok/s at batch {a.batch} ({SHAPE_NAME}, {PROMPT_LEN:,}-token prompts)",
         "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": a.steps, "warmup": a.warmup,
@@ -534,6 +563,7 @@ def main() -> int:
                      "frac": round(achieved / pk["hbm_gbs"], 4), "peaks": pk["source"],
                      "bytes_per_step": int(step_bytes), "mean_context": mean_ctx},
         "points": points,
+        "check": {"finite": finite, "decode_vs_whole": round(drift, 6)},
     }
     eng.close()
     print(json.dumps(out))

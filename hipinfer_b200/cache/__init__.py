@@ -1,7 +1,7 @@
 from .manager import (CacheError, CacheGroupSpec, CacheManager, OutOfPages, OutOfStateSlots, PagePool, RequestCache,
-                      SlotPool)
+                      SlotPool, register_retention)
 
 from .storage import CacheStorage, LayerCache
 
 __all__ = ["CacheStorage", "LayerCache", "CacheError", "CacheGroupSpec", "CacheManager", "OutOfPages", "OutOfStateSlots", "PagePool",
-           "RequestCache", "SlotPool"]
+           "RequestCache", "SlotPool", "register_retention"]

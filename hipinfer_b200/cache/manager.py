@@ -5,6 +5,10 @@ page ids index live in `hipinfer_b200/cache/storage.py`.
 Layers are put into GROUPS by what they need. A group of kind "full" keeps every key of a
 request; a group of kind "window" keeps the last `window` keys, and its pages are given back
 as soon as every position on them has fallen out of the window of all tokens still to come.
+A kind is a RETENTION RULE, a function from (group, position of the next query) to the ranges of
+positions that no later query can see; `register_retention` adds another. What a layer keeps
+per token is a tuple of PLANES (name, heads, width): keys and values of one shape for attention,
+any other set for a mixer that keeps a latent or keys and values of different widths.
 Each group has a page pool of its own and each request one block table per group, indexed by
 logical page (position // page_size); a released entry reads -1. All pages return to their
 pool when the request ends. A freed page is handed out again, lowest id first, so that which
@@ -23,7 +27,7 @@ from __future__ import annotations
 
 import heapq
 from dataclasses import dataclass, field
-from typing import Dict, List, Optional, Sequence, Tuple
+from typing import Callable, Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
 
@@ -40,26 +44,48 @@ class CacheError(RuntimeError):
     """Misuse: unknown or duplicate request, a page freed twice."""
 
 
+# kind -> rule(group spec, position of the next query) -> [(lo, hi)): positions that no query from there on can see
+RETENTION: Dict[str, Callable[["CacheGroupSpec", int], Sequence[Tuple[int, int]]]] = {}
+
+
+def register_retention(kind: str, dead_ranges: Callable[["CacheGroupSpec", int], Sequence[Tuple[int, int]]]) -> None:
+    """Adds a kind of cache group. `dead_ranges(spec, next_query_pos)` returns half-open ranges of positions whose
+    entries no query at next_query_pos or later reads; a page that lies wholly inside one is given back."""
+    RETENTION[kind] = dead_ranges
+
+
+register_retention("full", lambda spec, q: ())
+register_retention("window", lambda spec, q: ((0, max(0, q - spec.window + 1)),))
+
+
 @dataclass(frozen=True)
 class CacheGroupSpec:
-    """What one group of layers needs. `n_layers` cache-owning layers share the group's block
-    table; `kv_heads * head_dim` elements of K and of V per token and layer."""
+    """What one group of layers needs. `n_layers` cache-owning layers share the group's block table; each keeps, per
+    token, the `planes` (name, heads, width): by default keys and values of `kv_heads * head_dim` elements each.
+    `extra` holds (key, value) pairs for a retention rule of another kind."""
 
     name: str
-    kind: str  # "full" | "window"
+    kind: str  # a key of RETENTION: "full", "window", or one registered from outside
     n_layers: int
-    kv_heads: int
-    head_dim: int
+    kv_heads: int = 0
+    head_dim: int = 0
     window: int = 0
+    planes: Tuple[Tuple[str, int, int], ...] = ()
+    extra: Tuple[Tuple[str, object], ...] = ()
 
     def __post_init__(self):
-        if self.kind not in ("full", "window"):
-            raise ValueError(f"cache group {self.name!r}: kind must be 'full' or 'window', got {self.kind!r}")
+        if self.kind not in RETENTION:
+            raise ValueError(f"cache group {self.name!r}: kind must be one of {sorted(RETENTION)}, got {self.kind!r}")
         if self.kind == "window" and self.window <= 0:
             raise ValueError(f"cache group {self.name!r}: a window group needs window > 0")
+        if not self.planes:
+            object.__setattr__(self, "planes", (("k", self.kv_heads, self.head_dim), ("v", self.kv_heads, self.head_dim)))
+        names = [p[0] for p in self.planes]
+        if len(set(names)) != len(names) or any(h <= 0 or d <= 0 for _, h, d in self.planes):
+            raise ValueError(f"cache group {self.name!r}: planes need distinct names and positive sizes, got {self.planes}")
 
     def elements_per_token(self) -> int:
-        return 2 * self.n_layers * self.kv_heads * self.head_dim
+        return self.n_layers * sum(h * d for _, h, d in self.planes)
 
 
 class PagePool:
@@ -173,11 +199,6 @@ class CacheManager:
         del self.requests[request_id]
 
     # ---------------------------------------------------------------- pages
-    def _first_needed(self, g: int, first_query_pos: int) -> int:
-        """Lowest position whose key a query at `first_query_pos` (or later) of group g can still see."""
-        spec = self.groups[g]
-        return 0 if spec.kind == "full" else max(0, first_query_pos - spec.window + 1)
-
     def pages_needed(self, request_id, n_tokens: int) -> List[int]:
         """Per group: pages that appending n_tokens would take from the pool."""
         rc = self.requests.get(request_id)
@@ -221,20 +242,19 @@ class CacheManager:
         return slot_maps
 
     def release_behind_window(self, request_id) -> int:
-        """After a step: give back the pages of window groups that no later token can see.
+        """After a step: give back the pages that, by the group's retention rule, no later token can see.
         The next query is at position `length`. Returns how many pages were released."""
         rc = self.get(request_id)
         released = 0
+        ps = self.page_size
         for g, spec in enumerate(self.groups):
-            if spec.kind != "window":
-                continue
-            first = self._first_needed(g, rc.length)
             table = rc.tables[g]
-            for lp in range(min(first // self.page_size, len(table))):
-                if table[lp] >= 0:
-                    self.pools[g].release(table[lp])
-                    table[lp] = -1
-                    released += 1
+            for lo, hi in RETENTION[spec.kind](spec, rc.length):
+                for lp in range(-(-lo // ps), min(hi // ps, len(table))):
+                    if table[lp] >= 0:
+                        self.pools[g].release(table[lp])
+                        table[lp] = -1
+                        released += 1
         return released
 
     # ---------------------------------------------------------------- views and checks

@@ -1,10 +1,10 @@
 """Device memory behind the cache manager's page ids and state slots.
 
-Per cache group one tensor [layer cache, K/V, page, kv head, page_size, head_dim] in the
-compute element type: a (page, kv head) pair is one contiguous run of page_size * head_dim
-elements, which is what the attention kernels stream. Per declared state one tensor
-[state slot, *shape]. The pools start zeroed: a kernel that loads a whole page and masks the
-tail must never meet a NaN pattern there.
+Per cache group and plane (keys, values, or what else the group's mixers keep per token) one
+tensor [layer cache, page, head, page_size, width] in the compute element type: a (page, head)
+pair is one contiguous run of page_size * width elements, which is what the attention kernels
+stream. Per declared state one tensor [state slot, *shape]. The pools start zeroed: a kernel
+that loads a whole page and masks the tail must never meet a NaN pattern there.
 
 The reference allocates `[layer][slot][kv head][max_seq][head_dim]` once (src/api.cu:1409-1411).
 """
@@ -20,21 +20,29 @@ from .manager import CacheGroupSpec
 
 @dataclass
 class LayerCache:
-    k: torch.Tensor      # [page, kv head, page_size, head_dim]
-    v: torch.Tensor
+    planes: Dict[str, torch.Tensor]      # plane name -> [page, head, page_size, width]
     group: int
     write: bool
+
+    @property
+    def k(self) -> torch.Tensor:
+        return self.planes["k"]
+
+    @property
+    def v(self) -> torch.Tensor:
+        return self.planes["v"]
 
 
 class CacheStorage:
     def __init__(self, groups: Sequence[CacheGroupSpec], num_pages: Sequence[int], page_size: int, dtype, device,
                  state_specs: Dict[Tuple[int, str], Tuple[Tuple[int, ...], torch.dtype]], num_state_slots: int):
         self.groups, self.page_size, self.dtype = list(groups), page_size, dtype
-        self.kv = [torch.zeros(g.n_layers, 2, n, g.kv_heads, page_size, g.head_dim, dtype=dtype, device=device)
-                   for g, n in zip(self.groups, num_pages)]
+        self.kv = [{name: torch.zeros(g.n_layers, n, heads, page_size, width, dtype=dtype, device=device)
+                    for name, heads, width in g.planes} for g, n in zip(self.groups, num_pages)]
         self.state: Dict[Tuple[int, str], torch.Tensor] = {
             key: torch.zeros((num_state_slots,) + tuple(shape), dtype=dt, device=device)
             for key, (shape, dt) in state_specs.items()}
+        self._layer_caches: Dict[Tuple[int, int, bool], LayerCache] = {}
         self._by_step: Dict[int, Dict[str, torch.Tensor]] = {}
         for (step, name), t in self.state.items():
             self._by_step.setdefault(step, {})[name] = t
@@ -42,8 +50,11 @@ class CacheStorage:
     def layer_cache(self, plan) -> Optional[LayerCache]:
         if plan is None:
             return None
-        t = self.kv[plan.group][plan.slot]
-        return LayerCache(t[0], t[1], plan.group, plan.write)
+        key = (plan.group, plan.slot, plan.write)
+        if key not in self._layer_caches:
+            self._layer_caches[key] = LayerCache({name: t[plan.slot] for name, t in self.kv[plan.group].items()},
+                                                 plan.group, plan.write)
+        return self._layer_caches[key]
 
     def layer_state(self, step: int) -> Dict[str, torch.Tensor]:
         return self._by_step.get(step, {})
@@ -57,5 +68,5 @@ class CacheStorage:
         return sum(g.elements_per_token() for g in self.groups) * torch.empty((), dtype=self.dtype).element_size()
 
     def nbytes(self) -> int:
-        return sum(t.numel() * t.element_size() for t in self.kv) + \
+        return sum(t.numel() * t.element_size() for g in self.kv for t in g.values()) + \
             sum(t.numel() * t.element_size() for t in self.state.values())

@@ -52,11 +52,11 @@ class DecoderModel:
                     raise ValueError(f"order[{i}] reads a cache but its mixer keeps none")
                 self.cache_plan.append(None)
                 continue
-            key = (need.kind, need.window, need.kv_heads, need.head_dim)
+            key = need.key()
             if st.reads_cache_of is not None:
                 src = self.cache_plan[st.reads_cache_of]
                 src_need = self.layers[self.spec.order[st.reads_cache_of].layer].mixer.cache_need()
-                if src is None or (src_need.kind, src_need.window, src_need.kv_heads, src_need.head_dim) != key:
+                if src is None or src_need.key() != key:
                     raise ValueError(f"order[{i}] reads the cache of step {st.reads_cache_of}, whose mixer keeps a "
                                      f"different kind of cache")
                 self.cache_plan.append(StepCachePlan(src.group, src.slot, False))
@@ -67,8 +67,8 @@ class DecoderModel:
             g = keys.index(key)
             self.cache_plan.append(StepCachePlan(g, counts[g], True))
             counts[g] += 1
-        self.cache_groups = [CacheGroupSpec(f"{k[0]}{k[1] or ''}-h{k[2]}-d{k[3]}", k[0], n, k[2], k[3], k[1])
-                             for k, n in zip(keys, counts)]
+        self.cache_groups = [CacheGroupSpec(f"{k[0]}{k[1] or ''}-h{k[2]}-d{k[3]}" + "".join(f"-{p[0]}" for p in k[4]),
+                                            k[0], n, k[2], k[3], k[1], k[4], k[5]) for k, n in zip(keys, counts)]
 
     # ---------------------------------------------------------------- weights
     def param_specs(self):

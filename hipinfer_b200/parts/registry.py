@@ -44,12 +44,21 @@ class BuildContext:
 
 @dataclass(frozen=True)
 class CacheNeed:
-    """Keys and values a mixer keeps per token: `kind` "full" or "window" (of `window` tokens)."""
+    """What a mixer keeps per token in the paged cache. `kind` names the retention rule ("full": everything;
+    "window": the last `window` tokens; or one added with cache.register_retention, which reads `extra`).
+    By default the layer gets keys "k" and values "v" of kv_heads x head_dim; `planes` ((name, heads, width), ...)
+    asks for other tensors instead (a latent, keys and values of different widths). Layers whose needs are equal
+    share a group: one page pool and one block table per request."""
 
     kind: str
-    kv_heads: int
-    head_dim: int
+    kv_heads: int = 0
+    head_dim: int = 0
     window: int = 0
+    planes: Tuple[Tuple[str, int, int], ...] = ()
+    extra: Tuple[Tuple[str, object], ...] = ()
+
+    def key(self) -> tuple:
+        return (self.kind, self.window, self.kv_heads, self.head_dim, self.planes, self.extra)
 
 
 class Part:

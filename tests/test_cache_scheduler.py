@@ -104,6 +104,40 @@ def test_window_group_gives_pages_back_as_the_window_passes():
     assert cm.free_pages() == [16, 6]
 
 
+def test_a_retention_rule_and_planes_registered_from_outside():
+    """A kind of group that the package does not know: the first `sink` tokens and the last `window` are kept; what a
+    layer keeps per token is a latent and two gate vectors, not keys and values."""
+    from hipinfer_b200.cache import register_retention
+
+    def sink_window(spec, q):
+        sink = dict(spec.extra)["sink"]
+        return ((sink, max(sink, q - spec.window + 1)),)
+
+    with pytest.raises(ValueError, match="kind must be one of"):
+        CacheGroupSpec("g", "sink_window_for_test", 1, window=24, planes=(("c", 1, 24),))
+    register_retention("sink_window_for_test", sink_window)
+    g = CacheGroupSpec("g", "sink_window_for_test", 2, window=24, planes=(("c", 1, 24), ("g", 2, 8)), extra=(("sink", 3),))
+    assert g.elements_per_token() == 2 * (24 + 16) and FULL.elements_per_token() == 2 * 2 * 2 * 16
+    assert FULL.planes == (("k", 2, 16), ("v", 2, 16))
+    with pytest.raises(ValueError, match="distinct names"):
+        CacheGroupSpec("g", "full", 1, planes=(("c", 1, 24), ("c", 2, 8)))
+    cm = CacheManager([g, FULL], page_size=8, num_pages=[8, 20], num_state_slots=1)
+    cm.add_request("a")
+    total = 0
+    for n in (30, 1, 1, 20, 1, 17, 1, 1, 24):      # 96 tokens = 12 pages on a pool of 8: it works only because pages come back
+        cm.append("a", n)
+        total += n
+        cm.release_behind_window("a")
+        for lp, page in enumerate(cm.block_table("a", 0)):
+            dead = lp * 8 >= 3 and (lp + 1) * 8 <= total - 24 + 1
+            assert (page == -1) == dead, (total, lp)
+        assert all(p >= 0 for p in cm.block_table("a", 1))
+        cm.check()
+    assert cm.block_table("a", 0)[0] >= 0 and cm.free_pages()[0] >= 2
+    cm.free_request("a")
+    assert total == 96 and cm.free_pages() == [8, 20]
+
+
 @pytest.mark.parametrize("seed", range(6))
 def test_random_orders_lose_no_page(seed):
     rng = random.Random(seed)

@@ -520,6 +520,183 @@ def test_toy_position_encoding_and_routed_feed_forward():
         assert runner.cache.free_pages() == [30] and runner.cache.slots.free_count == 4
 
 
+# ------------------------------------------------------------------------------------------
+# A third toy architecture: a mixer whose cache is not keys and values of one shape, in a group with a retention
+# rule of its own. Per token it keeps a latent c (1 x Dc) and two gate vectors g (2 x Dg); a query sees the first
+# `sink` tokens and the last `window`; pages wholly between the two are given back while the request runs.
+#   layer 0: LatentMixer + SwiGLU      layer 1: attention (all keys) + SwiGLU      order: 0, 1, 0 again (a cache of its own)
+# ------------------------------------------------------------------------------------------
+def _register_toy3():
+    from hipinfer_b200.cache import register_retention
+    from hipinfer_b200.config import ModelConfig, register_architecture, take
+    from hipinfer_b200.parts import LayerSpec, Mixer, ModelSpec, PartSpec, RunStep, register_part
+    from hipinfer_b200.parts.registry import CacheNeed
+    from hipinfer_b200.weights import ParamSpec
+
+    def sink_window(spec, q):
+        sink = dict(spec.extra)["sink"]
+        return ((sink, max(sink, q - spec.window + 1)),)
+
+    register_retention("toy_sink_window", sink_window)
+
+    class LatentMixer(Mixer):
+        def __init__(self, params, ctx, prefix=""):
+            super().__init__(params, ctx, prefix)
+            self.H, self.Dc, self.Dg = params["hidden_size"], params["latent"], params["gate"]
+            self.sink, self.window = params["sink"], params["window"]
+            self.names = [prefix + f"latent.{n}.weight" for n in ("c", "g", "o")]
+
+        def param_specs(self):
+            return [ParamSpec(self.names[0], (self.Dc, self.H)), ParamSpec(self.names[1], (2 * self.Dg, self.H)),
+                    ParamSpec(self.names[2], (self.H, self.Dc))]
+
+        def load(self, tensors):
+            self.wc, self.wg, self.wo = (tensors[n].float() for n in self.names)
+
+        def cache_need(self):
+            return CacheNeed("toy_sink_window", window=self.window, planes=(("c", 1, self.Dc), ("g", 2, self.Dg)),
+                             extra=(("sink", self.sink),))
+
+        def forward(self, xn, x, batch, cache, state):
+            ps, T = self.ctx.page_size, xn.shape[0]
+            C, G = cache.planes["c"], cache.planes["g"]                  # [page, 1, ps, Dc], [page, 2, ps, Dg]
+            xf = xn.float()
+            c = (xf @ self.wc.T).to(C.dtype)
+            g = (xf @ self.wg.T).reshape(T, 2, self.Dg).to(G.dtype)
+            if cache.write:
+                slot = batch.slot_maps[cache.group].long()
+                C[slot // ps, 0, slot % ps] = c
+                G[slot // ps, :, slot % ps] = g
+            table = batch.block_tables[cache.group].long()               # [R, pages]; -1 where a page was given back
+            p = torch.arange(table.shape[1] * ps, device=xn.device)
+            page = table[batch.row_request.long()][:, p // ps]           # [T, L]
+            pos = batch.positions.long()[:, None]
+            visible = (page >= 0) & (p[None] <= pos) & ((p[None] < self.sink) | (p[None] > pos - self.window))
+            page, off = page.clamp(min=0), (p % ps)[None].expand_as(page)
+            ck, gk = C[page, 0, off].float(), G[page, :, off].float()    # [T, L, Dc], [T, L, 2, Dg]
+            score = torch.einsum("td,tld->tl", c.float(), ck) / math.sqrt(self.Dc) + \
+                torch.einsum("thd,tlhd->tl", g.float(), gk)
+            prob = torch.softmax(score.masked_fill(~visible, float("-inf")), -1)
+            x += torch.einsum("tl,tld->td", prob, ck) @ self.wo.T
+
+    @dataclass(frozen=True)
+    class Toy3Config(ModelConfig):
+        vocab_size: int
+        hidden_size: int
+        n_heads: int
+        n_kv_heads: int
+        head_dim: int
+        intermediate_size: int
+        latent: int
+        gate: int
+        sink: int
+        window: int
+        eps: float
+
+        KEYS = ("vocab_size", "hidden_size", "n_heads", "n_kv_heads", "head_dim", "intermediate_size", "latent", "gate",
+                "sink", "window")
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(d["architectures"][0], *(take(d, k, int) for k in cls.KEYS), take(d, "eps", float))
+
+        def to_dict(self):
+            return dict(architectures=[self.architecture], **{k: getattr(self, k) for k in self.KEYS + ("eps",)})
+
+    def toy3_spec(c):
+        H = c.hidden_size
+        norm = lambda name: PartSpec("rmsnorm", dict(name=name, size=H, eps=c.eps))
+        ffn = PartSpec("swiglu", dict(hidden_size=H, intermediate_size=c.intermediate_size))
+        mixers = [PartSpec("toy_latent", dict(hidden_size=H, latent=c.latent, gate=c.gate, sink=c.sink, window=c.window)),
+                  PartSpec("attention", dict(hidden_size=H, n_heads=c.n_heads, n_kv_heads=c.n_kv_heads, head_dim=c.head_dim, window=0,
+                                             position=PartSpec("rope", dict(head_dim=c.head_dim, theta=10000.0, scaling=None))))]
+        layers = tuple(LayerSpec(f"toy3.layers.{i}.", "pre_norm", dict(
+            mixer=m, mixer_norm=norm("input_layernorm.weight"), feed_forward=ffn,
+            feed_forward_norm=norm("post_attention_layernorm.weight"))) for i, m in enumerate(mixers))
+        return ModelSpec(c.architecture, H, c.vocab_size, 256,
+                         PartSpec("token", dict(name="toy3.embed.weight", vocab_size=c.vocab_size, hidden_size=H)), layers,
+                         (RunStep(0), RunStep(1), RunStep(0)), norm("toy3.norm.weight"),
+                         PartSpec("linear", dict(tied_to="toy3.embed.weight", vocab_size=c.vocab_size, hidden_size=H)))
+
+    register_part("mixer", "toy_latent", LatentMixer)
+    register_architecture("Toy3ForCausalLM", Toy3Config, toy3_spec)
+
+
+TOY3 = dict(architectures=["Toy3ForCausalLM"], vocab_size=180, hidden_size=80, n_heads=2, n_kv_heads=1, head_dim=32,
+            intermediate_size=112, latent=24, gate=8, sink=5, window=40, eps=1e-5)
+
+
+def toy3_plain(c, w, tokens):
+    T, H, Hq, Hkv, D, Dc, Dg = (len(tokens), c["hidden_size"], c["n_heads"], c["n_kv_heads"], c["head_dim"], c["latent"],
+                                c["gate"])
+    pos = list(range(T))
+    t = torch.arange(T)
+    visible = (t[None] <= t[:, None]) & ((t[None] < c["sink"]) | (t[None] > t[:, None] - c["window"]))
+
+    def norms(i):
+        p = f"toy3.layers.{i}."
+        return w[p + "input_layernorm.weight"], w[p + "post_attention_layernorm.weight"]
+
+    def mlp(i, x):
+        p = f"toy3.layers.{i}.mlp."
+        return x + plain.swiglu_mlp(plain.rmsnorm(x, norms(i)[1], c["eps"]), w[p + "gate_proj.weight"], w[p + "up_proj.weight"],
+                                    w[p + "down_proj.weight"])
+
+    def latent(x):
+        xn = plain.rmsnorm(x, norms(0)[0], c["eps"])
+        lc = xn @ w["toy3.layers.0.latent.c.weight"].T
+        lg = (xn @ w["toy3.layers.0.latent.g.weight"].T).reshape(T, 2, Dg)
+        score = lc @ lc.T / math.sqrt(Dc) + torch.einsum("thd,shd->ts", lg, lg)
+        prob = torch.softmax(score.masked_fill(~visible, float("-inf")), -1)
+        return mlp(0, x + (prob @ lc) @ w["toy3.layers.0.latent.o.weight"].T)
+
+    x = latent(plain.embed(tokens, w["toy3.embed.weight"]))
+    x = mlp(1, x + plain.attention_block(plain.rmsnorm(x, norms(1)[0], c["eps"]),
+                                         *(w[f"toy3.layers.1.self_attn.{k}_proj.weight"] for k in "qkvo"), pos, Hq, Hkv, D,
+                                         plain.rope_inv_freq(D, 10000.0)))
+    x = latent(x)
+    return plain.lm_head(x, w["toy3.norm.weight"], w["toy3.embed.weight"], c["eps"])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_mixer_with_cache_planes_and_a_retention_rule_of_its_own(dtype):
+    from hipinfer_b200.config import config_from_dict, get_architecture
+    from hipinfer_b200.engine import ModelRunner, StepEntry
+    from hipinfer_b200.parts import spec_param_specs
+    from hipinfer_b200.weights import random_weights
+
+    _register_toy3()
+    cfg = config_from_dict(TOY3)
+    spec = get_architecture("Toy3ForCausalLM").build_spec(cfg)
+    tensors = random_weights(spec_param_specs(spec), seed=13, std=0.08, norm_std=0.1, dtype=torch.bfloat16)
+    runner = ModelRunner(cfg, {k: v.to(DEV) for k, v in tensors.items()}, dtype=dtype, num_pages=40, max_model_len=256,
+                         max_num_seqs=4)
+    m = runner.model
+    assert [(g.kind, g.n_layers, g.planes) for g in m.cache_groups] == \
+        [("toy_sink_window", 2, (("c", 1, 24), ("g", 2, 8))), ("full", 1, (("k", 1, 32), ("v", 1, 32)))]
+    assert [(p.group, p.slot, p.write) for p in m.cache_plan] == [(0, 0, True), (1, 0, True), (0, 1, True)]
+    assert {n: tuple(t.shape) for n, t in runner.storage.kv[0].items()} == {"c": (2, 40, 1, 16, 24), "g": (2, 40, 2, 16, 8)}
+    assert runner.storage.bytes_per_token() == (2 * (24 + 16) + 2 * 32) * (4 if dtype == "float32" else 2)
+    w = {k: v.float() for k, v in tensors.items()}
+    requests = {f"v{i}": tiny.random_tokens(n, 180, 40 + i) for i, n in enumerate([150, 33, 90, 64, 7, 120])}
+    ref = {rid: toy3_plain(TOY3, w, toks) for rid, toks in requests.items()}
+    st = tiny.RunnerStepper(runner)
+    for name, plan in (("whole", tiny.plan_whole(requests)), ("portions", tiny.plan_portions(requests)),
+                       ("tail", tiny.plan_tail_decode(requests, 12)), ("mixed", tiny.plan_mixed(requests, 3))):
+        got = tiny.run_plan(st, requests, plan)
+        for rid in requests:
+            tiny.assert_logits_close(got[rid], ref[rid], dtype, f"toy3 {name} {rid}", group=("toy architecture 3", name))
+        runner.cache.check()
+        assert runner.cache.free_pages() == [40, 40] and runner.cache.slots.free_count == 4
+    assert runner._graphs, "no decode-only step went through a CUDA graph"
+    # 150 tokens: the latent group keeps page 0 (the first 5 tokens lie on it) and pages 6..9 (tokens 111..149 are
+    # still visible to the next query); pages 1..5 went back while the request runs. The attention group keeps all 10.
+    runner.step([StepEntry("long", requests["v0"], [])])
+    tables = runner.cache.get("long").tables
+    assert [i for i, p in enumerate(tables[0]) if p >= 0] == [0, 6, 7, 8, 9] and all(p >= 0 for p in tables[1])
+    runner.end("long")
+
+
 def test_unknown_part_kind_is_named():
     from hipinfer_b200.parts import BuildContext, PartSpec, build_part
 
