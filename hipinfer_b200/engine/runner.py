@@ -59,6 +59,7 @@ class ModelRunner:
         # graph captured per number of requests: same kernels, one launch
         self.cuda_graphs = bool(cuda_graphs)
         self._graphs: Dict[tuple, dict] = {}
+        self._graph_pool = None
         self._table_widths = [pages_per_seq] * len(groups)
         self._np_tables: Dict[object, list] = {}
 
@@ -197,7 +198,8 @@ class ModelRunner:
             ops.feed_tokens(tokens, device_tokens, map_dev)
 
     GRAPH_LENGTH_QUANTUM = 512     # tokens by which the length class of a decode graph grows
-    MAX_GRAPHS = 24                # captured graphs kept (each holds its batch buffer and its logits)
+    MAX_GRAPHS = 128               # captured graphs kept, least recently used first to go (each holds its batch buffer
+                                   # and its logits; what a step allocates besides comes from one pool they share)
 
     def _graph_step(self, entries, ctx_lens, slots, tables, slot_maps, device_tokens=None, token_map=None) -> torch.Tensor:
         """A decode-only step through the CUDA graph for this many requests and this length class (captured at
@@ -221,9 +223,13 @@ class ModelRunner:
             from ..kernels import library
             before = library.launches[0]
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):                      # recorded, not run
+            if self._graph_pool is None:
+                self._graph_pool = torch.cuda.graph_pool_handle()
+            # one memory pool for all graphs: they never run at the same time, and what a step allocates and frees
+            # on its way is the same memory in every graph (only the logits, which stay alive, are a graph's own)
+            with torch.cuda.graph(graph, pool=self._graph_pool):     # recorded, not run
                 logits = self.model.forward(batch, self.storage)
-            while len(self._graphs) >= self.MAX_GRAPHS:          # the oldest class goes (requests only grow)
+            while len(self._graphs) >= self.MAX_GRAPHS:
                 self._graphs.pop(next(iter(self._graphs)))
             self._graphs[key] = dict(graph=graph, static=static, logits=logits, tokens=batch.tokens,
                                    token_map=batch.token_map, launches=library.launches[0] - before)
@@ -231,6 +237,7 @@ class ModelRunner:
             # with state of its own (its state advances with every run) must not see
             return first
         else:
+            self._graphs[key] = self._graphs.pop(key)          # most recently used last
             build_step_batch(entries, ctx_lens, slots, tables, slot_maps, static=g["static"], token_map=token_map, **args)
             self._feed(g["tokens"], g["token_map"], device_tokens, token_map)
         g["graph"].replay()
