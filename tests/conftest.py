@@ -38,6 +38,6 @@ def pytest_terminal_summary(terminalreporter):
         plans[plan] = max(plans.get(plan, 0.0), rel)
     if worst:
         terminalreporter.write_line("logits against the plain implementation, largest |diff| / largest |logit| (bound: "
-                                    + ", ".join(f"{k} {v:.0e}" for k, v in tiny.TOL.items()) + "):")
+                                    + ", ".join(f"{k} {v:.1e}" for k, v in tiny.TOL.items()) + "):")
         for (config, dtype), plans in sorted(worst.items()):
             terminalreporter.write_line(f"  {config:22s} {dtype:9s} " + "  ".join(f"{p or 'all'} {r:.1e}" for p, r in sorted(plans.items())))

@@ -75,3 +75,27 @@ def test_wanted_subset_and_no_want(setup):
     assert tr.step([("w", toks[:10], [])]) is None
     got = tr.step([("w", toks[10:n], [0, n - 11])], end=["w"])
     tiny.assert_logits_close(got, ref[[10, n - 1]], setup["dtype"], "subset")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("which", ["d", "e"])
+def test_sizes_the_fast_kernels_take_only_in_part(which, dtype, tmp_path):
+    """Heads of 48 and of 80, a group of 7, widths that are no multiple of 32 or 64, odd vocabularies: whatever a
+    tensor-core kernel does not take goes to another kernel, never to a wrong result. Whole, in portions, with the
+    last tokens one by one, and mixed on a small pool, through the step function in this process."""
+    from hipinfer_b200.engine import ModelRunner
+
+    folder = tiny.make_model_folder(tmp_path / "m", which, torch.float32 if dtype == "float32" else torch.bfloat16)
+    cfg, weights = plain.read_model(folder)
+    requests = {f"o{i}": tiny.random_tokens(n, cfg["vocab_size"], 300 + i) for i, n in enumerate([130, 9, 64, 33, 200, 17])}
+    ref = {rid: plain.forward(cfg, weights, toks) for rid, toks in requests.items()}
+    runner = ModelRunner.from_folder(folder, dtype=dtype, page_size=16, num_pages=4 * 208 // 16, max_model_len=256, max_num_seqs=4)
+    st = tiny.RunnerStepper(runner)
+    for name, plan in (("whole", tiny.plan_whole(requests)), ("portions", tiny.plan_portions(requests)),
+                       ("tail", tiny.plan_tail_decode(requests, 32)), ("mixed", tiny.plan_mixed(requests, 1)),
+                       ("mixed-long", tiny.plan_mixed_long(requests, 2))):
+        got = tiny.run_plan(st, requests, plan)
+        for rid in requests:
+            tiny.assert_logits_close(got[rid], ref[rid], dtype, f"{which} {name} {rid}", group=(f"tiny {which}", name))
+        runner.cache.check()
+        assert runner.cache.free_pages() == [52]

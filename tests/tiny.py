@@ -32,6 +32,20 @@ TINY_C = dict(architectures=["LlamaForCausalLM"], vocab_size=1000, hidden_size=2
                                 original_max_position_embeddings=256),
               tie_word_embeddings=True, hidden_act="silu")
 
+# sizes that the fast kernels take only in part: heads of 48 (the tensor-core attention kernels take 64 and 128), a width
+# that is no multiple of 32, an odd vocabulary, multi-head attention without groups, one layer
+TINY_D = dict(architectures=["LlamaForCausalLM"], vocab_size=515, hidden_size=200, intermediate_size=272,
+              num_hidden_layers=1, num_attention_heads=5, num_key_value_heads=5, head_dim=48,
+              max_position_embeddings=512, rms_norm_eps=3e-6, rope_theta=20000.0, rope_scaling=None,
+              tie_word_embeddings=False, hidden_act="silu")
+# heads of 80 in groups of 7, four layers, a width that is a multiple of 32 but not of 64
+TINY_E = dict(architectures=["LlamaForCausalLM"], vocab_size=777, hidden_size=224, intermediate_size=400,
+              num_hidden_layers=4, num_attention_heads=7, num_key_value_heads=1, head_dim=80,
+              max_position_embeddings=512, rms_norm_eps=1e-5, rope_theta=1000000.0,
+              rope_scaling=dict(rope_type="llama3", factor=4.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                                original_max_position_embeddings=128),
+              tie_word_embeddings=True, hidden_act="silu")
+
 # the real layer sizes of the Llama-3.2-1B shape (width, heads, feed-forward, vocabulary, llama3 scaling, tied head)
 # with 2 of its 16 layers, so that the plain implementation on the CPU stays within seconds
 LLAMA_1B_LAYERS_FULL, LLAMA_1B_LAYERS_TESTED = 16, 2
@@ -45,7 +59,9 @@ LLAMA_1B_2L = dict(architectures=["LlamaForCausalLM"], vocab_size=128256, hidden
 WEIGHTS = {"1b2l": dict(cfg=LLAMA_1B_2L, seed=11, std=0.02, norm_std=0.1),
            "a": dict(cfg=TINY_A, seed=0, std=0.02, norm_std=0.0),
            "b": dict(cfg=TINY_B, seed=2, std=0.05, norm_std=0.1),
-           "c": dict(cfg=TINY_C, seed=5, std=0.04, norm_std=0.1)}
+           "c": dict(cfg=TINY_C, seed=5, std=0.04, norm_std=0.1),
+           "d": dict(cfg=TINY_D, seed=6, std=0.05, norm_std=0.1),
+           "e": dict(cfg=TINY_E, seed=8, std=0.04, norm_std=0.1)}
 
 
 def make_model_folder(folder, which, dtype=torch.bfloat16):
