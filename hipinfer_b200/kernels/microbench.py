@@ -43,6 +43,17 @@ def timeit(fn, iters, flush):
     return times[len(times) // 2]
 
 
+def _prepared(fast, x, nw):
+    """A filled NormFeed for residual rows x: what a product with the residual add in its epilogue leaves for the next norm."""
+    M, K = x.shape
+    feed = fast.NormFeed(nw, 1e-5, M)
+    feed.xb.copy_((x * nw.float()).bfloat16())
+    feed.ssq.zero_()
+    feed.ssq[:, :M] = (x * x).reshape(M, K // 16, 16).sum(-1).T
+    feed.filled = True
+    return feed
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
     ap.add_argument("kernel", choices=["gemm_tc", "gemm_stream", "rows_add", "rows_swiglu", "rows_qkv", "attn_decode", "flash_prefill", "flash_prefill_tc", "rmsnorm"])
@@ -60,6 +71,9 @@ def main(argv=None) -> int:
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no-flush", dest="flush", action="store_false")
+    ap.add_argument("--prepared-norm", action="store_true",
+                    help="rows_swiglu, rows_qkv: the rows come as a prepared norm (x times the norm's weight and the pieces of "
+                         "the sums of squares, as the product before leaves them) instead of the residual rows")
     a = ap.parse_args(argv)
 
     from . import fast, ops
@@ -78,6 +92,9 @@ def main(argv=None) -> int:
         elif a.kernel == "rows_swiglu":
             x, act = rnd(M, K), torch.empty(M, N // 2, device=dev, dtype=torch.bfloat16)
             fn = lambda: fast.rows_norm_swiglu(x, nw, 1e-5, w, act, 16)
+            if a.prepared_norm:
+                feed = _prepared(fast, x, nw)
+                fn = lambda: fast.rows_scaled_swiglu(feed, M, w, act, 16)
         else:
             Hq, Hkv, D = a.heads, a.kv_heads, a.head_dim
             N = (Hq + 2 * Hkv) * D
@@ -89,6 +106,9 @@ def main(argv=None) -> int:
             vc = torch.zeros_like(kc)
             slots = (torch.arange(M, dtype=torch.int32, device=dev) * a.page_size)
             fn = lambda: fast.rows_norm_qkv_rope(x, nw, 1e-5, w, pos, slots, table, q, kc, vc, Hq, Hkv, D, D, a.page_size)
+            if a.prepared_norm:
+                feed = _prepared(fast, x, nw)
+                fn = lambda: fast.rows_scaled_qkv_rope(feed, M, w, pos, slots, table, q, kc, vc, Hq, Hkv, D, D, a.page_size)
         assert fn(), "the rows kernel does not take these sizes"
         ms = timeit(fn, a.iters, a.flush)
         out.update(M=M, N=N, K=K, ms=ms, gbs=N * K * 2 / ms / 1e6)
