@@ -555,12 +555,15 @@ __device__ __forceinline__ float sample_uniform(uint32_t seed, uint32_t position
   return ((float)(h >> 8) + 0.5f) * (1.0f / 16777216.0f);
 }
 
-// Entries [s * slice, (s + 1) * slice) of row blockIdx.y: the best key of the slice to part[row][s], or, when the
-// slice is the whole row (part null), its index to out[row].
+// Entries [s * slice, (s + 1) * slice) of row blockIdx.y. One slice (best null): its best index goes to out[row]. Several:
+// the slice's best key meets the others' in best[row] by an atomic maximum (the order of the arrivals does not matter: the
+// keys are totally ordered), and the block that arrives last writes the row's index and leaves best[row] and count[row]
+// zero for the next call: no second kernel.
 __global__ void __launch_bounds__(1024) sample_slice_kernel(const float* __restrict__ logits, long ld, int V, int slice,
                                                             const float* __restrict__ temperature,
                                                             const uint32_t* __restrict__ seed, const int* __restrict__ position,
-                                                            unsigned long long* __restrict__ part, int* __restrict__ out) {
+                                                            unsigned long long* __restrict__ best, int* __restrict__ count,
+                                                            int* __restrict__ out) {
   __shared__ unsigned long long sh[32];
   hb_pdl_launch();
   hb_pdl_wait();
@@ -578,32 +581,25 @@ __global__ void __launch_bounds__(1024) sample_slice_kernel(const float* __restr
   }
   key = pick_block_max(key, sh);
   if (threadIdx.x == 0) {
-    if (part) part[(size_t)row * gridDim.x + s] = key;
-    else out[row] = pick_index(key);
+    if (!best) {
+      out[row] = pick_index(key);
+    } else {
+      atomicMax(&best[row], key);
+      __threadfence();
+      if (atomicAdd(&count[row], 1) == (int)gridDim.x - 1) {     // every slice of the row has arrived
+        __threadfence();
+        out[row] = pick_index(atomicExch(&best[row], 0ull));
+        count[row] = 0;
+      }
+    }
   }
 }
 
-// The second stage for large vocabularies: the best of a row's slices (one warp per row).
-__global__ void __launch_bounds__(32) sample_final_kernel(const unsigned long long* __restrict__ part, int n,
-                                                          int* __restrict__ out) {
-  hb_pdl_launch();
-  hb_pdl_wait();
-  const int row = blockIdx.x;
-  unsigned long long key = 0ull;
-  for (int i = threadIdx.x; i < n; i += 32) {
-    const unsigned long long k = part[(size_t)row * n + i];
-    key = k > key ? k : key;
-  }
-  for (int o = 16; o > 0; o >>= 1) {
-    const unsigned long long other = __shfl_xor_sync(0xffffffffu, key, o);
-    key = other > key ? other : key;
-  }
-  if (threadIdx.x == 0) out[row] = pick_index(key);
-}
-
-// Slices per row that hb_sample uses for a vocabulary of V (its workspace holds 2 * rows * slices 32-bit words).
+// Slices per row that hb_sample uses for a vocabulary of V.
 HB_EXPORT int hb_sample_slices(int V) { return V <= 4096 ? 1 : (V + 2047) / 2048 > 128 ? 128 : (V + 2047) / 2048; }
 
+// workspace (needed when hb_sample_slices(V) > 1): 12 bytes a row, 8-byte aligned, all zero; the call leaves it zero.
+// Calls that share it must not overlap.
 HB_EXPORT int hb_sample(const float* logits, long ld, int rows, int V, const float* temperature, const uint32_t* seed,
                         const int* position, int* out, void* workspace, cudaStream_t s) {
   if (rows <= 0) return 0;
@@ -613,13 +609,12 @@ HB_EXPORT int hb_sample(const float* logits, long ld, int rows, int V, const flo
   if (((uintptr_t)workspace & 7) != 0) HB_FAIL("hb_sample: the workspace must be 8-byte aligned");
   if (n == 1 || !workspace) {
     hb_launch(sample_slice_kernel, dim3(1, rows), 1024, 0, s, logits, ld, V, V, temperature, seed, position,
-              (unsigned long long*)nullptr, out);
+              (unsigned long long*)nullptr, (int*)nullptr, out);
   } else {
-    unsigned long long* part = (unsigned long long*)workspace;     // rows * n keys
+    unsigned long long* best = (unsigned long long*)workspace;     // rows keys, then rows counters
     const int slice = (V + n - 1) / n;
-    hb_launch(sample_slice_kernel, dim3(n, rows), 256, 0, s, logits, ld, V, slice, temperature, seed, position, part,
-              (int*)nullptr);
-    hb_launch(sample_final_kernel, rows, 32, 0, s, (const unsigned long long*)part, n, out);
+    hb_launch(sample_slice_kernel, dim3(n, rows), 256, 0, s, logits, ld, V, slice, temperature, seed, position, best,
+              (int*)(best + rows), out);
   }
   HB_CHECK_LAUNCH("hb_sample");
   return 0;

@@ -275,12 +275,25 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], seed: Opti
         assert seed is not None and seed.dtype in (torch.int32, torch.uint32) and seed.numel() == R
         assert position is not None and position.dtype == torch.int32 and position.numel() == R
     n = library.load("core").hb_sample_slices(V)
-    ws = torch.empty(2 * R * n, dtype=torch.int32, device=logits.device) if n > 1 else None
-    if n > 1:
-        library.launches[0] += 1     # two kernels: the slices' candidates, then the pick among them
+    ws = _sample_workspace(logits.device, R) if n > 1 else None
     _call("core", "hb_sample", logits.data_ptr(), logits.stride(0), R, V, _ptr(temperature), _ptr(seed),
           _ptr(position), out.data_ptr(), _ptr(ws), _stream())
     return out
+
+
+_sample_ws = {}
+_sample_ws_retired = []
+
+
+def _sample_workspace(device, rows):
+    """Zeroed words in which the slices of a large vocabulary meet (12 bytes a row: the kernel leaves them zero); one
+    buffer per device, shared by all calls (they run one after the other on the step's stream)."""
+    ws = _sample_ws.get(device)
+    if ws is None or ws.numel() < 3 * rows:
+        if ws is not None:
+            _sample_ws_retired.append(ws)       # a captured CUDA graph may still hold the old address
+        ws = _sample_ws[device] = torch.zeros(3 * max(rows, 256), dtype=torch.int32, device=device)
+    return ws
 
 
 def feed_tokens(tokens: torch.Tensor, src: torch.Tensor, token_map: torch.Tensor) -> torch.Tensor:
