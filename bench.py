@@ -407,8 +407,8 @@ def breakdown(layers: int, batch: int, prefill: bool = False) -> int:
     span = step[-1]["ts"] + step[-1]["dur"] - t0
     what = f"prefill step of {PREFILL_TOKENS} tokens" if prefill else f"decode step at batch {batch}, context {PROMPT_LEN}+"
     print(f"{what}: {per} kernels, {span:.1f} us from the first kernel's start to the last one's end")
-    # besides the layers: embedding, last norm, head, and in a decode step two kernels of sampling
-    per_layer = max(1, (per - (3 if prefill else 5)) // max(1, layers))
+    # besides the layers: embedding, last norm, head, and in a decode step the sampling kernel
+    per_layer = max(1, (per - (3 if prefill else 4)) // max(1, layers))
     lo = min(len(step) - 1, 1 + per_layer * (layers // 2))
     print(f"kernels {lo}..{lo + per_layer - 1} (one layer): start, duration, end minus the end of the kernel before")
     prev_end = max(e["ts"] + e["dur"] for e in step[:lo]) if lo else t0
